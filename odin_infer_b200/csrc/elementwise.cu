@@ -1,0 +1,171 @@
+// Row-wise kernels: embedding gather, residual add fused with RMSNorm,
+// SwiGLU, element type conversion.
+//
+// RMSNorm follows the reference's order of operations (infer/ops.odin:7-19):
+//   ss = sum x^2; ss /= n; ss += eps; r = 1/sqrt(ss); o = w * (r * x)
+// all in 32-bit.  The residual stream x is 32-bit in both precisions.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+template <typename TW>
+__global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
+                             float* __restrict__ out, int d, int V) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const bool ok = (id >= 0 && id < V);
+    const TW* row = table + (size_t)(ok ? id : 0) * d;
+    float* o = out + (size_t)t * d;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) o[j] = ok ? to_f32(row[j]) : 0.f;
+}
+
+extern "C" int odin_embed(const void* table, int table_dtype, const int* ids, float* out,
+                          int T, int d, int V, void* stream) {
+    if (T <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = d >= 1024 ? 256 : 128;
+    if (table_dtype == ODIN_BF16)
+        embed_kernel<bf16><<<T, threads, 0, s>>>((const bf16*)table, ids, out, d, V);
+    else if (table_dtype == ODIN_F32)
+        embed_kernel<float><<<T, threads, 0, s>>>((const float*)table, ids, out, d, V);
+    else
+        return ODIN_ERR_UNSUPPORTED;
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ------------------------------------------------- residual add + RMSNorm
+// One block per output row.  x_new = x + sum_s delta[s] (32-bit), written
+// back to x when there is no row gather; out = w * (r * x_new).
+// The sum of squares goes over the columns in an order fixed by the block
+// size alone, so a row's result does not depend on the other rows.
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_split,
+                                   size_t split_stride, VecRef w, float eps, TO* __restrict__ out,
+                                   const int* __restrict__ rows, int d) {
+    __shared__ float red[32];
+    extern __shared__ float rowbuf[];  // d floats
+    const int r = blockIdx.x;
+    int src = r;
+    if (rows != nullptr) src = rows[r];
+    TO* o = out + (size_t)r * d;
+    if (src < 0) {
+        for (int j = threadIdx.x; j < d; j += blockDim.x) o[j] = from_f32<TO>(0.f);
+        return;
+    }
+    float* xr = x + (size_t)src * d;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        float v = xr[j];
+        if (delta != nullptr) {
+            for (int sidx = 0; sidx < n_split; ++sidx)
+                v += to_f32(delta[(size_t)sidx * split_stride + (size_t)src * d + j]);
+        }
+        rowbuf[j] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    ss /= (float)d;
+    ss += eps;
+    const float rs = 1.0f / sqrtf(ss);
+    const bool write_back = (delta != nullptr) && (rows == nullptr);
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        const float v = rowbuf[j];
+        if (write_back) xr[j] = v;
+        o[j] = from_f32<TO>(w.at(j) * (rs * v));
+    }
+}
+
+template <typename TD, typename TO>
+static int launch_add_rmsnorm(float* x, const void* delta, int n_split, size_t split_stride, VecRef w,
+                              float eps, void* out, const int* rows, int n_rows, int d, cudaStream_t s) {
+    const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+    const size_t smem = (size_t)d * sizeof(float);
+    if (smem > 200 * 1024) return ODIN_ERR_UNSUPPORTED;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    add_rmsnorm_kernel<TD, TO><<<n_rows, threads, smem, s>>>(x, (const TD*)delta, n_split, split_stride, w,
+                                                             eps, (TO*)out, rows, d);
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}
+
+// x: [*, d] 32-bit residual stream.  delta: null, or [n_split][*, d] partial
+// sums of element type delta_dtype, split_stride elements apart.  rows: null
+// (row r of x -> row r of out, x updated in place), or n_rows source row
+// numbers (gather; x is not written; a negative number gives a zero row).
+extern "C" int odin_add_rmsnorm(float* x, const void* delta, int delta_dtype, int n_split,
+                                long long split_stride, const void* w, int w_dtype, float eps, void* out,
+                                int out_dtype, const int* rows, int n_rows, int d, void* stream) {
+    if (n_rows <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    VecRef wr{w, w_dtype == ODIN_BF16};
+    if (delta == nullptr) delta_dtype = ODIN_F32;
+    if (delta_dtype == ODIN_F32 && out_dtype == ODIN_F32)
+        return launch_add_rmsnorm<float, float>(x, delta, n_split, split_stride, wr, eps, out, rows, n_rows, d, s);
+    if (delta_dtype == ODIN_F32 && out_dtype == ODIN_BF16)
+        return launch_add_rmsnorm<float, bf16>(x, delta, n_split, split_stride, wr, eps, out, rows, n_rows, d, s);
+    if (delta_dtype == ODIN_BF16 && out_dtype == ODIN_BF16)
+        return launch_add_rmsnorm<bf16, bf16>(x, delta, n_split, split_stride, wr, eps, out, rows, n_rows, d, s);
+    if (delta_dtype == ODIN_BF16 && out_dtype == ODIN_F32)
+        return launch_add_rmsnorm<bf16, float>(x, delta, n_split, split_stride, wr, eps, out, rows, n_rows, d, s);
+    return ODIN_ERR_UNSUPPORTED;
+}
+
+// -------------------------------------------------------------------- SwiGLU
+// gu: [T, 2I], gate in columns [0, I), up in [I, 2I).  h = g * (1/(1+exp(-g))) * u
+// in that order of products (infer/forward.odin:128-133).
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I;
+        const int j = (int)(idx - t * I);
+        float g = to_f32(gu[t * 2 * (size_t)I + j]);
+        const float u = to_f32(gu[t * 2 * (size_t)I + I + j]);
+        g *= 1.0f / (1.0f + expf(-g));
+        g *= u;
+        out[idx] = from_f32<T>(g);
+    }
+}
+
+extern "C" int odin_swiglu(const void* gu, void* out, int dtype, int T, int I, void* stream) {
+    if (T <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t total = (size_t)T * I;
+    const int threads = 256;
+    size_t blocks = (total + threads - 1) / threads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == ODIN_BF16)
+        swiglu_kernel<bf16><<<(int)blocks, threads, 0, s>>>((const bf16*)gu, (bf16*)out, I, total);
+    else if (dtype == ODIN_F32)
+        swiglu_kernel<float><<<(int)blocks, threads, 0, s>>>((const float*)gu, (float*)out, I, total);
+    else
+        return ODIN_ERR_UNSUPPORTED;
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------- cast
+template <typename TI, typename TO>
+__global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = from_f32<TO>(to_f32(in[i]));
+}
+
+extern "C" int odin_cast(const void* in, int in_dtype, void* out, int out_dtype, long long n, void* stream) {
+    if (n <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    size_t blocks = ((size_t)n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (in_dtype == ODIN_F32 && out_dtype == ODIN_BF16)
+        cast_kernel<float, bf16><<<(int)blocks, 256, 0, s>>>((const float*)in, (bf16*)out, (size_t)n);
+    else if (in_dtype == ODIN_BF16 && out_dtype == ODIN_F32)
+        cast_kernel<bf16, float><<<(int)blocks, 256, 0, s>>>((const bf16*)in, (float*)out, (size_t)n);
+    else
+        return ODIN_ERR_UNSUPPORTED;
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}

@@ -1,0 +1,109 @@
+// Per-head preparation of the fused q|k|v projection, one warp per (token, head):
+//   q heads: RMSNorm over the head (optional), rotation, written back in place;
+//   k heads: RMSNorm (optional), rotation, written to the paged key cache;
+//   v heads: copied to the paged value cache.
+// Restates infer/forward.odin:58-85 (norm before rotation, one [hd] weight shared
+// by all heads, half-split pairs (i, i + rot/2)) and the cache write of :47-49.
+// The rotation reads cos/sin of 32-bit angles from a table built on the host.
+// All arithmetic is 32-bit.
+//
+// Cache layout of one layer: [page][kv head][slot in page][hd]; a sequence's
+// pages are named by its row of the block table.
+#include "common.cuh"
+
+#define HP_WARPS 4
+#define HP_MAX_HD 512
+
+template <typename T>
+__global__ void __launch_bounds__(HP_WARPS * 32)
+head_prep_kernel(T* __restrict__ qkv, int Hq, int Hkv, int hd, size_t row_stride, VecRef qw, VecRef kw,
+                 int has_norm, float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                 int rot, int table_len, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                 const int* __restrict__ block_table, int bt_stride, T* __restrict__ k_cache,
+                 T* __restrict__ v_cache, int page_size, int write_kv) {
+    __shared__ float buf[HP_WARPS][HP_MAX_HD];
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.y * HP_WARPS + warp;
+    const int n_heads = Hq + 2 * Hkv;
+    if (head >= n_heads) return;
+    const int seq = tok_seq[t];
+    if (seq < 0) return;  // padding token
+    const int pos = tok_pos[t];
+    T* src = qkv + (size_t)t * row_stride + (size_t)head * hd;
+
+    const bool is_q = head < Hq;
+    const bool is_k = !is_q && head < Hq + Hkv;
+    const int kvh = is_q ? 0 : (is_k ? head - Hq : head - Hq - Hkv);
+    if (!is_q && !write_kv) return;
+
+    T* dst = src;
+    if (!is_q) {
+        const int page = block_table[(size_t)seq * bt_stride + pos / page_size];
+        if (page < 0) return;
+        T* base = is_k ? k_cache : v_cache;
+        dst = base + (((size_t)page * Hkv + kvh) * page_size + (pos % page_size)) * hd;
+    }
+
+    if (!is_q && !is_k) {  // value head: plain copy
+        for (int j = lane; j < hd; j += 32) dst[j] = src[j];
+        return;
+    }
+
+    float* b = buf[warp];
+    float ss = 0.f;
+    for (int j = lane; j < hd; j += 32) {
+        const float v = to_f32(src[j]);
+        b[j] = v;
+        ss += v * v;
+    }
+    if (has_norm) {
+        ss = warp_sum(ss);
+        ss /= (float)hd;
+        ss += eps;
+        const float r = 1.0f / sqrtf(ss);
+        const VecRef& w = is_q ? qw : kw;
+        for (int j = lane; j < hd; j += 32) b[j] = w.at(j) * (r * b[j]);
+    }
+    __syncwarp();
+    const int half = rot >> 1;
+    const bool in_table = (pos >= 0 && pos < table_len);
+    for (int j = lane; j < hd; j += 32) {
+        float o;
+        if (j < rot && in_table) {
+            const int i = (j < half) ? j : j - half;
+            const float c = cos_t[(size_t)pos * half + i], s = sin_t[(size_t)pos * half + i];
+            const float x = b[i], y = b[i + half];
+            o = (j < half) ? (x * c - y * s) : (x * s + y * c);
+        } else {
+            o = b[j];
+        }
+        dst[j] = from_f32<T>(o);
+    }
+}
+
+extern "C" int odin_head_prep(void* qkv, int dtype, int T, int Hq, int Hkv, int hd, long long row_stride,
+                              const void* q_norm_w, const void* k_norm_w, int w_dtype, int has_norm, float eps,
+                              const float* cos_t, const float* sin_t, int rot, int table_len,
+                              const int* tok_pos, const int* tok_seq, const int* block_table, int bt_stride,
+                              void* k_cache, void* v_cache, int page_size, int write_kv, void* stream) {
+    if (T <= 0) return 0;
+    if (hd > HP_MAX_HD || hd <= 0 || (rot & 1) || rot > hd || rot < 0) return ODIN_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int n_heads = Hq + 2 * Hkv;
+    dim3 grid(T, (n_heads + HP_WARPS - 1) / HP_WARPS);
+    if (grid.y > 65535) return ODIN_ERR_UNSUPPORTED;
+    VecRef qw{q_norm_w, w_dtype == ODIN_BF16}, kw{k_norm_w, w_dtype == ODIN_BF16};
+    if (dtype == ODIN_BF16)
+        head_prep_kernel<bf16><<<grid, HP_WARPS * 32, 0, s>>>(
+            (bf16*)qkv, Hq, Hkv, hd, (size_t)row_stride, qw, kw, has_norm, eps, cos_t, sin_t, rot, table_len,
+            tok_pos, tok_seq, block_table, bt_stride, (bf16*)k_cache, (bf16*)v_cache, page_size, write_kv);
+    else if (dtype == ODIN_F32)
+        head_prep_kernel<float><<<grid, HP_WARPS * 32, 0, s>>>(
+            (float*)qkv, Hq, Hkv, hd, (size_t)row_stride, qw, kw, has_norm, eps, cos_t, sin_t, rot, table_len,
+            tok_pos, tok_seq, block_table, bt_stride, (float*)k_cache, (float*)v_cache, page_size, write_kv);
+    else
+        return ODIN_ERR_UNSUPPORTED;
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}

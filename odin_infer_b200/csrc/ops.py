@@ -1,0 +1,196 @@
+"""Python bindings of the kernels: torch tensors in, raw pointers out.
+
+Every function launches on torch's current CUDA stream (so a CUDA graph
+capture records it), checks its arguments on the host, and raises on any
+error code.  There is no fallback of any kind: a tensor that is not on a
+CUDA device is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from . import build
+
+PAGE = 64  # tokens per cache page
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DT[dt]
+    except KeyError:
+        raise KernelError(f"unsupported element type {dt}; kernels take float32 and bfloat16") from None
+
+
+def _ptr(t: torch.Tensor | None) -> c_void_p:
+    if t is None:
+        return c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError("kernel argument is not on a CUDA device (there is no CPU path)")
+    return c_void_p(t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+_ERRORS = {-1: "unsupported size or element type", -2: "bad argument", -3: "device wait ran out"}
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        msg = _ERRORS.get(code, f"CUDA error {code}")
+        raise KernelError(f"{what}: {msg}")
+
+
+def _fn(group: str, name: str):
+    f = getattr(build.load(group), name)
+    f.restype = c_int
+    return f
+
+
+# ----------------------------------------------------------------------------
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, :] = table[ids[t], :] as 32-bit floats; ids int32 [T]."""
+    T, d = out.shape
+    assert out.dtype == torch.float32 and ids.dtype == torch.int32 and table.shape[1] == d
+    assert table.is_contiguous() and out.is_contiguous()
+    _check(_fn("elementwise", "odin_embed")(
+        _ptr(table), c_int(dtype_code(table.dtype)), _ptr(ids), _ptr(out), c_int(T), c_int(d),
+        c_int(table.shape[0]), _stream()), "embed")
+
+
+def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: torch.Tensor | None = None) -> None:
+    """x += sum of delta's leading splits (in place, 32-bit); out = RMSNorm(x) * weight.
+
+    x: [n, d] float32.  delta: None, [n, d] or [splits, n, d].  rows: None, or
+    int32 row numbers to gather (then x is left as it is).
+    """
+    d = x.shape[-1]
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
+    n_split, stride = 1, 0
+    if delta is not None:
+        assert delta.is_contiguous() and delta.shape[-1] == d
+        if delta.dim() == 3:
+            n_split, stride = delta.shape[0], delta.shape[1] * d
+            assert delta.shape[1] == x.shape[0]
+        else:
+            assert delta.shape[0] == x.shape[0]
+    n_rows = out.shape[0]
+    if rows is None:
+        assert n_rows == x.shape[0]
+    else:
+        assert rows.dtype == torch.int32 and rows.numel() == n_rows
+    assert weight.numel() == d
+    _check(_fn("elementwise", "odin_add_rmsnorm")(
+        _ptr(x), _ptr(delta), c_int(dtype_code(delta.dtype) if delta is not None else 0), c_int(n_split),
+        c_longlong(stride), _ptr(weight), c_int(dtype_code(weight.dtype)), c_float(eps), _ptr(out),
+        c_int(dtype_code(out.dtype)), _ptr(rows), c_int(n_rows), c_int(d), _stream()), "add_rmsnorm")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out = silu(gate) * up for gate_up = [T, 2I] (gate columns first)."""
+    T, I = out.shape
+    assert gate_up.shape == (T, 2 * I) and gate_up.dtype == out.dtype
+    assert gate_up.is_contiguous() and out.is_contiguous()
+    _check(_fn("elementwise", "odin_swiglu")(
+        _ptr(gate_up), _ptr(out), c_int(dtype_code(out.dtype)), c_int(T), c_int(I), _stream()), "swiglu")
+
+
+def cast(src: torch.Tensor, dst: torch.Tensor) -> None:
+    assert src.is_contiguous() and dst.is_contiguous() and src.numel() == dst.numel()
+    _check(_fn("elementwise", "odin_cast")(
+        _ptr(src), c_int(dtype_code(src.dtype)), _ptr(dst), c_int(dtype_code(dst.dtype)),
+        c_longlong(src.numel()), _stream()), "cast")
+
+
+def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = a[M, K] @ w[N, K]^T on the CUDA cores with 32-bit accumulation."""
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N)
+    assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    _check(_fn("gemm_plain", "odin_gemm_plain")(
+        _ptr(a), c_int(dtype_code(a.dtype)), _ptr(w), c_int(dtype_code(w.dtype)), _ptr(out),
+        c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K), c_longlong(a.stride(0)),
+        c_longlong(w.stride(0)), c_longlong(out.stride(0)), _stream()), "gemm_plain")
+
+
+def head_prep(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, q_norm: torch.Tensor | None,
+              k_norm: torch.Tensor | None, eps: float, cos: torch.Tensor, sin: torch.Tensor, rotary_dim: int,
+              tok_pos: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
+              k_cache: torch.Tensor | None, v_cache: torch.Tensor | None, write_kv: bool = True) -> None:
+    """Per-head RMSNorm and rotation of q (in place) and k, and the cache write of k and v."""
+    T = qkv.shape[0]
+    assert qkv.stride(1) == 1 and qkv.shape[1] == (n_q + 2 * n_kv) * head_dim
+    assert cos.dtype == torch.float32 and sin.dtype == torch.float32
+    assert tok_pos.dtype == torch.int32 and tok_seq.dtype == torch.int32 and block_table.dtype == torch.int32
+    has_norm = q_norm is not None
+    if has_norm:
+        assert k_norm is not None and q_norm.dtype == k_norm.dtype
+        assert q_norm.numel() == head_dim and k_norm.numel() == head_dim
+    if write_kv:
+        assert k_cache is not None and v_cache is not None
+        assert k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
+        assert k_cache.is_contiguous() and v_cache.is_contiguous()
+        assert tuple(k_cache.shape[1:]) == (n_kv, PAGE, head_dim), "cache layout is [page][kv head][64][hd]"
+    _check(_fn("head_prep", "odin_head_prep")(
+        _ptr(qkv), c_int(dtype_code(qkv.dtype)), c_int(T), c_int(n_q), c_int(n_kv), c_int(head_dim),
+        c_longlong(qkv.stride(0)), _ptr(q_norm), _ptr(k_norm),
+        c_int(dtype_code(q_norm.dtype) if has_norm else 0), c_int(1 if has_norm else 0), c_float(eps),
+        _ptr(cos), _ptr(sin), c_int(rotary_dim), c_int(cos.shape[0]), _ptr(tok_pos), _ptr(tok_seq),
+        _ptr(block_table), c_int(block_table.stride(0)), _ptr(k_cache), _ptr(v_cache), c_int(PAGE),
+        c_int(1 if write_kv else 0), _stream()), "head_prep")
+
+
+def attention_plain(q: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
+                    k_cache: torch.Tensor, v_cache: torch.Tensor, tok_pos: torch.Tensor, tok_seq: torch.Tensor,
+                    block_table: torch.Tensor, window: int = 0) -> None:
+    """Causal attention of each token over its sequence's cache; q may be a strided view."""
+    T = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_cache.dtype
+    assert q.shape[1] == n_q * head_dim and out.shape == (T, n_q * head_dim)
+    assert tuple(k_cache.shape[1:]) == (n_kv, PAGE, head_dim) and k_cache.is_contiguous()
+    _check(_fn("attention_plain", "odin_attention_plain")(
+        _ptr(q), c_longlong(q.stride(0)), _ptr(out), c_longlong(out.stride(0)), c_int(dtype_code(q.dtype)),
+        c_int(T), c_int(n_q), c_int(n_kv), c_int(head_dim), _ptr(k_cache), _ptr(v_cache), c_int(PAGE),
+        _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table), c_int(block_table.stride(0)), c_int(window),
+        _stream()), "attention_plain")
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[b] = index of the first maximum of logits[b, :] (float32)."""
+    B, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
+    _check(_fn("sampling", "odin_argmax")(
+        _ptr(logits), c_longlong(logits.stride(0)), c_int(B), c_int(V), _ptr(out), _stream()), "argmax")
+
+
+def sample(logits: torch.Tensor, temperature: float, top_p: float, coins: torch.Tensor,
+           out: torch.Tensor) -> None:
+    """Temperature (and top-p) draw, one coin in [0, 1) per row."""
+    B, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    assert coins.dtype == torch.float32 and coins.numel() >= B and out.dtype == torch.int32
+    _check(_fn("sampling", "odin_sample")(
+        _ptr(logits), c_longlong(logits.stride(0)), c_int(B), c_int(V), c_float(temperature),
+        c_float(top_p), _ptr(coins), _ptr(out), _stream()), "sample")
+
+
+def repetition_penalty(logits: torch.Tensor, recent: torch.Tensor, penalty: float) -> None:
+    """In place on logits (a copy of the model's): recent is int32 [B, W], negative = empty."""
+    B, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    assert recent.dtype == torch.int32 and recent.is_contiguous() and recent.shape[0] == B
+    _check(_fn("sampling", "odin_repetition_penalty")(
+        _ptr(logits), c_longlong(logits.stride(0)), c_int(B), c_int(V), _ptr(recent),
+        c_int(recent.shape[1]), c_float(penalty), _stream()), "repetition_penalty")

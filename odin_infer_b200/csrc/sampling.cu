@@ -1,0 +1,202 @@
+// Sampling over rows of 32-bit logits, one thread block per sequence.
+//
+// Restates sampler/sampler.odin on the device:
+//   argmax: the first maximum wins (strict >, :79-89);
+//   temperature: logits / T, softmax with the maximum subtracted, one coin in
+//     [0,1) per token, walk of the cumulative sum in index order (:91-100, :179-185);
+//   top-p: keep the most probable tokens until their sum first exceeds topp
+//     (:106-139), then draw among the kept ones;
+//   repetition penalty: each distinct recent token has a positive logit divided
+//     and a negative one multiplied (:143-160).
+// The logits are never modified by the sampling kernels (the reference
+// overwrites the caller's logits with probabilities; this does not).
+// All sums run in an order fixed by the block size, so a seed gives the same
+// tokens whatever else is in the batch.
+#include "common.cuh"
+#include <math_constants.h>
+
+#define SB 1024  // threads per block
+
+// ------------------------------------------------------------------ argmax
+__global__ void __launch_bounds__(SB) argmax_kernel(const float* __restrict__ logits, size_t ld, int V,
+                                                    int* __restrict__ out) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const float* row = logits + (size_t)blockIdx.x * ld;
+    float best = -CUDART_INF_F;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += SB) {
+        const float v = row[i];
+        if (v > best || bi == 0x7fffffff) { best = v; bi = i; }
+    }
+    // NaN-free logits assumed; ties go to the lower index.
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        best = sv[lane];
+        bi = si[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (lane == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
+    }
+}
+
+extern "C" int odin_argmax(const float* logits, long long ld, int B, int V, int* out, void* stream) {
+    if (B <= 0) return 0;
+    if (V <= 0) return ODIN_ERR_BAD_ARG;
+    argmax_kernel<<<B, SB, 0, (cudaStream_t)stream>>>(logits, (size_t)ld, V, out);
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ------------------------------------------------- temperature / top-p draw
+__device__ __forceinline__ float block_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = red[lane];  // SB = 1024 threads = 32 warps
+    return warp_max(t);
+}
+
+// Sum of e_i = exp(l_i / T - m) over the tokens with e_i >= thr.
+__device__ __forceinline__ float masked_sum(const float* row, int V, float inv_t, float m, float thr, float* red) {
+    float s = 0.f;
+    for (int i = threadIdx.x; i < V; i += SB) {
+        const float e = expf(row[i] * inv_t - m);
+        if (e >= thr) s += e;
+    }
+    return block_sum(s, red);
+}
+
+__global__ void __launch_bounds__(SB) sample_kernel(const float* __restrict__ logits, size_t ld, int V,
+                                                    float temperature, float top_p,
+                                                    const float* __restrict__ coins, int* __restrict__ out) {
+    __shared__ float red[32];
+    __shared__ float chunk_sum[SB];
+    __shared__ int chosen;
+    const float* row = logits + (size_t)blockIdx.x * ld;
+    const float inv_t = 1.0f / temperature;
+    float mx = -CUDART_INF_F;
+    for (int i = threadIdx.x; i < V; i += SB) mx = fmaxf(mx, row[i] * inv_t);
+    mx = block_max(mx, red);
+    const float total = masked_sum(row, V, inv_t, mx, 0.f, red);
+
+    // threshold on e (unnormalised probability): keep e_i >= thr
+    float thr = 0.f;
+    if (top_p > 0.f && top_p < 1.f && V > 1) {
+        const float cutoff = (1.0f - top_p) / (float)(V - 1) * total;
+        const float target = top_p * total;
+        if (masked_sum(row, V, inv_t, mx, cutoff, red) <= target) {
+            thr = cutoff;  // the candidates together do not exceed topp: keep them all
+        } else {
+            // largest thr with sum(e >= thr) > target; positive floats order like their bits
+            unsigned lo = __float_as_uint(cutoff), hi = __float_as_uint(1.0f);  // e <= 1
+            // invariant: S(lo) > target, S(hi+) may not
+            while (lo < hi) {
+                const unsigned mid = lo + (hi - lo + 1) / 2;
+                if (masked_sum(row, V, inv_t, mx, __uint_as_float(mid), red) > target) lo = mid;
+                else hi = mid - 1;
+            }
+            thr = __uint_as_float(lo);
+        }
+    }
+    const float kept = (thr > 0.f) ? masked_sum(row, V, inv_t, mx, thr, red) : total;
+    const float target = coins[blockIdx.x] * kept;
+
+    // cumulative walk in index order: contiguous chunk per thread, then a scan
+    const int per = (V + SB - 1) / SB;
+    const int c0 = min(V, (int)threadIdx.x * per), c1 = min(V, c0 + per);
+    float cs = 0.f;
+    for (int i = c0; i < c1; ++i) {
+        const float e = expf(row[i] * inv_t - mx);
+        if (e >= thr) cs += e;
+    }
+    chunk_sum[threadIdx.x] = cs;
+    if (threadIdx.x == 0) chosen = -1;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // serial exclusive scan over 1024 chunk sums: fixed order
+        float run = 0.f;
+        int owner = -1;
+        for (int t = 0; t < SB; ++t) {
+            const float nxt = run + chunk_sum[t];
+            if (target < nxt) { owner = t; break; }
+            run = nxt;
+        }
+        if (owner >= 0) {
+            const int o0 = min(V, owner * per), o1 = min(V, o0 + per);
+            float cdf = run;
+            int pick = -1, last_kept = -1;
+            for (int i = o0; i < o1; ++i) {
+                const float e = expf(row[i] * inv_t - mx);
+                if (e >= thr) {
+                    cdf += e;
+                    last_kept = i;
+                    if (target < cdf) { pick = i; break; }
+                }
+            }
+            chosen = (pick >= 0) ? pick : last_kept;
+        }
+    }
+    __syncthreads();
+    if (chosen < 0) {
+        // rounding left the coin beyond the last sum: the last kept token (reference: n - 1)
+        int last = -1;
+        for (int i = threadIdx.x; i < V; i += SB) {
+            const float e = expf(row[i] * inv_t - mx);
+            if (e >= thr) last = max(last, i);
+        }
+        float lf = block_max((float)last, red);
+        if (threadIdx.x == 0) chosen = (int)lf;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = max(chosen, 0);
+}
+
+extern "C" int odin_sample(const float* logits, long long ld, int B, int V, float temperature, float top_p,
+                           const float* coins, int* out, void* stream) {
+    if (B <= 0) return 0;
+    if (V <= 0 || !(temperature > 0.f)) return ODIN_ERR_BAD_ARG;
+    sample_kernel<<<B, SB, 0, (cudaStream_t)stream>>>(logits, (size_t)ld, V, temperature, top_p, coins, out);
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ------------------------------------------------------ repetition penalty
+// recent: [B, W] token ids, negative = empty.  logits are changed in place (the
+// caller passes a copy).
+__global__ void repetition_penalty_kernel(float* __restrict__ logits, size_t ld, int V,
+                                          const int* __restrict__ recent, int W, float penalty) {
+    float* row = logits + (size_t)blockIdx.x * ld;
+    const int* rec = recent + (size_t)blockIdx.x * W;
+    for (int j = threadIdx.x; j < W; j += blockDim.x) {
+        const int tok = rec[j];
+        if (tok < 0 || tok >= V) continue;
+        bool dup = false;
+        for (int i = 0; i < j; ++i) dup |= (rec[i] == tok);
+        if (dup) continue;
+        const float v = row[tok];
+        row[tok] = (v > 0.f) ? v / penalty : v * penalty;
+    }
+}
+
+extern "C" int odin_repetition_penalty(float* logits, long long ld, int B, int V, const int* recent, int W,
+                                       float penalty, void* stream) {
+    if (B <= 0 || W <= 0) return 0;
+    repetition_penalty_kernel<<<B, 128, 0, (cudaStream_t)stream>>>(logits, (size_t)ld, V, recent, W, penalty);
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}

@@ -1,0 +1,223 @@
+"""The engine: a loaded model, its cache, the step function and generation.
+
+The public names follow the reference's library API (infer/engine.odin):
+`Engine_Opts`, `engine_load`, `engine_forward`, `engine_config`,
+`engine_destroy`.  Where the reference runs one token of one sequence per call
+(infer/engine.odin:45), `Engine.step` runs a batch of sequences; the reference's
+single-sequence call is kept as `engine_forward(e, token, pos)` on top of it.
+"""
+from __future__ import annotations
+
+import dataclasses
+import sys
+
+import torch
+
+from ..cache import CacheManager, PAGE, pages_for
+from ..config import ModelConfig, load_config, lookup_architecture
+from ..csrc import build as kernel_build
+from ..sampling import SamplingParams, sample_batch
+from ..weights import load_weights, random_weights
+from .generate import GenerationResult, GenerationStats, generate
+from .model import DecoderModel
+from .runtime import Runtime
+from .step import StepBatch, StepEntry, StepError
+
+DEFAULT_MAX_CONTEXT = 4096  # infer/model.odin:10
+
+
+@dataclasses.dataclass
+class Engine_Opts:
+    """max_ctx: cap on a sequence's length (infer/engine.odin:7-11; 0: the model's own
+    limit, else min of both, infer/model.odin:220-223).  max_tokens: the most tokens
+    that live sequences hold together, each rounded up to a page of 64; it sizes the
+    cache (0: max_batch sequences of max_ctx).  dtype: "bfloat16" (the kernels and
+    precisions of serving) or "float32" (everything in true 32-bit)."""
+    max_ctx: int = DEFAULT_MAX_CONTEXT
+    max_tokens: int = 0
+    max_batch: int = 8
+    dtype: str = "bfloat16"
+    device: str = "cuda:0"
+    verbose: bool = True
+
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+class Engine:
+    def __init__(self, config: ModelConfig, opts: Engine_Opts, folder: str | None = None, seed: int | None = None):
+        if opts.dtype not in _DTYPES:
+            raise ValueError(f"dtype must be one of {sorted(_DTYPES)}, got {opts.dtype!r}")
+        if not torch.cuda.is_available():
+            raise RuntimeError("odin_infer_b200 runs on a CUDA device (sm_100a) only; there is no CPU path")
+        self.config = config
+        self.opts = opts
+        self.rt = Runtime(opts.device, _DTYPES[opts.dtype])
+        torch.cuda.set_device(self.rt.device)
+        spec = lookup_architecture(config.architecture).build_spec(config)
+        self.spec = spec
+        self.model = DecoderModel(spec)
+        self.vocab_size = spec.vocab_size
+
+        model_limit = spec.max_positions
+        self.max_ctx = min(model_limit, opts.max_ctx) if (model_limit and opts.max_ctx > 0) else (opts.max_ctx or model_limit)
+        if self.max_ctx <= 0:
+            self.max_ctx = DEFAULT_MAX_CONTEXT
+        self.max_batch = max(1, opts.max_batch)
+        max_tokens = opts.max_tokens or self.max_batch * pages_for(self.max_ctx) * PAGE
+        self.cache = CacheManager(max_tokens, self.max_ctx)
+        self.max_ctx = self.cache.max_seq_len
+        self.model.register_cache(self.cache)
+
+        kernel_build.ensure_built(sorted(self.model.kernel_groups() | self.rt.kernel_groups()), verbose=opts.verbose)
+        params = self.model.params()
+        if folder is not None:
+            tensors = load_weights(folder, params, self.rt.dtype, self.rt.device)
+        else:
+            tensors = random_weights(params, seed or 0, self.rt.dtype, self.rt.device)
+        self.weight_bytes = sum(t.numel() * t.element_size() for t in {id(t): t for t in tensors.values()}.values())
+        self.model.bind(tensors, self.rt, self.max_ctx)
+        del tensors
+
+        itemsize = 4 if self.rt.dtype == torch.float32 else 2
+        self.cache_bytes = 0
+        for g in self.cache.groups.values():
+            shape = g.storage_shape()
+            k = torch.empty(shape, dtype=self.rt.dtype, device=self.rt.device)
+            v = torch.empty(shape, dtype=self.rt.dtype, device=self.rt.device)
+            g.attach_storage(k, v)
+            self.cache_bytes += 2 * k.numel() * itemsize
+        nstate = self.cache.state_bytes_per_slot
+        self.cache.state = torch.zeros(self.cache.max_slots, nstate, dtype=torch.uint8, device=self.rt.device)
+        self.cache.zero_state = (lambda slot: self.cache.state[slot].zero_()) if nstate else None
+        if opts.verbose:
+            print(self.summary(), file=sys.stderr, flush=True)
+
+    # ---- construction ------------------------------------------------------
+    @classmethod
+    def load(cls, folder: str, opts: Engine_Opts | None = None) -> "Engine":
+        return cls(load_config(folder), opts or Engine_Opts(), folder=folder)
+
+    @classmethod
+    def random(cls, config: ModelConfig, seed: int, opts: Engine_Opts | None = None) -> "Engine":
+        """Random weights generated on the device (nothing is written)."""
+        return cls(config, opts or Engine_Opts(), seed=seed)
+
+    def summary(self) -> str:
+        """One line at load, as the reference prints (infer/model.odin:228-241)."""
+        c = self.config
+        return (f"odin_infer_b200: {c.architecture} {type(c).__name__} layers={len(self.spec.layers)} "
+                f"width={self.spec.width} vocab={self.vocab_size} ctx={self.max_ctx} dtype={self.opts.dtype} "
+                f"weights={self.weight_bytes / 2**30:.2f} GiB cache={self.cache_bytes / 2**20:.1f} MiB "
+                f"({self.cache.n_pages} pages of {PAGE} tokens, {len(self.cache.groups)} group(s), "
+                f"state {self.cache.state_bytes_per_slot} B/seq)")
+
+    # ---- slots ------------------------------------------------------------
+    def take_slot(self) -> int:
+        return self.cache.take_slot()
+
+    def give_back_slot(self, slot: int) -> None:
+        self.cache.give_back_slot(slot)
+
+    def fits(self, lengths: list[int]) -> bool:
+        """Can sequences of these lengths be live together (beside what is live now)?"""
+        need = sum(pages_for(n) for n in lengths)
+        free = min((g.pool.n_free for g in self.cache.groups.values()), default=need)
+        return need <= free and len(lengths) <= self.cache.n_free_slots
+
+    def default_stop_token_ids(self) -> tuple[int, ...]:
+        return tuple(self.spec.stop_token_ids)
+
+    # ---- the step function ---------------------------------------------
+    def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
+        """Run the given tokens of every entry as one batch from the cache; returns the
+        32-bit logits at the wanted places, [wanted, vocab], on the device, in the order
+        of the entries and of their `want` lists (None when nothing is wanted)."""
+        if not entries:
+            return None
+        seen = set()
+        for e in entries:
+            if e.slot in seen:
+                raise StepError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            if not self.cache.is_live(e.slot):
+                raise StepError(f"slot {e.slot} is not held by a sequence")
+            if len(e.tokens) == 0:
+                raise StepError(f"slot {e.slot}: a step must bring at least one token")
+            for t in e.tokens:
+                if not (0 <= t < self.vocab_size):  # infer/forward.odin:26-29
+                    raise StepError(f"slot {e.slot}: token {t} is out of range (vocab {self.vocab_size})")
+        starts, grown = [], []
+        try:
+            for e in entries:
+                starts.append(self.cache.extend(e.slot, len(e.tokens)))
+                grown.append(e)
+        except Exception:
+            for e, s in zip(grown, starts):  # leave the cache as it was
+                self._shrink(e.slot, s)
+            raise
+        batch = StepBatch(self.cache, entries, starts, self.rt.device)
+        logits = self.rt.run(self.model, batch)
+        for e in entries:
+            self.cache.after_step(e.slot)
+        return logits
+
+    def _shrink(self, slot: int, length: int) -> None:
+        have, keep = pages_for(self.cache.lengths[slot]), pages_for(length)
+        for g in self.cache.groups.values():
+            pages = [int(p) for p in g.block_table[slot, keep:have] if p >= 0]
+            g.pool.give_back(pages)
+            g.block_table[slot, keep:have] = -1
+        self.cache.lengths[slot] = length
+
+    # ---- sampling and generation ----------------------------------------
+    def sample(self, logits: torch.Tensor, samplers, params: SamplingParams) -> list[int]:
+        return sample_batch(logits, samplers, params)
+
+    def generate(self, prompts, max_new_tokens: int = 256, temperature: float = 0.0, top_p: float = 1.0,
+                 seed: int = 0, stop_token_ids=None, repetition_penalty: float = 1.0, include_stop_token: bool = False,
+                 stats: GenerationStats | None = None) -> list[GenerationResult]:
+        """prompts: lists of token ids.  Returns, in order, the generated tokens and why each ended."""
+        params = SamplingParams(temperature=temperature, top_p=top_p, seed=seed, repetition_penalty=repetition_penalty)
+        return generate(self, [list(map(int, p)) for p in prompts], max_new_tokens, params, stop_token_ids,
+                        include_stop_token, stats)
+
+    def destroy(self) -> None:
+        for g in self.cache.groups.values():
+            g.k = g.v = None
+        self.cache.state = None
+        self.model = None
+        torch.cuda.empty_cache()
+
+
+# ---- the reference's procedural API (infer/engine.odin:18-60) -----------------
+def engine_load(path: str, opts: Engine_Opts | None = None) -> Engine:
+    """infer/engine.odin:18-34.  Raises instead of exiting the process."""
+    return Engine.load(path, opts)
+
+
+def engine_config(e: Engine) -> ModelConfig:
+    """infer/engine.odin:54-56."""
+    return e.config
+
+
+def engine_forward(e: Engine, token: int, pos: int) -> torch.Tensor:
+    """One token of one sequence at position `pos`; returns its 32-bit logits [vocab]
+    (infer/engine.odin:45-52).  The engine keeps one slot for this call; pos 0 starts the
+    sequence afresh, any other pos must be the next position."""
+    slot = getattr(e, "_single_slot", None)
+    if pos == 0:
+        if slot is not None:
+            e.give_back_slot(slot)
+        slot = e._single_slot = e.take_slot()
+    if slot is None or e.cache.lengths[slot] != pos:
+        have = None if slot is None else e.cache.lengths[slot]
+        raise StepError(f"engine_forward: pos={pos} is not the next position (the sequence holds {have} tokens)")
+    if pos >= e.max_ctx:  # infer/forward.odin:22-25
+        raise StepError(f"engine_forward: pos={pos} out of range (seq_len={e.max_ctx})")
+    return e.step([StepEntry(slot, [int(token)], [0])])[0]
+
+
+def engine_destroy(e: Engine) -> None:
+    """infer/engine.odin:36-43."""
+    e.destroy()

@@ -1,0 +1,39 @@
+"""Dense feed-forward parts."""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from .base import FeedForward, ParamSpec, register_part
+
+
+@register_part("feed_forward", "swiglu")
+class SwiGLU(FeedForward):
+    """down( silu(gate(x)) * up(x) ), no bias (infer/forward.odin:125-135).  The gate
+    and up matrices are fused into one at load time."""
+
+    def __init__(self, width: int, inner: int, names: dict):
+        self.width, self.inner, self.names = width, inner, dict(names)
+        self.w_gate_up = self.w_down = None
+
+    def params(self):
+        n = self.names
+        return [ParamSpec(n["gate"], (self.inner, self.width)), ParamSpec(n["up"], (self.inner, self.width)),
+                ParamSpec(n["down"], (self.width, self.inner))]
+
+    def bind(self, tensors, rt):
+        n = self.names
+        g, u = tensors.pop(n["gate"]), tensors.pop(n["up"])
+        if g.dtype != u.dtype:
+            g, u = g.float(), u.float()
+        self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
+        self.w_down = tensors[n["down"]]
+
+    def kernel_groups(self):
+        return {"elementwise", "gemm_plain"}
+
+    def forward(self, rt, step, h):
+        gu = rt.linear(h, self.w_gate_up)
+        act = rt.empty(h.shape[0], self.inner)
+        ops.swiglu(gu, act)
+        return rt.linear(act, self.w_down, out_dtype=torch.float32)

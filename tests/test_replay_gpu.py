@@ -1,0 +1,115 @@
+"""The engine against the plain implementation, through trace replay: each request
+alone and whole; with its last 32 tokens one by one; in batches of unequal lengths
+whose shorter requests end earlier, batch after batch so that slots and pages are
+used again.  In 32-bit and in bfloat16, for tiny configurations that differ in
+every size and option."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from tests import tiny, traces
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [5, 11, 17, 70, 129], "B": [1, 7, 23, 40, 64, 65, 200], "C": [3, 33, 90]}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("models")
+    return {name: tiny.make_folder(root, raw, seed) for name, (raw, seed) in tiny.TINIES.items()}
+
+
+@pytest.fixture(scope="module")
+def requests_and_refs(folders):
+    out = {}
+    for name, folder in folders.items():
+        vocab = tiny.TINIES[name][0]["vocab_size"]
+        reqs = {f"r{i}": tiny.random_tokens(n, vocab, 100 + i) for i, n in enumerate(LENGTHS[name])}
+        refs = {rid: tiny.plain_logits(folder, toks) for rid, toks in reqs.items()}
+        out[name] = (reqs, refs)
+    return out
+
+
+def run(folder, dtype, recs):
+    from odin_infer_b200 import Engine, Engine_Opts
+    from odin_infer_b200.engine.trace import replay
+    n = traces.max_live_tokens(recs)
+    engine = Engine.load(folder, Engine_Opts(max_ctx=n, max_tokens=n, dtype=dtype, verbose=False))
+    try:
+        results = replay(engine, recs)
+        engine.cache.check()
+        assert all(g.pool.n_held == 0 for g in engine.cache.groups.values())
+        return traces.collect(recs, results)
+    finally:
+        engine.destroy()
+
+
+def check(got, refs, dtype, what):
+    worst = 0.0
+    for rid, ref in refs.items():
+        assert got[rid].shape == ref.shape, (what, rid, got[rid].shape, ref.shape)
+        for pos in range(ref.shape[0]):
+            err = tiny.rel_err(got[rid][pos], ref[pos])
+            worst = max(worst, err)
+            assert err <= tiny.TOL[dtype], f"{what} {dtype}: request {rid} first differs at position {pos}: {err:.3e}"
+    return worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_whole(folders, requests_and_refs, name, dtype):
+    reqs, refs = requests_and_refs[name]
+    check(run(folders[name], dtype, traces.whole(reqs)), refs, dtype, "whole")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_last_32_one_by_one(folders, requests_and_refs, name, dtype):
+    reqs, refs = requests_and_refs[name]
+    check(run(folders[name], dtype, traces.tail_one_by_one(reqs, 32)), refs, dtype, "last32")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_unequal_batches_slots_reused(folders, requests_and_refs, name, dtype):
+    reqs, refs = requests_and_refs[name]
+    check(run(folders[name], dtype, traces.batches(reqs, 3)), refs, dtype, "batches of 3")
+    check(run(folders[name], dtype, traces.batches(reqs, 2, first_part=lambda n: max(1, n - 5))), refs, dtype,
+          "batches of 2")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_cuts_agree_with_each_other(folders, requests_and_refs, dtype):
+    """The same position under different cuts: equal beyond rounding (far tighter than
+    the distance to the plain implementation in bfloat16)."""
+    reqs, _ = requests_and_refs["B"]
+    a = run(folders["B"], dtype, traces.whole(reqs))
+    b = run(folders["B"], dtype, traces.tail_one_by_one(reqs, 32))
+    c = run(folders["B"], dtype, traces.batches(reqs, 4))
+    tol = 1e-6 if dtype == "float32" else 2e-2
+    for rid in reqs:
+        assert tiny.rel_err(b[rid], a[rid].astype(np.float64)) <= tol
+        assert tiny.rel_err(c[rid], a[rid].astype(np.float64)) <= tol
+
+
+def test_trace_run_program(folders, requests_and_refs, tmp_path):
+    """The program itself: JSON lines in, .f32 files and `done` lines out."""
+    reqs, refs = requests_and_refs["A"]
+    recs = traces.batches(reqs, 3)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = str(tmp_path / "out")
+    proc = subprocess.run(
+        [sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folders["A"], "--dtype", "float32",
+         "--out", out, "--max-tokens", str(traces.max_live_tokens(recs))],
+        input="".join(json.dumps(r) + "\n" for r in recs), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {r['step']}" for r in recs]
+    vocab = tiny.TINY_A["vocab_size"]
+    results = {r["step"]: np.fromfile(os.path.join(out, f"{r['step']}.f32"), dtype="<f4").reshape(-1, vocab) for r in recs}
+    check(traces.collect(recs, results), refs, "float32", "trace_run")
