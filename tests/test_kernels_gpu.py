@@ -1,0 +1,283 @@
+"""Each kernel alone against a plain float32/float64 torch reference of the same
+operation, at sizes other than the engine's (odd widths, head sizes 16..160, groups
+1..5, vocabularies that are no power of two)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, k=1):
+    return (2e-6 if dtype == torch.float32 else 1e-2) * max(1.0, math.sqrt(k) / 8)
+
+
+def close(got, ref, rtol):
+    got, ref = got.double().cpu(), ref.double().cpu()
+    err = (got - ref).abs().max().item() / max(ref.abs().max().item(), 1e-30)
+    assert err <= rtol, f"relative error {err:.3e} > {rtol:.1e}"
+
+
+@pytest.mark.parametrize("table_dtype", DTYPES)
+def test_embed(table_dtype):
+    from odin_infer_b200.csrc import ops
+    V, d = 301, 72
+    table = torch.randn(V, d, device=DEV).to(table_dtype)
+    ids = torch.tensor([0, 300, 5, 5, 17], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, d, device=DEV)
+    ops.embed(table, ids, out)
+    assert torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("out_dtype", DTYPES)
+@pytest.mark.parametrize("w_dtype", DTYPES)
+@pytest.mark.parametrize("d", [72, 1000, 4096])
+def test_add_rmsnorm(d, w_dtype, out_dtype):
+    from odin_infer_b200.csrc import ops
+    n, eps = 7, 1e-5
+    x = torch.randn(n, d, device=DEV)
+    delta = torch.randn(3, n, d, device=DEV)
+    w = (1 + 0.1 * torch.randn(d, device=DEV)).to(w_dtype)
+    x0 = x.clone()
+    out = torch.empty(n, d, device=DEV, dtype=out_dtype)
+    ops.add_rmsnorm(x, delta, w, eps, out)
+    xr = x0.double() + delta.double().sum(0)
+    ref = w.double() * (xr / torch.sqrt((xr * xr).mean(-1, keepdim=True) + eps))
+    close(x, xr, 1e-6)
+    close(out, ref, 2e-6 if out_dtype == torch.float32 else 5e-3)
+    # gather of rows, no write-back, bf16 delta
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    d2 = torch.randn(n, d, device=DEV).bfloat16()
+    x1 = x.clone()
+    out2 = torch.empty(3, d, device=DEV, dtype=out_dtype)
+    ops.add_rmsnorm(x, d2, w, eps, out2, rows)
+    assert torch.equal(x, x1)
+    xr2 = (x1.double() + d2.double())[rows.long()]
+    ref2 = w.double() * (xr2 / torch.sqrt((xr2 * xr2).mean(-1, keepdim=True) + eps))
+    close(out2, ref2, 2e-6 if out_dtype == torch.float32 else 5e-3)
+    # no delta at all
+    out3 = torch.empty(n, d, device=DEV, dtype=out_dtype)
+    ops.add_rmsnorm(x, None, w, eps, out3)
+    ref3 = w.double() * (x1.double() / torch.sqrt((x1.double() ** 2).mean(-1, keepdim=True) + eps))
+    close(out3, ref3, 2e-6 if out_dtype == torch.float32 else 5e-3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(dtype):
+    from odin_infer_b200.csrc import ops
+    T, I = 5, 203
+    gu = (3 * torch.randn(T, 2 * I, device=DEV)).to(dtype)
+    out = torch.empty(T, I, device=DEV, dtype=dtype)
+    ops.swiglu(gu, out)
+    g, u = gu[:, :I].double(), gu[:, I:].double()
+    close(out, g * torch.sigmoid(g) * u, 2e-6 if dtype == torch.float32 else 5e-3)
+
+
+@pytest.mark.parametrize("shape", [(1, 5, 3), (7, 130, 72), (65, 64, 16), (130, 301, 200), (3, 1000, 1032)])
+@pytest.mark.parametrize("combo", [(torch.float32,) * 3, (torch.bfloat16,) * 3,
+                                   (torch.bfloat16, torch.bfloat16, torch.float32),
+                                   (torch.bfloat16, torch.float32, torch.bfloat16)])
+def test_gemm_plain_ladder(shape, combo):
+    """Structured inputs first (all ones gives K; an identity copies; rows and columns
+    that differ), then random ones, as the reference's matrix-product harness does
+    (gemm_harness/gemm_test.odin:1063-1072)."""
+    from odin_infer_b200.csrc import ops
+    M, N, K = shape
+    ta, tw, tc = combo
+
+    def run(a, w):
+        out = torch.empty(M, N, device=DEV, dtype=tc)
+        ops.gemm_plain(a.to(ta), w.to(tw), out)
+        return out
+    exact = 1e-7 if tc == torch.float32 else 4e-3
+    close(run(torch.ones(M, K, device=DEV), torch.ones(N, K, device=DEV)), torch.full((M, N), float(K)), exact)
+    eye = torch.eye(N, K, device=DEV)
+    a = torch.randn(M, K, device=DEV).to(ta).float()
+    close(run(a, eye), (a.double() @ eye.double().t()), exact)
+    rows = torch.arange(M, device=DEV, dtype=torch.float32)[:, None].expand(M, K) % 7
+    cols = (torch.arange(N, device=DEV, dtype=torch.float32)[:, None].expand(N, K) % 5) * 0.25
+    close(run(rows, cols), rows.double() @ cols.double().t(), exact)
+    a = torch.randn(M, K, device=DEV).to(ta)
+    w = torch.randn(N, K, device=DEV).to(tw)
+    # 32-bit: rounding of a K-term sum grows like sqrt(K) * 2^-24
+    close(run(a, w), a.double() @ w.double().t(), (1e-7 * math.sqrt(K) if tc == torch.float32 else 5e-3))
+
+
+def paged_cache(n_seqs, lengths, n_kv, hd, dtype, shuffle=True):
+    """A cache whose pages are handed out in a scrambled order."""
+    PAGE = 64
+    pages_per = [(n + PAGE - 1) // PAGE for n in lengths]
+    total = sum(pages_per) + 3
+    order = torch.randperm(total).tolist() if shuffle else list(range(total))
+    bt = torch.full((n_seqs, max(pages_per)), -1, dtype=torch.int32)
+    it = iter(order)
+    for s, n in enumerate(pages_per):
+        for p in range(n):
+            bt[s, p] = next(it)
+    k = torch.full((total, n_kv, PAGE, hd), float("nan"), device=DEV, dtype=dtype)
+    v = torch.full((total, n_kv, PAGE, hd), float("nan"), device=DEV, dtype=dtype)
+    return k, v, bt.to(DEV)
+
+
+def rope_ref(v, pos, rot, theta):
+    half = rot // 2
+    i = np.arange(half, dtype=np.float32)
+    freq = (np.float32(1) / np.power(np.float32(theta), i / np.float32(half))).astype(np.float32)
+    ang = torch.from_numpy((np.asarray(pos, dtype=np.float32)[:, None] * freq[None, :]).astype(np.float32).astype(np.float64))
+    c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    x, y = v[..., :half], v[..., half:rot]
+    return torch.cat([x * c - y * s, x * s + y * c, v[..., rot:]], dim=-1)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("geom", [(4, 2, 16, 16), (6, 2, 32, 32), (5, 1, 48, 48), (8, 8, 128, 128), (3, 3, 160, 64),
+                                  (2, 1, 64, 0)])
+def test_head_prep_and_attention_plain(geom, dtype):
+    """q/k norm + rotation + cache write, then attention over the scrambled pages, for
+    sequences that continue from a non-zero position, against a direct computation."""
+    from odin_infer_b200.csrc import ops
+    from odin_infer_b200.parts.position import RotaryEncoding
+    from odin_infer_b200.engine.runtime import Runtime
+    n_q, n_kv, hd, rot = geom
+    theta, eps = 1e4, 1e-5
+    lengths = [70, 1, 130]
+    torch.manual_seed(n_q * 100 + hd)
+    k_cache, v_cache, bt = paged_cache(3, lengths, n_kv, hd, dtype)
+    rt = Runtime(DEV, dtype)
+    pe = RotaryEncoding(max(rot, 2), theta)
+    pe.prepare(rt, 256)
+    qn = (1 + 0.1 * torch.randn(hd, device=DEV))
+    kn = (1 + 0.1 * torch.randn(hd, device=DEV))
+    width = (n_q + 2 * n_kv) * hd
+    all_q, all_k, all_v = {}, {}, {}
+    # two steps: first all but the last 3 tokens of each sequence (at least 1), then the rest
+    cuts = [max(1, n - 3) for n in lengths]
+    full = [torch.randn(n, width, device=DEV).to(dtype) for n in lengths]
+    outs = [[] for _ in lengths]
+    for part in range(2):
+        seqs = [(s, (0, cuts[s]) if part == 0 else (cuts[s], lengths[s])) for s in range(3)]
+        seqs = [(s, r) for s, r in seqs if r[1] > r[0]]
+        qkv = torch.cat([full[s][a:b] for s, (a, b) in seqs]).clone()
+        tok_pos = torch.tensor([p for s, (a, b) in seqs for p in range(a, b)], dtype=torch.int32, device=DEV)
+        tok_seq = torch.tensor([s for s, (a, b) in seqs for _ in range(a, b)], dtype=torch.int32, device=DEV)
+        ops.head_prep(qkv, n_q, n_kv, hd, qn, kn, eps, pe.cos, pe.sin, rot, tok_pos, tok_seq, bt, k_cache, v_cache)
+        q = qkv[:, :n_q * hd]
+        out = torch.empty(qkv.shape[0], n_q * hd, device=DEV, dtype=dtype)
+        ops.attention_plain(q, out, n_q, n_kv, hd, k_cache, v_cache, tok_pos, tok_seq, bt, 0)
+        r = 0
+        for s, (a, b) in seqs:
+            outs[s].append(out[r:r + b - a])
+            r += b - a
+    for s, n in enumerate(lengths):
+        x = full[s].double().cpu().view(n, n_q + 2 * n_kv, hd)
+        def norm(v, w):
+            return w.double().cpu() * (v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps))
+        pos = list(range(n))
+        qr = rope_ref(norm(x[:, :n_q], qn), pos, rot, theta) if rot else norm(x[:, :n_q], qn)
+        kr = rope_ref(norm(x[:, n_q:n_q + n_kv], kn), pos, rot, theta) if rot else norm(x[:, n_q:n_q + n_kv], kn)
+        if dtype == torch.bfloat16:  # what the kernel stores
+            qr, kr = qr.bfloat16().double(), kr.bfloat16().double()
+        vr = x[:, n_q + n_kv:]
+        ref = torch.zeros(n, n_q, hd, dtype=torch.float64)
+        mask = torch.tril(torch.ones(n, n, dtype=torch.bool))
+        for h in range(n_q):
+            kh = h // (n_q // n_kv)
+            sc = (qr[:, h] @ kr[:, kh].t()) / math.sqrt(hd)
+            sc = sc.masked_fill(~mask, float("-inf"))
+            ref[:, h] = torch.softmax(sc, -1) @ vr[:, kh]
+        got = torch.cat(outs[s]).double().cpu().view(n, n_q, hd)
+        close(got, ref, 3e-6 if dtype == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_a_far_key_and_respects_window(dtype):
+    """One key far back among hundreds is made to stand out (its score dominates), so a
+    kernel that skips or misplaces a page, or reads beyond the window, shows."""
+    from odin_infer_b200.csrc import ops
+    n_q, n_kv, hd, n = 4, 2, 32, 300
+    torch.manual_seed(3)
+    k_cache, v_cache, bt = paged_cache(1, [n], n_kv, hd, dtype)
+    keys = 0.1 * torch.randn(n, n_kv, hd, device=DEV)
+    vals = torch.randn(n, n_kv, hd, device=DEV)
+    far = 67  # second page
+    q = 0.1 * torch.randn(1, n_q, hd, device=DEV)
+    keys[far] = 0.0
+    keys[far, :, 0] = 40.0
+    q[0, :, 0] = 40.0 / math.sqrt(hd) * 2
+    for p in range(n):
+        page = int(bt[0, p // 64])
+        k_cache[page, :, p % 64] = keys[p].to(dtype)
+        v_cache[page, :, p % 64] = vals[p].to(dtype)
+    tok_pos = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+    tok_seq = torch.zeros(1, dtype=torch.int32, device=DEV)
+    qf = q.reshape(1, n_q * hd).to(dtype)
+    out = torch.empty(1, n_q * hd, device=DEV, dtype=dtype)
+    ops.attention_plain(qf, out, n_q, n_kv, hd, k_cache, v_cache, tok_pos, tok_seq, bt, 0)
+    got = out.float().view(n_q, hd)
+    for h in range(n_q):
+        close(got[h], vals[far, h // 2].to(dtype).float(), 2e-2)
+    # with a window that ends after the far key, it must not be seen
+    ops.attention_plain(qf, out, n_q, n_kv, hd, k_cache, v_cache, tok_pos, tok_seq, bt, n - 1 - far)
+    got_w = out.float().view(n_q, hd)
+    assert (got_w - vals[far, 0].to(dtype).float()).abs().max() > 0.1
+    # and with a window that just includes it, it is seen again
+    ops.attention_plain(qf, out, n_q, n_kv, hd, k_cache, v_cache, tok_pos, tok_seq, bt, n - far)
+    close(out.float().view(n_q, hd)[0], vals[far, 0].to(dtype).float(), 2e-2)
+
+
+def test_argmax_and_sampling():
+    from odin_infer_b200.csrc import ops
+    from tests.plain import qwen3_plain as P
+    B, V = 5, 1003
+    torch.manual_seed(0)
+    logits = torch.randn(B, V, device=DEV) * 3
+    logits[1, 17] = logits[1, 900] = 50.0  # a tie: the first wins
+    out = torch.empty(B, dtype=torch.int32, device=DEV)
+    ops.argmax(logits, out)
+    assert out.tolist() == [P.argmax_first(logits[b].tolist()) for b in range(B)]
+    assert out[1].item() == 17
+    keep = logits.clone()
+    # temperature draw: the token must be the one the plain CDF walk finds (or its neighbour
+    # when the coin falls within rounding of a boundary)
+    coins = torch.tensor([0.0, 0.25, 0.5, 0.75, 0.999], device=DEV)
+    ops.sample(logits, 0.8, 1.0, coins, out)
+    assert torch.equal(logits, keep), "sampling must leave the logits as they are"
+    for b in range(B):
+        p = P.temperature_probs(logits[b].double().cpu(), 0.8)
+        cdf = torch.cumsum(p, 0)
+        i = out[b].item()
+        lo = cdf[i - 1].item() if i > 0 else 0.0
+        assert lo - 1e-5 <= coins[b].item() < cdf[i].item() + 1e-5, (b, i)
+    # top-p: the drawn token is always in the kept set; with a tiny top_p it is the argmax
+    # (no tied logits here: which of two equal tokens a sort keeps is not defined)
+    logits[1, 900] = 49.0
+    for tp in (0.3, 0.9):
+        for c in (0.0, 0.37, 0.99):
+            ops.sample(logits, 1.0, tp, torch.full((B,), c, device=DEV), out)
+            for b in range(B):
+                p = P.temperature_probs(logits[b].double().cpu(), 1.0)
+                assert out[b].item() in P.top_p_keep(p, tp)
+    ops.sample(logits, 1.0, 1e-4, torch.full((B,), 0.9, device=DEV), out)
+    assert out.tolist() == logits.argmax(-1).tolist()
+    # the draws follow the distribution
+    small = torch.tensor([[0.0, 1.0, 2.0, -1.0]], device=DEV).repeat(4000, 1)
+    cs = torch.rand(4000, device=DEV)
+    o = torch.empty(4000, dtype=torch.int32, device=DEV)
+    ops.sample(small, 1.0, 1.0, cs, o)
+    freq = torch.bincount(o.long(), minlength=4).double() / 4000
+    assert (freq.cpu() - torch.softmax(small[0].double().cpu(), 0)).abs().max() < 0.03
+
+
+def test_repetition_penalty():
+    from odin_infer_b200.csrc import ops
+    from tests.plain import qwen3_plain as P
+    logits = torch.tensor([[1.0, -1.0, 3.0, 0.5], [2.0, 2.0, -2.0, 0.0]], device=DEV)
+    recent = torch.tensor([[0, 1, 1, -1], [2, 2, 2, 3]], dtype=torch.int32, device=DEV)
+    ref = torch.stack([P.repetition_penalty(logits[b].cpu(), [t for t in recent[b].tolist() if t >= 0], 2.0) for b in range(2)])
+    ops.repetition_penalty(logits, recent, 2.0)
+    assert torch.equal(logits.cpu(), ref)
