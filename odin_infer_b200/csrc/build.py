@@ -31,6 +31,7 @@ GROUPS = {
     "head_prep": ["head_prep.cu"],
     "attention_plain": ["attention_plain.cu"],
     "sampling": ["sampling.cu"],
+    "gemm_tc": ["gemm_tc.cu"],
 }
 HEADERS = ["common.cuh"]
 

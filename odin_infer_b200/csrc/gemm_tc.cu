@@ -1,0 +1,429 @@
+// C[M,N] = A[M,K] * W[N,K]^T in bfloat16 on the 5th-generation tensor cores:
+// tcgen05.mma with the accumulator in tensor memory, operands brought to shared
+// memory by TMA in the 128-byte swizzle, a ring of stages, and a persistent CTA per
+// SM that walks over output tiles with two accumulators, so the epilogue of one
+// tile overlaps the products of the next.
+//
+// Roles (192 threads): warp 0 issues TMA loads, warp 1 allocates tensor memory and
+// issues the MMAs (one thread), warps 2..5 read the accumulator back and store.
+//
+// The product is computed as D = X * Y^T with X on the 128-row side of the MMA and
+// Y on its N side.  Two modes map the matrices to X and Y:
+//   mode 0 (many tokens):  X = A (tokens),  Y = W;  D[i][j] -> C[i][j]
+//   mode 1 (few tokens):   X = W,           Y = A;  D[i][j] -> C[j][i]
+// Mode 1 puts the weight rows on the wide side, so decoding a handful of tokens
+// still fills the MMA and streams each weight exactly once.
+//
+// Split-K: the K range can be cut into `n_split` parts, each written as a 32-bit
+// partial sum to its own slice of the output ([n_split][M][N]); the consumer adds
+// them in a fixed order.  Which part a CTA takes never depends on M, so a token's
+// result does not depend on what else is in the batch.
+//
+// In the reference this is the weight-times-activation product of every layer
+// (infer/matmul.odin:77-109, one row-dot per thread on the CPU; gemv kernels in
+// infer/metal.odin:76-109 on the GPU).
+#include <mutex>
+#include <unordered_map>
+
+#include "tc_common.cuh"
+
+namespace {
+
+constexpr int BM = 128;  // rows of X per tile (MMA M)
+constexpr int BK = 64;   // K elements per stage: 128 bytes, one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int ACC_BUFS = 2;
+
+struct GemmParams {
+    void* out;             // C (or the partial-sum slices)
+    long long ldc;         // leading dimension of C in elements
+    long long split_stride;  // elements between partial-sum slices
+    int rows_x, rows_y;    // rows of X and Y
+    int K;
+    int tiles_x, tiles_y;
+    int n_split, kb_per_split, kb_total;
+    int* error;            // set when a wait runs out
+};
+
+template <int BN>
+struct Cfg {
+    static constexpr int STAGE_X = BM * BK * 2;
+    static constexpr int STAGE_Y = BN * BK * 2;
+    static constexpr int STAGE = STAGE_X + STAGE_Y;
+    static constexpr int STAGES = (196608 / STAGE) > 10 ? 10 : (196608 / STAGE);
+    static constexpr int TMEM_COLS = (ACC_BUFS * BN) < 32 ? 32 : (ACC_BUFS * BN);
+    static constexpr int SMEM = STAGES * STAGE + 1024 /*alignment*/ + 256 /*barriers*/;
+};
+
+template <typename TO>
+__device__ __forceinline__ void store_vec(TO* dst, const uint32_t* r, int n);
+
+// n floats (bit patterns in r) to consecutive elements, vectorised when aligned
+template <>
+__device__ __forceinline__ void store_vec<float>(float* dst, const uint32_t* r, int n) {
+    if (n == 32 && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            reinterpret_cast<uint4*>(dst)[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+    } else {
+        for (int i = 0; i < n; ++i) dst[i] = __uint_as_float(r[i]);
+    }
+}
+
+template <>
+__device__ __forceinline__ void store_vec<bf16>(bf16* dst, const uint32_t* r, int n) {
+    if (n == 32 && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t p[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[8 * i + 2 * j]),
+                                                         __uint_as_float(r[8 * i + 2 * j + 1]));
+                p[j] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            reinterpret_cast<uint4*>(dst)[i] = make_uint4(p[0], p[1], p[2], p[3]);
+        }
+    } else {
+        for (int i = 0; i < n; ++i) dst[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
+    }
+}
+
+template <int BN, int MODE, typename TO>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
+               const GemmParams p) {
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE);
+    uint64_t* full = bars;                        // [STAGES] TMA landed
+    uint64_t* empty = bars + C::STAGES;           // [STAGES] MMAs that read the stage are done
+    uint64_t* acc_full = bars + 2 * C::STAGES;    // [ACC_BUFS] accumulator complete
+    uint64_t* acc_empty = acc_full + ACC_BUFS;    // [ACC_BUFS] accumulator read back
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_BUFS);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) {
+            tc::mbar_init(&full[s], 1);
+            tc::mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < ACC_BUFS; ++a) {
+            tc::mbar_init(&acc_full[a], 1);
+            tc::mbar_init(&acc_empty[a], 4);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        tc::fence_barrier_init();
+        tc::prefetch_tensormap(&map_x);
+        tc::prefetch_tensormap(&map_y);
+    }
+    if (warp == 1) tc::tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const long long n_items = (long long)p.tiles_x * p.tiles_y * p.n_split;
+
+    if (warp == 0) {
+        // ------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (long long w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
+                const int s = (int)(w % p.n_split);
+                const long long rest = w / p.n_split;
+                const int tx = (int)(rest % p.tiles_x), ty = (int)(rest / p.tiles_x);
+                const int kb0 = s * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!tc::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+                    uint8_t* sx = smem + stage * C::STAGE;
+                    uint8_t* sy = sx + C::STAGE_X;
+                    tc::mbar_expect_tx(&full[stage], C::STAGE);
+                    tc::tma_load_2d(sx, &map_x, kb * BK, tx * BM, &full[stage]);
+                    tc::tma_load_2d(sy, &map_y, kb * BK, ty * BN, &full[stage]);
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                // aborted: let the copies already in flight land before the CTA's memory is released
+                for (int s2 = 0; s2 < C::STAGES; ++s2)
+                    for (uint32_t i = 0; i < 4096; ++i)
+                        if (tc::mbar_try_wait(&full[s2], 0) || tc::mbar_try_wait(&full[s2], 1)) break;
+            }
+        }
+    } else if (warp == 1) {
+        // --------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = tc::make_idesc_bf16(BM, BN);
+            uint32_t stage = 0, phase = 0;
+            uint32_t local = 0;
+            bool ok = true;
+            for (long long w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++local) {
+                const int s = (int)(w % p.n_split);
+                const int kb0 = s * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                const uint32_t acc = local % ACC_BUFS, acc_phase = (local / ACC_BUFS) & 1;
+                if (!tc::mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+                tc::fence_after_sync();
+                const uint32_t tmem_d = tmem_base + acc * BN;
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!tc::mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+                    tc::fence_after_sync();
+                    const uint32_t ax = tc::smem_u32(smem + stage * C::STAGE);
+                    const uint64_t dx = tc::make_smem_desc_sw128(ax);
+                    const uint64_t dy = tc::make_smem_desc_sw128(ax + C::STAGE_X);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // +32 bytes per K step inside the 128-byte swizzle row: +2 in 16-byte units
+                        tc::umma_bf16(tmem_d, dx + 2 * k, dy + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                    }
+                    tc::umma_commit(&empty[stage]);
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) tc::umma_commit(&acc_full[acc]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue
+        const int quarter = warp & 3;  // the TMEM lanes this warp may read: [32*quarter, +32)
+        uint32_t local = 0;
+        bool ok = true;
+        for (long long w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++local) {
+            const int s = (int)(w % p.n_split);
+            const long long rest = w / p.n_split;
+            const int tx = (int)(rest % p.tiles_x), ty = (int)(rest / p.tiles_x);
+            const uint32_t acc = local % ACC_BUFS, acc_phase = (local / ACC_BUFS) & 1;
+            if (!tc::mbar_wait(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+            tc::fence_after_sync();
+            const int i = tx * BM + quarter * 32 + lane;  // row of X
+            TO* out = reinterpret_cast<TO*>(p.out) + (size_t)s * p.split_stride;
+            constexpr int CH = (BN >= 32) ? 32 : 16;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += CH) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + c0;
+                if (CH == 32) {
+                    tc::tmem_ld32(taddr, r);
+                } else {
+                    uint32_t r16[16];
+                    tc::tmem_ld16(taddr, r16);
+#pragma unroll
+                    for (int q = 0; q < 16; ++q) r[q] = r16[q];
+                }
+                tc::tmem_ld_wait();
+                const int j0 = ty * BN + c0;  // first row of Y in this chunk
+                if (MODE == 0) {
+                    // C[i][j0 + c]: each thread writes a run of its own row
+                    if (i < p.rows_x && j0 < p.rows_y) {
+                        const int n = min(CH, p.rows_y - j0);
+                        store_vec<TO>(out + (size_t)i * p.ldc + j0, r, n);
+                    }
+                } else {
+                    // C[j0 + c][i]: the warp writes 32 consecutive elements of one row
+                    if (i < p.rows_x) {
+#pragma unroll
+                        for (int c = 0; c < CH; ++c) {
+                            if (j0 + c < p.rows_y)
+                                out[(size_t)(j0 + c) * p.ldc + i] = from_f32<TO>(__uint_as_float(r[c]));
+                        }
+                    }
+                }
+            }
+            tc::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&acc_empty[acc]);
+        }
+    }
+
+    tc::fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag && p.error != nullptr) atomicExch(p.error, 1);
+    if (warp == 1) {
+        tc::fence_after_sync();
+        tc::tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(f);
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr;
+    long long rows, K, ld;
+    int box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && K == o.K && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = std::hash<const void*>()(k.ptr);
+        h = h * 1000003u ^ std::hash<long long>()(k.rows);
+        h = h * 1000003u ^ std::hash<long long>()(k.K);
+        h = h * 1000003u ^ std::hash<long long>()(k.ld);
+        return h * 1000003u ^ (size_t)k.box_rows;
+    }
+};
+
+// A row-major [rows, K] bfloat16 matrix with row stride ld, read in boxes of
+// 64 (K) x box_rows, 128-byte swizzle, zeros beyond the edges.
+int make_map(CUtensorMap* out, const void* ptr, long long rows, long long K, long long ld, int box_rows) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    MapKey key{ptr, rows, K, ld, box_rows};
+    {
+        std::lock_guard<std::mutex> g(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) { *out = it->second; return 0; }
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return ODIN_ERR_UNSUPPORTED;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return ODIN_ERR_BAD_ARG;
+    std::lock_guard<std::mutex> g(mu);
+    if (cache.size() > 65536) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+
+int* error_flag() {
+    static int* flag = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        if (cudaMalloc(&flag, sizeof(int)) == cudaSuccess) cudaMemset(flag, 0, sizeof(int));
+        else flag = nullptr;
+    });
+    return flag;
+}
+
+int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <int BN, int MODE, typename TO>
+int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, cudaStream_t s) {
+    using C = Cfg<BN>;
+    auto kern = gemm_tc_kernel<BN, MODE, TO>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const long long items = (long long)p.tiles_x * p.tiles_y * p.n_split;
+    const int grid = (int)(items < sm_count() ? items : sm_count());
+    kern<<<grid, 192, C::SMEM, s>>>(mx, my, p);
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}
+
+template <int MODE, typename TO>
+int dispatch_bn(int bn, const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, cudaStream_t s) {
+    switch (bn) {
+        case 16: return launch<16, MODE, TO>(mx, my, p, s);
+        case 32: return launch<32, MODE, TO>(mx, my, p, s);
+        case 64: return launch<64, MODE, TO>(mx, my, p, s);
+        case 128: return launch<128, MODE, TO>(mx, my, p, s);
+        case 256: return launch<256, MODE, TO>(mx, my, p, s);
+        default: return ODIN_ERR_UNSUPPORTED;
+    }
+}
+
+}  // namespace
+
+// A: [M, K] bfloat16, row stride lda; W: [N, K] bfloat16, row stride ldw; C: [M, N] of
+// c_dtype, row stride ldc, or with n_split > 1: float32 partial sums [n_split][M][ldc...]
+// split_stride elements apart.  mode 0: tokens on the 128-row side; mode 1: weights on
+// it (for M <= bn).  bn: the tile's N side: 16..256.  Strides and K must be multiples
+// of 8 elements and the pointers 16-byte aligned (TMA), else ODIN_ERR_UNSUPPORTED.
+extern "C" int odin_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, long long lda,
+                            long long ldw, long long ldc, int mode, int bn, int n_split, long long split_stride,
+                            void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || n_split < 1) return ODIN_ERR_BAD_ARG;
+    if ((lda % 8) || (ldw % 8) || (K % 8) || (((uintptr_t)A) & 15) || (((uintptr_t)W) & 15)) return ODIN_ERR_UNSUPPORTED;
+    if (n_split > 1 && c_dtype != ODIN_F32) return ODIN_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    GemmParams p;
+    p.out = C;
+    p.ldc = ldc;
+    p.split_stride = split_stride;
+    p.K = K;
+    p.kb_total = (K + BK - 1) / BK;
+    if (n_split > p.kb_total) n_split = p.kb_total;
+    p.kb_per_split = (p.kb_total + n_split - 1) / n_split;
+    if ((p.kb_total + p.kb_per_split - 1) / p.kb_per_split != n_split) return ODIN_ERR_BAD_ARG;  // an empty part
+    p.n_split = n_split;
+    p.error = error_flag();
+    CUtensorMap mx, my;
+    int rc;
+    if (mode == 0) {
+        p.rows_x = M; p.rows_y = N;
+        if ((rc = make_map(&mx, A, M, K, lda, BM))) return rc;
+        if ((rc = make_map(&my, W, N, K, ldw, bn))) return rc;
+    } else if (mode == 1) {
+        p.rows_x = N; p.rows_y = M;
+        if ((rc = make_map(&mx, W, N, K, ldw, BM))) return rc;
+        if ((rc = make_map(&my, A, M, K, lda, bn))) return rc;
+    } else {
+        return ODIN_ERR_BAD_ARG;
+    }
+    p.tiles_x = (p.rows_x + BM - 1) / BM;
+    p.tiles_y = (p.rows_y + bn - 1) / bn;
+    if (c_dtype == ODIN_F32)
+        return mode == 0 ? dispatch_bn<0, float>(bn, mx, my, p, s) : dispatch_bn<1, float>(bn, mx, my, p, s);
+    if (c_dtype == ODIN_BF16)
+        return mode == 0 ? dispatch_bn<0, bf16>(bn, mx, my, p, s) : dispatch_bn<1, bf16>(bn, mx, my, p, s);
+    return ODIN_ERR_UNSUPPORTED;
+}
+
+// The number of K parts that odin_gemm_tc will really use for (K, n_split).
+extern "C" int odin_gemm_tc_splits(int K, int n_split) {
+    const int kb_total = (K + BK - 1) / BK;
+    if (n_split > kb_total) n_split = kb_total;
+    if (n_split < 1) n_split = 1;
+    const int per = (kb_total + n_split - 1) / n_split;
+    return (kb_total + per - 1) / per;
+}
+
+// Reads and clears the flag that a kernel sets when one of its bounded waits ran
+// out (synchronises the device).  0: all well.
+extern "C" int odin_gemm_tc_error() {
+    int* f = error_flag();
+    if (f == nullptr) return 0;
+    int v = 0;
+    if (cudaMemcpy(&v, f, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (v) cudaMemset(f, 0, sizeof(int));
+    return v;
+}

@@ -125,6 +125,53 @@ def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         c_longlong(w.stride(0)), c_longlong(out.stride(0)), _stream()), "gemm_plain")
 
 
+def gemm_tc_splits(K: int, n_split: int) -> int:
+    """How many K parts `gemm_tc` really uses when asked for n_split."""
+    f = build.load("gemm_tc").odin_gemm_tc_splits
+    f.restype = c_int
+    return int(f(c_int(K), c_int(n_split)))
+
+
+def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Shapes and strides that the tensor-core kernel takes (TMA wants 16-byte rows)."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.stride(1) == 1 and w.stride(1) == 1
+            and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, bn: int, n_split: int = 1) -> None:
+    """out = a[M, K] @ w[N, K]^T on the tcgen05 tensor cores (bfloat16 in, 32-bit accumulation).
+
+    mode 0: tokens on the 128-row side of the MMA, tiles of bn weight rows.
+    mode 1: weight rows on the 128-row side, tiles of bn tokens (M <= bn is usual).
+    n_split > 1: out is float32 [n_split, M, N]; slice s holds the partial sum of K part s.
+    """
+    M, K = a.shape
+    N = w.shape[0]
+    if not gemm_tc_supported(a, w):
+        raise KernelError("gemm_tc: operands must be bfloat16 with 16-byte aligned rows (K and strides multiples of 8)")
+    assert w.shape[1] == K and out.stride(-1) == 1
+    if n_split > 1:
+        assert out.dtype == torch.float32 and out.dim() == 3 and tuple(out.shape[1:]) == (M, N)
+        assert out.shape[0] == gemm_tc_splits(K, n_split), "allocate gemm_tc_splits(K, n_split) slices"
+        ldc, stride = out.stride(1), out.stride(0)
+    else:
+        assert tuple(out.shape) == (M, N)
+        ldc, stride = out.stride(0), 0
+    _check(_fn("gemm_tc", "odin_gemm_tc")(
+        _ptr(a), _ptr(w), _ptr(out), c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K),
+        c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(ldc), c_int(mode), c_int(bn), c_int(n_split),
+        c_longlong(stride), _stream()), "gemm_tc")
+
+
+def gemm_tc_check() -> None:
+    """Raise if a tensor-core kernel gave up a bounded wait since the last check (synchronises)."""
+    f = build.load("gemm_tc").odin_gemm_tc_error
+    f.restype = c_int
+    if f() != 0:
+        raise KernelError("gemm_tc: a device-side wait ran out (pipeline stalled); results are invalid")
+
+
 def head_prep(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, q_norm: torch.Tensor | None,
               k_norm: torch.Tensor | None, eps: float, cos: torch.Tensor, sin: torch.Tensor, rotary_dim: int,
               tok_pos: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,

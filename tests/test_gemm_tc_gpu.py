@@ -1,0 +1,101 @@
+"""The tcgen05 matrix product alone against a float64 reference: structured inputs
+first (all ones gives K, an identity copies, rows and columns that differ), then
+random ones; both operand modes, every tile width, ragged edges, K tails, split-K."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def close(got, ref, rtol, what=""):
+    got, ref = got.double().cpu(), ref.double().cpu()
+    err = (got - ref).abs().max().item() / max(ref.abs().max().item(), 1e-30)
+    assert err <= rtol, f"{what}: relative error {err:.3e} > {rtol:.1e}"
+
+
+def run(a, w, mode, bn, out_dtype, n_split=1):
+    from odin_infer_b200.csrc import ops
+    M, N = a.shape[0], w.shape[0]
+    if n_split > 1:
+        s = ops.gemm_tc_splits(a.shape[1], n_split)
+        out = torch.full((s, M, N), float("nan"), device=DEV, dtype=torch.float32)
+        ops.gemm_tc(a, w, out, mode, bn, n_split)
+        ops.gemm_tc_check()
+        assert not torch.isnan(out).any()
+        return out.sum(0)
+    out = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
+    ops.gemm_tc(a, w, out, mode, bn)
+    ops.gemm_tc_check()
+    assert not torch.isnan(out.float()).any()
+    return out
+
+
+CASES = [
+    # (M, N, K, mode, bn)
+    (128, 256, 64, 0, 256), (128, 128, 128, 0, 128), (2048, 512, 256, 0, 256), (300, 200, 96, 0, 64),
+    (129, 1000, 72, 0, 256), (130, 40, 1032, 0, 64), (1000, 384, 4096, 0, 128),
+    (1, 128, 64, 1, 16), (1, 384, 96, 1, 16), (8, 6144, 4096, 1, 16), (16, 300, 72, 1, 16), (17, 256, 128, 1, 32),
+    (64, 1000, 1032, 1, 64), (100, 512, 256, 1, 128), (33, 12288, 512, 1, 64),
+]
+
+
+@pytest.mark.parametrize("case", CASES)
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_ladder(case, out_dtype):
+    M, N, K, mode, bn = case
+    exact = 1e-6 if out_dtype == torch.float32 else 4e-3
+    ones_a = torch.ones(M, K, device=DEV, dtype=torch.bfloat16)
+    ones_w = torch.ones(N, K, device=DEV, dtype=torch.bfloat16)
+    close(run(ones_a, ones_w, mode, bn, out_dtype), torch.full((M, N), float(K)), exact, "ones")
+    eye = torch.eye(N, K, device=DEV, dtype=torch.bfloat16)
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    close(run(a, eye, mode, bn, out_dtype), a.double() @ eye.double().t(), exact, "identity")
+    rows = (torch.arange(M, device=DEV)[:, None].expand(M, K) % 7).bfloat16().contiguous()
+    cols = ((torch.arange(N, device=DEV)[:, None].expand(N, K) % 5) * 0.25).bfloat16().contiguous()
+    close(run(rows, cols, mode, bn, out_dtype), rows.double() @ cols.double().t(), exact, "rows/columns")
+    # every (row, k) and (column, k) distinct: a wrong swizzle or K step shows as a wrong sum
+    ka = ((torch.arange(M, device=DEV)[:, None] * 3 + torch.arange(K, device=DEV)[None, :] * 5) % 11 - 5).bfloat16()
+    kw = ((torch.arange(N, device=DEV)[:, None] * 7 + torch.arange(K, device=DEV)[None, :] * 2) % 13 - 6).bfloat16()
+    close(run(ka, kw, mode, bn, out_dtype), ka.double() @ kw.double().t(), exact, "k-distinct")
+    w = torch.randn(N, K, device=DEV).bfloat16()
+    close(run(a, w, mode, bn, out_dtype), a.double() @ w.double().t(),
+          (2e-7 * math.sqrt(K) if out_dtype == torch.float32 else 5e-3), "random")
+
+
+@pytest.mark.parametrize("case", [(8, 4096, 12288, 1, 16, 6), (64, 512, 1032, 1, 64, 4), (3, 256, 640, 1, 16, 4),
+                                  (200, 300, 4096, 0, 128, 3), (5, 128, 96, 1, 16, 7)])
+def test_split_k(case):
+    M, N, K, mode, bn, n_split = case
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    w = torch.randn(N, K, device=DEV).bfloat16()
+    close(run(a, w, mode, bn, torch.float32, n_split), a.double() @ w.double().t(), 2e-7 * math.sqrt(K), "split")
+
+
+def test_strided_views_and_batch_invariance():
+    """A row's result must not depend on the other rows (same mode, tile and split)."""
+    from odin_infer_b200.csrc import ops
+    K, N = 1024, 640
+    big = torch.randn(40, 2 * K, device=DEV).bfloat16()
+    a = big[:, :K]                       # row stride 2K
+    w = torch.randn(N, K, device=DEV).bfloat16()
+    full = run(a, w, 1, 64, torch.float32)
+    close(full, a.double() @ w.double().t(), 2e-7 * math.sqrt(K))
+    one = run(a[7:8], w, 1, 64, torch.float32)
+    assert torch.equal(one[0], full[7])
+    few = run(a[5:17], w, 1, 64, torch.float32)
+    assert torch.equal(few, full[5:17])
+    sp_full = run(a, w, 1, 64, torch.float32, 4)
+    sp_one = run(a[7:8], w, 1, 64, torch.float32, 4)
+    assert torch.equal(sp_one[0], sp_full[7])
+
+
+def test_refuses_what_it_cannot_do():
+    from odin_infer_b200.csrc import ops
+    a = torch.randn(4, 100, device=DEV).bfloat16()   # K not a multiple of 8
+    w = torch.randn(16, 100, device=DEV).bfloat16()
+    assert not ops.gemm_tc_supported(a, w)
+    with pytest.raises(ops.KernelError):
+        ops.gemm_tc(a, w, torch.empty(4, 16, device=DEV, dtype=torch.bfloat16), 1, 16)
