@@ -1,0 +1,275 @@
+// Attention of one new token per sequence over its paged bfloat16 cache, split
+// along the keys so that a small batch still occupies every SM.
+//
+// Grid: (key splits, kv heads x query-head groups, sequences).  A CTA takes one
+// sequence, one kv head, up to G of its query heads, and a contiguous range of the
+// sequence's pages; every key and value it loads serves all G query heads.  Inside
+// a warp a key's head_dim elements are spread over LPK lanes (16-byte loads, whole
+// rows coalesced), so one warp instruction covers 32/LPK keys.  Each lane group
+// keeps an "online softmax" of its own (running maximum, sum, weighted values);
+// groups, warps and finally splits are merged with the usual rescaling.  A second
+// kernel merges the splits and writes bfloat16.
+//
+// Arithmetic follows infer/forward.odin:88-115 (scores scaled by 1/sqrt(hd), softmax
+// with the maximum subtracted, weighted sum of values), all in 32-bit; the scale and
+// log2(e) are folded into q so that the exponentials are exp2.
+//
+// Scratch: partial results [sequence][query head][split] of head_dim + 2 floats, in
+// memory the caller provides.
+#include "common.cuh"
+
+namespace {
+
+constexpr int AD_WARPS = 4;
+constexpr float NEG_BIG = -1.0e30f;
+
+template <int HD>
+struct Geo {
+    static constexpr int EPL = (HD >= 64) ? 16 : 8;  // elements per lane
+    static constexpr int LPK = HD / EPL;             // lanes per key
+    static constexpr int KPI = 32 / LPK;             // keys per warp instruction
+    static_assert(LPK >= 1 && LPK <= 32 && (LPK & (LPK - 1)) == 0, "head_dim must give a power-of-two lane count");
+};
+
+template <int N>
+__device__ __forceinline__ void load_bf16(const bf16* p, float (&out)[N]) {
+#pragma unroll
+    for (int i = 0; i < N / 8; ++i) {
+        const uint4 v = reinterpret_cast<const uint4*>(p)[i];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            out[8 * i + 2 * j] = f.x;
+            out[8 * i + 2 * j + 1] = f.y;
+        }
+    }
+}
+
+template <int HD, int G>
+__global__ void __launch_bounds__(AD_WARPS * 32)
+attn_decode_kernel(const bf16* __restrict__ q, size_t q_stride, int Hq, int Hkv, const bf16* __restrict__ k_cache,
+                   const bf16* __restrict__ v_cache, int page_size, const int* __restrict__ tok_pos,
+                   const int* __restrict__ tok_seq, const int* __restrict__ block_table, int bt_stride, int window,
+                   float scale_log2, float* __restrict__ part_acc, float* __restrict__ part_ml, int n_split) {
+    using GE = Geo<HD>;
+    constexpr int EPL = GE::EPL, LPK = GE::LPK, KPI = GE::KPI;
+    const int split = blockIdx.x;
+    const int g_total = Hq / Hkv;
+    const int g_parts = (g_total + G - 1) / G;
+    const int kvh = blockIdx.y / g_parts;
+    const int h0 = kvh * g_total + (blockIdx.y % g_parts) * G;   // first query head of this CTA
+    const int n_h = min(G, kvh * g_total + g_total - h0);
+    const int t = blockIdx.z;                                    // token row = sequence of the step
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane % LPK, kg = lane / LPK;
+
+    const int seq = tok_seq[t];
+    float* my_acc = part_acc + (((size_t)t * Hq + h0) * n_split + split) * HD;
+    float* my_ml = part_ml + (((size_t)t * Hq + h0) * n_split + split) * 2;
+    const size_t head_step_acc = (size_t)n_split * HD, head_step_ml = (size_t)n_split * 2;
+
+    int t_lo = 0, t_hi = 0;  // keys [t_lo, t_hi) of this split
+    if (seq >= 0) {
+        const int pos = tok_pos[t];
+        int first = 0;
+        if (window > 0 && pos - window + 1 > 0) first = pos - window + 1;
+        const int p_first = first / page_size, p_last = pos / page_size;
+        const int n_pages = p_last - p_first + 1;
+        const int per = (n_pages + n_split - 1) / n_split;
+        const int pa = p_first + split * per, pb = min(p_last + 1, pa + per);
+        t_lo = max(first, pa * page_size);
+        t_hi = min(pos + 1, pb * page_size);
+    }
+
+    float qf[G][EPL], acc[G][EPL], m[G], l[G];
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+        m[h] = NEG_BIG;
+        l[h] = 0.f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) { acc[h][e] = 0.f; qf[h][e] = 0.f; }
+        if (h < n_h && seq >= 0) {
+            load_bf16<EPL>(q + (size_t)t * q_stride + (size_t)(h0 + h) * HD + sub * EPL, qf[h]);
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) qf[h][e] *= scale_log2;
+        }
+    }
+
+    const int* bt = block_table + (size_t)max(seq, 0) * bt_stride;
+    for (int base = t_lo + warp * KPI; base < t_hi; base += AD_WARPS * KPI) {
+        const int tk = base + kg;
+        const bool valid = tk < t_hi;
+        float kf[EPL], vf[EPL];
+        size_t row = 0;
+        bool have = false;
+        if (valid) {
+            const int page = bt[tk / page_size];
+            if (page >= 0) {
+                row = (((size_t)page * Hkv + kvh) * page_size + (tk % page_size)) * HD + sub * EPL;
+                have = true;
+            }
+        }
+        if (have) {
+            load_bf16<EPL>(k_cache + row, kf);
+            load_bf16<EPL>(v_cache + row, vf);
+        } else {
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) { kf[e] = 0.f; vf[e] = 0.f; }
+        }
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+            float s = 0.f;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) s = fmaf(qf[h][e], kf[e], s);
+#pragma unroll
+            for (int o = LPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            if (have) {
+                const float m_new = fmaxf(m[h], s);
+                const float corr = exp2f(m[h] - m_new);
+                const float p = exp2f(s - m_new);
+                l[h] = l[h] * corr + p;
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) acc[h][e] = fmaf(p, vf[e], acc[h][e] * corr);
+                m[h] = m_new;
+            }
+        }
+    }
+
+    // merge the lane groups of the warp (lanes that hold the same elements of different keys)
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+#pragma unroll
+        for (int o = LPK; o < 32; o <<= 1) {
+            const float m_o = __shfl_xor_sync(0xffffffffu, m[h], o);
+            const float l_o = __shfl_xor_sync(0xffffffffu, l[h], o);
+            const float m_new = fmaxf(m[h], m_o);
+            const float ca = exp2f(m[h] - m_new), cb = exp2f(m_o - m_new);
+            l[h] = l[h] * ca + l_o * cb;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) {
+                const float a_o = __shfl_xor_sync(0xffffffffu, acc[h][e], o);
+                acc[h][e] = acc[h][e] * ca + a_o * cb;
+            }
+            m[h] = m_new;
+        }
+    }
+
+    // merge the warps through shared memory
+    __shared__ float s_acc[AD_WARPS][G][HD];
+    __shared__ float s_ml[AD_WARPS][G][2];
+    if (kg == 0) {
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) s_acc[warp][h][sub * EPL + e] = acc[h][e];
+            if (sub == 0) { s_ml[warp][h][0] = m[h]; s_ml[warp][h][1] = l[h]; }
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * HD; idx += AD_WARPS * 32) {
+        const int h = idx / HD, d = idx % HD;
+        if (h >= n_h) continue;
+        float mm = s_ml[0][h][0];
+#pragma unroll
+        for (int w = 1; w < AD_WARPS; ++w) mm = fmaxf(mm, s_ml[w][h][0]);
+        float a = 0.f, ll = 0.f;
+#pragma unroll
+        for (int w = 0; w < AD_WARPS; ++w) {
+            const float c = exp2f(s_ml[w][h][0] - mm);
+            a += s_acc[w][h][d] * c;
+            ll += s_ml[w][h][1] * c;
+        }
+        my_acc[(size_t)h * head_step_acc + d] = a;
+        if (d == 0) {
+            my_ml[(size_t)h * head_step_ml] = mm;
+            my_ml[(size_t)h * head_step_ml + 1] = ll;
+        }
+    }
+}
+
+// out[t][h][:] = sum_s w_s acc_s / sum_s w_s l_s, w_s = 2^(m_s - max m)
+__global__ void attn_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml, int n_split,
+                                    int hd, bf16* __restrict__ out, size_t out_stride, int Hq,
+                                    const int* __restrict__ tok_seq) {
+    const int t = blockIdx.x / Hq, h = blockIdx.x % Hq;
+    if (tok_seq[t] < 0) return;
+    const float* ml = part_ml + ((size_t)t * Hq + h) * n_split * 2;
+    const float* ac = part_acc + ((size_t)t * Hq + h) * n_split * hd;
+    float mm = NEG_BIG;
+    for (int s = 0; s < n_split; ++s) mm = fmaxf(mm, ml[2 * s]);
+    float ll = 0.f;
+    for (int s = 0; s < n_split; ++s) ll += ml[2 * s + 1] * exp2f(ml[2 * s] - mm);
+    const float inv = ll > 0.f ? 1.0f / ll : 0.f;
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float a = 0.f;
+        for (int s = 0; s < n_split; ++s) a += ac[(size_t)s * hd + d] * exp2f(ml[2 * s] - mm);
+        out[(size_t)t * out_stride + (size_t)h * hd + d] = __float2bfloat16_rn(a * inv);
+    }
+}
+
+template <int HD>
+int launch_decode(const bf16* q, size_t q_stride, bf16* out, size_t out_stride, int B, int Hq, int Hkv,
+                  const bf16* k_cache, const bf16* v_cache, int page_size, const int* tok_pos, const int* tok_seq,
+                  const int* block_table, int bt_stride, int window, float* part_acc, float* part_ml, int n_split,
+                  cudaStream_t s) {
+    const int g = Hq / Hkv;
+    const float scale_log2 = 1.4426950408889634f / sqrtf((float)HD);
+#define GO(G)                                                                                                      \
+    do {                                                                                                           \
+        dim3 grid(n_split, Hkv * ((g + G - 1) / G), B);                                                            \
+        attn_decode_kernel<HD, G><<<grid, AD_WARPS * 32, 0, s>>>(q, q_stride, Hq, Hkv, k_cache, v_cache, page_size, \
+                                                                 tok_pos, tok_seq, block_table, bt_stride, window, \
+                                                                 scale_log2, part_acc, part_ml, n_split);          \
+    } while (0)
+    if (g == 1) GO(1);
+    else if (g == 2) GO(2);
+    else if (g == 3) GO(3);
+    else GO(4);
+#undef GO
+    ODIN_LAUNCH_CHECK();
+    attn_combine_kernel<<<B * Hq, HD < 128 ? 32 : 128, 0, s>>>(part_acc, part_ml, n_split, HD, out, out_stride, Hq,
+                                                              tok_seq);
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}
+
+}  // namespace
+
+// Floats of scratch that odin_attention_decode needs for B tokens, Hq query heads and n_split key splits.
+extern "C" long long odin_attention_decode_scratch(int B, int Hq, int hd, int n_split) {
+    return (long long)B * Hq * n_split * (hd + 2);
+}
+
+// Does the split kernel take this head size?  (Others go to the plain kernel.)
+extern "C" int odin_attention_decode_supported(int hd) {
+    return hd == 16 || hd == 32 || hd == 64 || hd == 128 || hd == 256;
+}
+
+// One query token per row of q ([B, Hq*hd] bfloat16, row stride q_row_stride); row t
+// belongs to sequence tok_seq[t] (row of the block table; negative: padding, skipped)
+// at position tok_pos[t].  scratch: odin_attention_decode_scratch(...) floats.
+extern "C" int odin_attention_decode(const void* q, long long q_row_stride, void* out, long long out_row_stride, int B,
+                                     int Hq, int Hkv, int hd, const void* k_cache, const void* v_cache, int page_size,
+                                     const int* tok_pos, const int* tok_seq, const int* block_table, int bt_stride,
+                                     int window, float* scratch, int n_split, void* stream) {
+    if (B <= 0) return 0;
+    if (Hkv <= 0 || Hq % Hkv != 0 || n_split < 1 || scratch == nullptr) return ODIN_ERR_BAD_ARG;
+    if (B > 65535 || Hq > 65535 || n_split > 65535) return ODIN_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    float* part_acc = scratch;
+    float* part_ml = scratch + (size_t)B * Hq * n_split * hd;
+#define CALL(HD)                                                                                                  \
+    return launch_decode<HD>((const bf16*)q, (size_t)q_row_stride, (bf16*)out, (size_t)out_row_stride, B, Hq, Hkv, \
+                             (const bf16*)k_cache, (const bf16*)v_cache, page_size, tok_pos, tok_seq, block_table, \
+                             bt_stride, window, part_acc, part_ml, n_split, s)
+    switch (hd) {
+        case 16: CALL(16);
+        case 32: CALL(32);
+        case 64: CALL(64);
+        case 128: CALL(128);
+        case 256: CALL(256);
+        default: return ODIN_ERR_UNSUPPORTED;
+    }
+#undef CALL
+}

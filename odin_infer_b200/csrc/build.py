@@ -32,6 +32,7 @@ GROUPS = {
     "attention_plain": ["attention_plain.cu"],
     "sampling": ["sampling.cu"],
     "gemm_tc": ["gemm_tc.cu"],
+    "attention_decode": ["attention_decode.cu"],
 }
 HEADERS = ["common.cuh"]
 

@@ -45,10 +45,25 @@ def _stream() -> c_void_p:
 _ERRORS = {-1: "unsupported size or element type", -2: "bad argument", -3: "device wait ran out"}
 
 
-def _check(code: int, what: str) -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this package launched so far (kernels inside replayed CUDA graphs included)."""
+    return _launches
+
+
+def add_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
+def _check(code: int, what: str, kernels: int = 1) -> None:
+    global _launches
     if code != 0:
         msg = _ERRORS.get(code, f"CUDA error {code}")
         raise KernelError(f"{what}: {msg}")
+    _launches += kernels
 
 
 def _fn(group: str, name: str):
@@ -212,6 +227,31 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int, hea
         c_int(T), c_int(n_q), c_int(n_kv), c_int(head_dim), _ptr(k_cache), _ptr(v_cache), c_int(PAGE),
         _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table), c_int(block_table.stride(0)), c_int(window),
         _stream()), "attention_plain")
+
+
+def attention_decode_supported(head_dim: int) -> bool:
+    return head_dim in (16, 32, 64, 128, 256)
+
+
+def attention_decode_scratch(n_tokens: int, n_q: int, head_dim: int, n_split: int) -> int:
+    """Floats of scratch that `attention_decode` needs."""
+    return n_tokens * n_q * n_split * (head_dim + 2)
+
+
+def attention_decode(q: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
+                     k_cache: torch.Tensor, v_cache: torch.Tensor, tok_pos: torch.Tensor, tok_seq: torch.Tensor,
+                     block_table: torch.Tensor, window: int, scratch: torch.Tensor, n_split: int) -> None:
+    """One query token per row over its sequence's bfloat16 cache, keys split n_split ways."""
+    B = q.shape[0]
+    assert q.dtype == out.dtype == k_cache.dtype == torch.bfloat16
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
+    assert q.shape[1] == n_q * head_dim and out.shape == (B, n_q * head_dim)
+    assert tuple(k_cache.shape[1:]) == (n_kv, PAGE, head_dim) and k_cache.is_contiguous()
+    assert scratch.dtype == torch.float32 and scratch.numel() >= attention_decode_scratch(B, n_q, head_dim, n_split)
+    _check(_fn("attention_decode", "odin_attention_decode")(
+        _ptr(q), c_longlong(q.stride(0)), _ptr(out), c_longlong(out.stride(0)), c_int(B), c_int(n_q), c_int(n_kv),
+        c_int(head_dim), _ptr(k_cache), _ptr(v_cache), c_int(PAGE), _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table),
+        c_int(block_table.stride(0)), c_int(window), _ptr(scratch), c_int(n_split), _stream()), "attention_decode", kernels=2)
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

@@ -18,6 +18,7 @@ from ..config import ModelConfig, load_config, lookup_architecture
 from ..csrc import build as kernel_build
 from ..sampling import SamplingParams, sample_batch
 from ..weights import load_weights, random_weights
+from .graphs import DecodeGraphs
 from .generate import GenerationResult, GenerationStats, generate
 from .model import DecoderModel
 from .runtime import Runtime
@@ -32,13 +33,15 @@ class Engine_Opts:
     limit, else min of both, infer/model.odin:220-223).  max_tokens: the most tokens
     that live sequences hold together, each rounded up to a page of 64; it sizes the
     cache (0: max_batch sequences of max_ctx).  dtype: "bfloat16" (the kernels and
-    precisions of serving) or "float32" (everything in true 32-bit)."""
+    precisions of serving) or "float32" (everything in true 32-bit).  cuda_graphs: replay
+    captured graphs for one-token-per-sequence steps (bfloat16 only)."""
     max_ctx: int = DEFAULT_MAX_CONTEXT
     max_tokens: int = 0
     max_batch: int = 8
     dtype: str = "bfloat16"
     device: str = "cuda:0"
     verbose: bool = True
+    cuda_graphs: bool = True
 
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
@@ -90,6 +93,9 @@ class Engine:
         nstate = self.cache.state_bytes_per_slot
         self.cache.state = torch.zeros(self.cache.max_slots, nstate, dtype=torch.uint8, device=self.rt.device)
         self.cache.zero_state = (lambda slot: self.cache.state[slot].zero_()) if nstate else None
+        # decode steps replay CUDA graphs in the serving precision; the 32-bit path stays eager
+        self.last_step_h2d_bytes = 0
+        self.graphs = DecodeGraphs(self.rt, self.model, self.cache) if (opts.cuda_graphs and self.rt.dtype == torch.bfloat16) else None
         if opts.verbose:
             print(self.summary(), file=sys.stderr, flush=True)
 
@@ -156,8 +162,14 @@ class Engine:
             for e, s in zip(grown, starts):  # leave the cache as it was
                 self._shrink(e.slot, s)
             raise
-        batch = StepBatch(self.cache, entries, starts, self.rt.device)
-        logits = self.rt.run(self.model, batch)
+        logits = NotImplemented
+        if self.graphs is not None and all(len(e.tokens) == 1 for e in entries):
+            logits = self.graphs.run(entries, starts)
+            self.last_step_h2d_bytes = self.graphs.last_h2d_bytes
+        if logits is NotImplemented:
+            batch = StepBatch(self.cache, entries, starts, self.rt.device)
+            logits = self.rt.run(self.model, batch)
+            self.last_step_h2d_bytes = batch.h2d_bytes
         for e in entries:
             self.cache.after_step(e.slot)
         return logits
@@ -186,6 +198,8 @@ class Engine:
         for g in self.cache.groups.values():
             g.k = g.v = None
         self.cache.state = None
+        if self.graphs is not None:
+            self.graphs.clear()
         self.model = None
         torch.cuda.empty_cache()
 

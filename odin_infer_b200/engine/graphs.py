@@ -1,0 +1,67 @@
+"""CUDA graphs of the decode step.
+
+A step in which every sequence brings one token launches a few hundred small
+kernels; at small batches the launches cost more than the kernels.  Such steps
+are captured once per batch-size bucket and replayed: the step's integer tables
+live in fixed device buffers that are refilled before every replay, padding rows
+(sequence -1) make up the difference to the bucket size and change no result.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import ops
+from .step import StepBatch, StepEntry
+
+BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+
+
+def bucket_for(n: int) -> int | None:
+    for b in BUCKETS:
+        if n <= b:
+            return b
+    return None
+
+
+class DecodeGraphs:
+    def __init__(self, rt, model, cache):
+        self.rt, self.model, self.cache = rt, model, cache
+        self._graphs: dict[int, tuple] = {}
+        self.last_h2d_bytes = 0
+
+    def run(self, entries: list[StepEntry], starts: list[int]) -> torch.Tensor | None:
+        """Logits [wanted, vocab] of a one-token-per-sequence step, or NotImplemented if
+        the batch is larger than the largest bucket."""
+        bucket = bucket_for(len(entries))
+        if bucket is None:
+            return NotImplemented
+        hit = self._graphs.get(bucket)
+        if hit is None:
+            batch = StepBatch(self.cache, entries, starts, self.rt.device, pad_rows_to=bucket, pad_seqs_to=bucket,
+                              all_rows_wanted=True)
+            # once eagerly: first-use set-up of the kernels (function attributes, tensor maps,
+            # error flags, the allocator's pools) must not fall into the capture
+            self.model.forward(self.rt, batch)
+            torch.cuda.current_stream().synchronize()
+            graph = torch.cuda.CUDAGraph()
+            n0 = ops.launch_count()
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(self.rt, batch)
+            self._graphs[bucket] = (graph, batch, logits, ops.launch_count() - n0)
+            # the eager run and the capture have written this step's keys already; a replay writes them again
+        else:
+            batch = hit[1]
+            batch.fill(entries, starts)
+        graph, batch, logits, n_kernels = self._graphs[bucket]
+        graph.replay()
+        ops.add_launches(n_kernels)
+        self.last_h2d_bytes = batch.h2d_bytes
+        rows = batch.wanted_rows
+        if not rows:
+            return None
+        if rows == list(range(len(rows))):
+            return logits[:len(rows)]
+        return logits[torch.tensor(rows, device=logits.device)]
+
+    def clear(self) -> None:
+        self._graphs.clear()

@@ -8,31 +8,85 @@ import torch
 from ..csrc import ops
 
 
+def choose_k_split(n_tiles: int, k_blocks: int, m: int, n_sms: int = 148, max_split: int = 16) -> int:
+    """Into how many parts to cut K for a product of few tokens, so that the tiles fill
+    the SMs in whole waves.  Cost of a choice, in units of one 64-wide K block of one
+    tile: waves x (blocks per part + pipeline fill + the partial sums' traffic).
+    The choice depends on the weight's shape alone, never on the tokens of the batch
+    beyond their padded count, so a token's sums are cut the same way in every batch
+    of the same bucket."""
+    best, best_cost = 1, None
+    for s in range(1, max_split + 1):
+        per = (k_blocks + s - 1) // s
+        if per < 4 and s > 1:
+            break
+        parts = (k_blocks + per - 1) // per
+        waves = (n_tiles * parts + n_sms - 1) // n_sms
+        cost = waves * (per + 4 + (m / 16.0 if parts > 1 else 0.0))
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = parts, cost
+    return best
+
+
 class Runtime:
     def __init__(self, device, dtype: torch.dtype):
         if dtype not in (torch.float32, torch.bfloat16):
             raise ValueError(f"the engine runs in float32 or bfloat16, not {dtype}")
         self.device = torch.device(device)
         self.dtype = dtype
+        self.n_sms = torch.cuda.get_device_properties(self.device).multi_processor_count if self.device.type == "cuda" else 148
 
     def kernel_groups(self) -> set[str]:
         """Kernel libraries the runtime itself may launch, beside those of the parts."""
-        return set()
+        return {"gemm_tc", "attention_decode"} if self.dtype == torch.bfloat16 else set()
 
     def run(self, model, batch):
-        """Run one step of `model`; returns the logits at the wanted rows."""
+        """Run one step of `model` eagerly; returns the logits at the wanted rows."""
         return model.forward(self, batch)
 
     def empty(self, *shape, dtype: torch.dtype | None = None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
 
     # ---- matrix product: out[M, N] = a[M, K] @ w[N, K]^T -----------------
-    def linear(self, a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
-        out = self.empty(a.shape[0], w.shape[0], dtype=out_dtype or self.dtype)
+    def linear(self, a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
+               may_split: bool = False) -> torch.Tensor:
+        """bfloat16 operands that TMA can read go to the tcgen05 kernel, everything else
+        (the 32-bit path, odd widths, tensors stored in 32-bit) to the CUDA-core kernel.
+
+        may_split: the caller's consumer adds partial sums, so a product of few tokens
+        may come back as float32 [parts, M, N] (split along K to occupy every SM)."""
+        M, N, K = a.shape[0], w.shape[0], a.shape[1]
+        out_dtype = out_dtype or self.dtype
+        if M > 0 and ops.gemm_tc_supported(a, w):
+            if M <= 128:
+                bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
+                n_split = choose_k_split((N + 127) // 128, (K + 63) // 64, M, self.n_sms) if may_split else 1
+                n_split = ops.gemm_tc_splits(K, n_split)
+                if n_split > 1:
+                    out = self.empty(n_split, M, N, dtype=torch.float32)
+                    ops.gemm_tc(a, w, out, 1, bn, n_split)
+                    return out
+                out = self.empty(M, N, dtype=out_dtype)
+                ops.gemm_tc(a, w, out, 1, bn)
+                return out
+            out = self.empty(M, N, dtype=out_dtype)
+            ops.gemm_tc(a, w, out, 0, 256 if N > 128 else 128 if N > 64 else 64)
+            return out
+        out = self.empty(M, N, dtype=out_dtype)
         ops.gemm_plain(a, w, out)
         return out
 
     # ---- attention over the cache ---------------------------------------
     def attention(self, step, q, out, n_q, n_kv, head_dim, k_line, v_line, block_table, window) -> None:
+        """One token per sequence in bfloat16: the split-key kernel.  Everything else (the
+        32-bit path, prompts, head sizes the fast kernels refuse): the plain kernel."""
+        if self.dtype == torch.bfloat16 and step.all_single and ops.attention_decode_supported(head_dim):
+            B = q.shape[0]
+            ctas = B * n_kv * ((n_q // n_kv + 3) // 4)
+            n_split = max(1, min(16, (2 * self.n_sms + ctas - 1) // ctas))
+            scratch = self.empty(ops.attention_decode_scratch(B, n_q, head_dim, n_split), dtype=torch.float32)
+            ops.attention_decode(q, out, n_q, n_kv, head_dim, k_line, v_line, step.tok_pos, step.tok_seq, block_table,
+                                 window, scratch, n_split)
+            return
         ops.attention_plain(q, out, n_q, n_kv, head_dim, k_line, v_line, step.tok_pos, step.tok_seq, block_table,
                             window)

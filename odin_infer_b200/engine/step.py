@@ -4,8 +4,12 @@ to find each token's sequence, position and cache pages.
 A step is either a start (sequences bring their first tokens, of unequal
 number) or a continuation by one token each; continuations by several tokens
 are accepted too (a prompt cut in pieces).  Only the tokens given are run.
-Padding rows (used to give a replayed CUDA graph a fixed shape) carry sequence
+Padding rows (they give a replayed CUDA graph a fixed shape) carry sequence
 number -1 and are skipped by every kernel that reads or writes the cache.
+
+All integer tables of a step live in one pinned host array and one device array
+of the same layout, so a step costs one host-to-device copy; a captured decode
+graph keeps its device array and is refilled in place.
 """
 from __future__ import annotations
 
@@ -28,49 +32,123 @@ class StepError(ValueError):
 
 
 class StepBatch:
-    """Device-side view of a step, handed to every part."""
+    """Device-side view of a step, handed to every part.
 
-    def __init__(self, cache, entries: list[StepEntry], start_positions: list[int], device, pad_rows_to: int = 0):
+    Per token row t (n_rows of them, the first n_tokens real): tok_ids[t], tok_pos[t]
+    (position in its sequence), tok_seq[t] (which sequence of this step; -1 padding).
+    Per sequence b: seq_slots[b] (its slot: row of the state area), seq_start[b]
+    (first token row; n_seqs + 1 entries), seq_len_after[b] (its length once this step
+    is done), and one block table row per cache group.  logit_rows: the token rows
+    whose logits are wanted.
+    """
+
+    def __init__(self, cache, entries: list[StepEntry], start_positions: list[int], device,
+                 pad_rows_to: int = 0, pad_seqs_to: int = 0, all_rows_wanted: bool = False):
         self.cache = cache
-        self.n_seqs = len(entries)
-        tok_ids, tok_pos, tok_seq, rows = [], [], [], []
-        seq_start = [0]
+        self.device = device
+        self.n_seq_cap = max(len(entries), pad_seqs_to)
+        self.n_row_cap = max(sum(len(e.tokens) for e in entries), pad_rows_to)
+        self.all_rows_wanted = all_rows_wanted
+        wanted = sum(len(e.want) for e in entries)
+        self.n_logit_cap = self.n_row_cap if all_rows_wanted else wanted
+        # layout of the arena (int32 counts)
+        off = 0
+        self._where: dict[str, tuple[int, tuple[int, ...]]] = {}
+
+        def put(name, *shape):
+            nonlocal off
+            n = int(np.prod(shape)) if shape else 1
+            self._where[name] = (off, shape)
+            off += (n + 3) // 4 * 4  # keep every table 16-byte aligned
+        put("tok_ids", self.n_row_cap)
+        put("tok_pos", self.n_row_cap)
+        put("tok_seq", self.n_row_cap)
+        put("logit_rows", self.n_logit_cap)
+        put("seq_start", self.n_seq_cap + 1)
+        put("seq_slots", self.n_seq_cap)
+        put("seq_len_after", self.n_seq_cap)
+        for key, g in cache.groups.items():
+            put(("bt", key), self.n_seq_cap, g.max_pages_per_seq)
+        self._host_t = torch.empty(max(off, 4), dtype=torch.int32, pin_memory=(torch.device(device).type == "cuda"))
+        self._host = self._host_t.numpy()
+        self._dev = torch.empty(max(off, 4), dtype=torch.int32, device=device)
+
+        def view(name):
+            o, shape = self._where[name]
+            n = int(np.prod(shape)) if shape else 1
+            return self._dev[o:o + n].view(*shape)
+        self.tok_ids, self.tok_pos, self.tok_seq = view("tok_ids"), view("tok_pos"), view("tok_seq")
+        self.logit_rows = view("logit_rows")
+        self.seq_start, self.seq_slots, self.seq_len_after = view("seq_start"), view("seq_slots"), view("seq_len_after")
+        self.block_tables = {key: view(("bt", key)) for key in cache.groups}
+        self._copied = None
+        self.h2d_bytes = self._host_t.numel() * 4
+        self.fill(entries, start_positions)
+
+    def _h(self, name):
+        o, shape = self._where[name]
+        n = int(np.prod(shape)) if shape else 1
+        return self._host[o:o + n].reshape(shape)
+
+    def fill(self, entries: list[StepEntry], start_positions: list[int]) -> None:
+        """(Re)write the tables for these entries and copy them to the device."""
+        if self._copied is not None:
+            self._copied.synchronize()  # the last copy out of the pinned array must be over before it is rewritten
+        n_tok = sum(len(e.tokens) for e in entries)
+        if len(entries) > self.n_seq_cap or n_tok > self.n_row_cap:
+            raise StepError("step does not fit the buffers it was built for")
+        ids, pos, seq = self._h("tok_ids"), self._h("tok_pos"), self._h("tok_seq")
+        ids[:] = 0
+        pos[:] = 0
+        seq[:] = -1
+        starts = self._h("seq_start")
+        starts[:] = n_tok
+        rows = []
+        r = 0
         for b, (e, p0) in enumerate(zip(entries, start_positions)):
-            base = len(tok_ids)
             n = len(e.tokens)
-            tok_ids.extend(e.tokens)
-            tok_pos.extend(range(p0, p0 + n))
-            tok_seq.extend([b] * n)
-            seq_start.append(base + n)
+            ids[r:r + n] = e.tokens
+            pos[r:r + n] = np.arange(p0, p0 + n, dtype=np.int32)
+            seq[r:r + n] = b
+            starts[b] = r
             for w in e.want:
                 if not (0 <= w < n):
                     raise StepError(f"slot {e.slot}: wanted place {w} is outside its {n} token(s)")
-                rows.append(base + w)
-        self.n_tokens = len(tok_ids)
-        self.n_rows = max(self.n_tokens, pad_rows_to)
-        pad = self.n_rows - self.n_tokens
-        tok_ids += [0] * pad
-        tok_pos += [0] * pad
-        tok_seq += [-1] * pad
-        self.all_single = all(len(e.tokens) == 1 for e in entries)
-        self.max_new = max((len(e.tokens) for e in entries), default=0)
+                rows.append(r + w)
+            r += n
+        self.n_seqs = len(entries)
+        self.n_tokens = n_tok
+        self.n_rows = self.n_row_cap
         self.slots = [e.slot for e in entries]
+        self.wanted_rows = rows
+        lr = self._h("logit_rows")
+        if self.all_rows_wanted:
+            lr[:] = np.arange(self.n_row_cap, dtype=np.int32)
+            self.n_logit_rows = self.n_row_cap
+        else:
+            if len(rows) != self.n_logit_cap:
+                raise StepError("the number of wanted rows changed under fixed buffers")
+            lr[:] = rows
+            self.n_logit_rows = len(rows)
+        sl, la = self._h("seq_slots"), self._h("seq_len_after")
+        sl[:] = 0
+        la[:] = 0
+        sl[:self.n_seqs] = self.slots
         self.lengths_after = [p0 + len(e.tokens) for e, p0 in zip(entries, start_positions)]
+        la[:self.n_seqs] = self.lengths_after
+        self.all_single = all(len(e.tokens) == 1 for e in entries)
+        self.all_start = all(p0 == 0 for p0 in start_positions)
+        self.max_new = max((len(e.tokens) for e in entries), default=0)
         self.max_len_after = max(self.lengths_after, default=0)
-        self.n_logit_rows = len(rows)
-
-        def dev(a):
-            return torch.tensor(a, dtype=torch.int32).to(device, non_blocking=True) if len(a) else \
-                torch.zeros(0, dtype=torch.int32, device=device)
-        self.tok_ids, self.tok_pos, self.tok_seq = dev(tok_ids), dev(tok_pos), dev(tok_seq)
-        self.logit_rows = dev(rows)
-        self.seq_start = dev(seq_start)
-        self.seq_slots = dev(self.slots)
-        self.seq_len_after = dev(self.lengths_after)
-        self.block_tables = {}
-        for key, g in cache.groups.items():
-            bt = np.ascontiguousarray(g.block_table[self.slots]) if self.slots else np.zeros((0, g.max_pages_per_seq), np.int32)
-            self.block_tables[key] = torch.from_numpy(bt).to(device, non_blocking=True)
+        for key, g in self.cache.groups.items():
+            bt = self._h(("bt", key))
+            bt[:] = -1
+            if self.slots:
+                bt[:self.n_seqs] = g.block_table[self.slots]
+        self._dev.copy_(self._host_t, non_blocking=True)
+        if self._dev.is_cuda:
+            self._copied = torch.cuda.Event()
+            self._copied.record()
 
     # ---- what a mixer asks for ------------------------------------------
     def kv(self, entry: int):

@@ -80,4 +80,4 @@ class GQAttention(Mixer):
         q = qkv[:, : self.n_q * self.hd]
         o = rt.empty(T, self.n_q * self.hd)
         rt.attention(step, q, o, self.n_q, self.n_kv, self.hd, k_line, v_line, block_table, self.window)
-        return rt.linear(o, self.w_o, out_dtype=torch.float32)
+        return rt.linear(o, self.w_o, out_dtype=torch.float32, may_split=True)

@@ -36,4 +36,4 @@ class SwiGLU(FeedForward):
         gu = rt.linear(h, self.w_gate_up)
         act = rt.empty(h.shape[0], self.inner)
         ops.swiglu(gu, act)
-        return rt.linear(act, self.w_down, out_dtype=torch.float32)
+        return rt.linear(act, self.w_down, out_dtype=torch.float32, may_split=True)

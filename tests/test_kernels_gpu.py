@@ -281,3 +281,78 @@ def test_repetition_penalty():
     ref = torch.stack([P.repetition_penalty(logits[b].cpu(), [t for t in recent[b].tolist() if t >= 0], 2.0) for b in range(2)])
     ops.repetition_penalty(logits, recent, 2.0)
     assert torch.equal(logits.cpu(), ref)
+
+
+@pytest.mark.parametrize("geom", [(4, 2, 16), (6, 2, 32), (8, 8, 64), (32, 8, 128), (5, 1, 128), (3, 3, 256), (16, 2, 64)])
+@pytest.mark.parametrize("n_split", [1, 3, 16])
+def test_attention_decode_against_plain_kernel_and_reference(geom, n_split):
+    """The split-key decode kernel: every sequence at its own length (1 .. several pages),
+    scrambled pages, a padding row, all split counts; against a direct computation."""
+    from odin_infer_b200.csrc import ops
+    n_q, n_kv, hd = geom
+    lengths = [1, 64, 65, 200, 333]
+    B = len(lengths)
+    torch.manual_seed(n_q + hd + n_split)
+    k_cache, v_cache, bt = paged_cache(B, lengths, n_kv, hd, torch.bfloat16)
+    keys = [torch.randn(n, n_kv, hd, device=DEV).bfloat16() for n in lengths]
+    vals = [torch.randn(n, n_kv, hd, device=DEV).bfloat16() for n in lengths]
+    for s, n in enumerate(lengths):
+        for p in range(n):
+            page = int(bt[s, p // 64])
+            k_cache[page, :, p % 64] = keys[s][p]
+            v_cache[page, :, p % 64] = vals[s][p]
+    # rows: the sequences in a shuffled order plus one padding row in the middle
+    order = [3, 0, -1, 4, 1, 2]
+    tok_seq = torch.tensor(order, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([lengths[s] - 1 if s >= 0 else 0 for s in order], dtype=torch.int32, device=DEV)
+    q = torch.randn(len(order), n_q * hd, device=DEV).bfloat16()
+    out = torch.full((len(order), n_q * hd), 7.0, device=DEV, dtype=torch.bfloat16)
+    scratch = torch.empty(ops.attention_decode_scratch(len(order), n_q, hd, n_split), device=DEV)
+    ops.attention_decode(q, out, n_q, n_kv, hd, k_cache, v_cache, tok_pos, tok_seq, bt, 0, scratch, n_split)
+    plain = torch.full_like(out, 7.0)
+    ops.attention_plain(q, plain, n_q, n_kv, hd, k_cache, v_cache, tok_pos, tok_seq, bt, 0)
+    assert torch.equal(out[2], torch.full_like(out[2], 7.0)), "a padding row must not be written"
+    for r, s in enumerate(order):
+        if s < 0:
+            continue
+        qs = q[r].double().view(n_q, hd).cpu()
+        ref = torch.zeros(n_q, hd, dtype=torch.float64)
+        for h in range(n_q):
+            kh = h // (n_q // n_kv)
+            sc = (keys[s][:, kh].double().cpu() @ qs[h]) / math.sqrt(hd)
+            ref[h] = torch.softmax(sc, 0) @ vals[s][:, kh].double().cpu()
+        close(out[r].view(n_q, hd), ref, 1e-2)
+        close(out[r].float(), plain[r].float(), 1e-2)
+
+
+def test_attention_decode_window_and_far_key():
+    from odin_infer_b200.csrc import ops
+    n_q, n_kv, hd, n = 4, 2, 64, 300
+    torch.manual_seed(5)
+    k_cache, v_cache, bt = paged_cache(1, [n], n_kv, hd, torch.bfloat16)
+    keys = 0.1 * torch.randn(n, n_kv, hd, device=DEV)
+    vals = torch.randn(n, n_kv, hd, device=DEV)
+    far = 67
+    keys[far] = 0.0
+    keys[far, :, 0] = 40.0
+    q = 0.1 * torch.randn(1, n_q, hd, device=DEV)
+    q[0, :, 0] = 40.0 / math.sqrt(hd) * 2
+    for p in range(n):
+        page = int(bt[0, p // 64])
+        k_cache[page, :, p % 64] = keys[p].bfloat16()
+        v_cache[page, :, p % 64] = vals[p].bfloat16()
+    tok_pos = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
+    tok_seq = torch.zeros(1, dtype=torch.int32, device=DEV)
+    qf = q.reshape(1, n_q * hd).bfloat16()
+    out = torch.empty(1, n_q * hd, device=DEV, dtype=torch.bfloat16)
+    for n_split in (1, 4, 7):
+        scratch = torch.empty(ops.attention_decode_scratch(1, n_q, hd, n_split), device=DEV)
+        ops.attention_decode(qf, out, n_q, n_kv, hd, k_cache, v_cache, tok_pos, tok_seq, bt, 0, scratch, n_split)
+        close(out.float().view(n_q, hd)[0], vals[far, 0].bfloat16().float(), 2e-2)
+        ops.attention_decode(qf, out, n_q, n_kv, hd, k_cache, v_cache, tok_pos, tok_seq, bt, n - 1 - far, scratch, n_split)
+        assert (out.float().view(n_q, hd)[0] - vals[far, 0]).abs().max() > 0.1      # just outside the window
+        ref = torch.empty_like(out)
+        ops.attention_plain(qf, ref, n_q, n_kv, hd, k_cache, v_cache, tok_pos, tok_seq, bt, n - 1 - far)
+        close(out.float(), ref.float(), 1e-2)
+        ops.attention_decode(qf, out, n_q, n_kv, hd, k_cache, v_cache, tok_pos, tok_seq, bt, n - far, scratch, n_split)
+        close(out.float().view(n_q, hd)[0], vals[far, 0].bfloat16().float(), 2e-2)  # just inside
