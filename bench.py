@@ -189,6 +189,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (both numbers are reported)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for profilers)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end run (for profilers)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -218,7 +220,8 @@ def main() -> int:
     need = PROMPT + warmup + args.steps + 8
     max_tokens = max(max_batch * ((need + 63) // 64 * 64), ((PREFILL_TOKENS + 63) // 64) * 64)
     engine = Engine.random(cfg, WEIGHT_SEED, Engine_Opts(max_ctx=CONTEXT, max_tokens=max_tokens, max_batch=max_batch,
-                                                         dtype="bfloat16", verbose=False))
+                                                         dtype="bfloat16", verbose=False,
+                                                         cuda_graphs=not args.no_graphs))
 
     sampler = ClockSampler()
     sampler.start()
@@ -231,10 +234,13 @@ def main() -> int:
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": round(achieved / peaks["hbm_gbs"], 4), "peak_source": peak_source}
 
-    stats = run_e2e(engine, args.batch, args.steps, vocab)
-    e2e = {"value": round(stats.decode_tokens_per_s, 1), "unit": "tokens/s",
-           "h2d_bytes_per_step": int(engine.last_step_h2d_bytes), "d2h_bytes_per_step": 4 * args.batch,
-           "ttft_ms": round(stats.ttft_s * 1e3, 2)}
+    if args.no_e2e:
+        e2e = None
+    else:
+        stats = run_e2e(engine, args.batch, args.steps, vocab)
+        e2e = {"value": round(stats.decode_tokens_per_s, 1), "unit": "tokens/s",
+               "h2d_bytes_per_step": int(engine.last_step_h2d_bytes), "d2h_bytes_per_step": 4 * args.batch,
+               "ttft_ms": round(stats.ttft_s * 1e3, 2)}
 
     out = {
         "metric": "decode tokens/s (Qwen3-8B shape, bf16, batch %d, 512-token prompts)" % args.batch,
@@ -247,8 +253,8 @@ def main() -> int:
                    "kv_heads": cfg_raw["num_key_value_heads"], "head_dim": cfg_raw["head_dim"],
                    "intermediate": cfg_raw["intermediate_size"], "vocab": vocab, "global_batch": args.batch,
                    "prompt_len": PROMPT, "seq_len": CONTEXT, "decode_ctx_mean": round(mean_ctx, 1),
-                   "parallelism": "single GPU", "l2": "inputs larger than L2 (15 GB of weights per step)",
-                   "cuda_graphs": True},
+                   "parallelism": "single GPU", "l2": "inputs larger than L2 (%.1f GB read per step)" % (bytes_step / 1e9),
+                   "cuda_graphs": not args.no_graphs},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline,
     }
     if not args.no_points:

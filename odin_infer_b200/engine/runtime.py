@@ -38,7 +38,7 @@ class Runtime:
 
     def kernel_groups(self) -> set[str]:
         """Kernel libraries the runtime itself may launch, beside those of the parts."""
-        return {"gemm_tc", "attention_decode"} if self.dtype == torch.bfloat16 else set()
+        return {"gemm_tc", "attention_decode", "attention_prefill"} if self.dtype == torch.bfloat16 else set()
 
     def run(self, model, batch):
         """Run one step of `model` eagerly; returns the logits at the wanted rows."""
@@ -78,8 +78,9 @@ class Runtime:
 
     # ---- attention over the cache ---------------------------------------
     def attention(self, step, q, out, n_q, n_kv, head_dim, k_line, v_line, block_table, window) -> None:
-        """One token per sequence in bfloat16: the split-key kernel.  Everything else (the
-        32-bit path, prompts, head sizes the fast kernels refuse): the plain kernel."""
+        """bfloat16: one token per sequence goes to the split-key kernel, prompts (and pieces
+        of prompts) to the flash kernel.  The 32-bit path and head sizes that the fast
+        kernels refuse go to the plain kernel."""
         if self.dtype == torch.bfloat16 and step.all_single and ops.attention_decode_supported(head_dim):
             B = q.shape[0]
             ctas = B * n_kv * ((n_q // n_kv + 3) // 4)
@@ -87,6 +88,10 @@ class Runtime:
             scratch = self.empty(ops.attention_decode_scratch(B, n_q, head_dim, n_split), dtype=torch.float32)
             ops.attention_decode(q, out, n_q, n_kv, head_dim, k_line, v_line, step.tok_pos, step.tok_seq, block_table,
                                  window, scratch, n_split)
+            return
+        if self.dtype == torch.bfloat16 and not step.all_single and ops.attention_prefill_supported(head_dim):
+            ops.attention_prefill(q, out, step.n_seqs, step.max_new, n_q, n_kv, head_dim, k_line, v_line,
+                                  step.seq_start, step.seq_len_after, block_table, window)
             return
         ops.attention_plain(q, out, n_q, n_kv, head_dim, k_line, v_line, step.tok_pos, step.tok_seq, block_table,
                             window)

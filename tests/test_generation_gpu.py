@@ -41,7 +41,7 @@ def check_greedy(folder, prompts, outs, margin):
 
 
 @pytest.mark.parametrize("dtype,margin", [("float32", 1e-5), ("bfloat16", 3e-2)])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_greedy_generation_matches_plain(folders, name, dtype, margin):
     vocab = tiny.TINIES[name][0]["vocab_size"]
     prompts = [tiny.random_tokens(n, vocab, 200 + n) for n in (5, 11, 17, 1, 70, 40, 23)]

@@ -356,3 +356,87 @@ def test_attention_decode_window_and_far_key():
         close(out.float(), ref.float(), 1e-2)
         ops.attention_decode(qf, out, n_q, n_kv, hd, k_cache, v_cache, tok_pos, tok_seq, bt, n - far, scratch, n_split)
         close(out.float().view(n_q, hd)[0], vals[far, 0].bfloat16().float(), 2e-2)  # just inside
+
+
+@pytest.mark.parametrize("geom", [(4, 2, 64), (8, 8, 64), (4, 1, 128), (6, 2, 128), (32, 8, 128)])
+@pytest.mark.parametrize("window", [0, 50])
+def test_attention_prefill_against_plain_kernel_and_reference(geom, window):
+    """The flash kernel: prompts of unequal lengths that start at 0 or continue from a
+    non-zero position, pages scrambled, lengths around the tile and page sizes; unwritten
+    cache slots hold NaN, which must never reach a result."""
+    from odin_infer_b200.csrc import ops
+    n_q, n_kv, hd = geom
+    # (already in the cache, new in this step)
+    parts = [(0, 1), (0, 63), (0, 64), (0, 65), (0, 200), (70, 3), (64, 64), (5, 130)]
+    lengths = [a + b for a, b in parts]
+    B = len(parts)
+    torch.manual_seed(n_q * 7 + hd + window)
+    k_cache, v_cache, bt = paged_cache(B, lengths, n_kv, hd, torch.bfloat16)
+    keys = [torch.randn(n, n_kv, hd, device=DEV).bfloat16() for n in lengths]
+    vals = [torch.randn(n, n_kv, hd, device=DEV).bfloat16() for n in lengths]
+    for s, n in enumerate(lengths):
+        for pg in range((n + 63) // 64):
+            page = int(bt[s, pg])
+            a, b = pg * 64, min(n, pg * 64 + 64)
+            k_cache[page, :, : b - a] = keys[s][a:b].transpose(0, 1)
+            v_cache[page, :, : b - a] = vals[s][a:b].transpose(0, 1)
+    T = sum(b for _, b in parts)
+    q = torch.randn(T, n_q * hd, device=DEV).bfloat16()
+    seq_start = torch.tensor([0] + list(np.cumsum([b for _, b in parts])), dtype=torch.int32, device=DEV)
+    seq_len_after = torch.tensor(lengths, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([a + i for a, b in parts for i in range(b)], dtype=torch.int32, device=DEV)
+    tok_seq = torch.tensor([s for s, (a, b) in enumerate(parts) for _ in range(b)], dtype=torch.int32, device=DEV)
+    out = torch.empty(T, n_q * hd, device=DEV, dtype=torch.bfloat16)
+    ops.attention_prefill(q, out, B, max(b for _, b in parts), n_q, n_kv, hd, k_cache, v_cache, seq_start,
+                          seq_len_after, bt, window)
+    ops.attention_prefill_check()
+    assert not torch.isnan(out.float()).any()
+    plain = torch.empty_like(out)
+    ops.attention_plain(q, plain, n_q, n_kv, hd, k_cache, v_cache, tok_pos, tok_seq, bt, window)
+    close(out.float(), plain.float(), 1e-2)
+    r = 0
+    for s, (a, b) in enumerate(parts):
+        n = a + b
+        qs = q[r:r + b].double().view(b, n_q, hd).cpu()
+        pos = torch.arange(a, n)
+        t = torch.arange(n)
+        allowed = t[None, :] <= pos[:, None]
+        if window:
+            allowed &= t[None, :] > pos[:, None] - window
+        for h in range(n_q):
+            kh = h // (n_q // n_kv)
+            sc = (qs[:, h] @ keys[s][:, kh].double().cpu().t()) / math.sqrt(hd)
+            sc = sc.masked_fill(~allowed, float("-inf"))
+            ref = torch.softmax(sc, -1) @ vals[s][:, kh].double().cpu()
+            close(out[r:r + b].view(b, n_q, hd)[:, h], ref, 1e-2)
+        r += b
+
+
+def test_attention_prefill_long_prompt_far_key():
+    """2,048 tokens: one key early in the prompt is made to dominate every later query."""
+    from odin_infer_b200.csrc import ops
+    n_q, n_kv, hd, n = 4, 2, 128, 2048
+    torch.manual_seed(9)
+    k_cache, v_cache, bt = paged_cache(1, [n], n_kv, hd, torch.bfloat16)
+    keys = 0.05 * torch.randn(n, n_kv, hd, device=DEV)
+    vals = torch.randn(n, n_kv, hd, device=DEV)
+    far = 100
+    keys[far] = 0.0
+    keys[far, :, 5] = 30.0
+    q = 0.05 * torch.randn(n, n_q, hd, device=DEV)
+    q[:, :, 5] = 30.0 / math.sqrt(hd) * 3
+    for pg in range(n // 64):
+        page = int(bt[0, pg])
+        k_cache[page] = keys[pg * 64:pg * 64 + 64].transpose(0, 1).bfloat16()
+        v_cache[page] = vals[pg * 64:pg * 64 + 64].transpose(0, 1).bfloat16()
+    out = torch.empty(n, n_q * hd, device=DEV, dtype=torch.bfloat16)
+    seq_start = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+    seq_len_after = torch.tensor([n], dtype=torch.int32, device=DEV)
+    ops.attention_prefill(q.reshape(n, -1).bfloat16(), out, 1, n, n_q, n_kv, hd, k_cache, v_cache, seq_start,
+                          seq_len_after, bt, 0)
+    ops.attention_prefill_check()
+    got = out.float().view(n, n_q, hd)
+    for t in (far, far + 1, 777, n - 1):
+        for h in range(n_q):
+            close(got[t, h], vals[far, h // 2].bfloat16().float(), 2e-2)
+    assert (got[far - 1, 0] - vals[far, 0]).abs().max() > 0.1   # causal: the key is not yet visible

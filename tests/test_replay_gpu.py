@@ -16,7 +16,8 @@ from tests import tiny, traces
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [5, 11, 17, 70, 129], "B": [1, 7, 23, 40, 64, 65, 200], "C": [3, 33, 90]}
+LENGTHS = {"A": [5, 11, 17, 70, 129], "B": [1, 7, 23, 40, 64, 65, 200], "C": [3, 33, 90],
+           "D": [1, 63, 64, 65, 130, 300], "E": [2, 40, 128, 257]}
 
 
 @pytest.fixture(scope="module")
@@ -62,21 +63,21 @@ def check(got, refs, dtype, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_whole(folders, requests_and_refs, name, dtype):
     reqs, refs = requests_and_refs[name]
     check(run(folders[name], dtype, traces.whole(reqs)), refs, dtype, "whole")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_last_32_one_by_one(folders, requests_and_refs, name, dtype):
     reqs, refs = requests_and_refs[name]
     check(run(folders[name], dtype, traces.tail_one_by_one(reqs, 32)), refs, dtype, "last32")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_unequal_batches_slots_reused(folders, requests_and_refs, name, dtype):
     reqs, refs = requests_and_refs[name]
     check(run(folders[name], dtype, traces.batches(reqs, 3)), refs, dtype, "batches of 3")

@@ -23,7 +23,15 @@ TINY_C = dict(architectures=["Qwen3ForCausalLM"], hidden_size=72, intermediate_s
               num_attention_heads=5, num_key_value_heads=1, head_dim=48, vocab_size=301, rope_theta=5e5,
               rms_norm_eps=1e-6, tie_word_embeddings=False)
 
-TINIES = {"A": (TINY_A, 0), "B": (TINY_B, 2), "C": (TINY_C, 8)}  # config, weight seed
+# head sizes 64 and 128: the ones the tensor-core attention kernels take
+TINY_D = dict(architectures=["Qwen3ForCausalLM"], hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+              num_attention_heads=4, num_key_value_heads=2, head_dim=64, vocab_size=512, rope_theta=1e6,
+              rms_norm_eps=1e-6, tie_word_embeddings=True)
+TINY_E = dict(architectures=["Qwen3ForCausalLM"], hidden_size=192, intermediate_size=320, num_hidden_layers=2,
+              num_attention_heads=4, num_key_value_heads=1, head_dim=128, vocab_size=1000, rope_theta=1e4,
+              rms_norm_eps=1e-5, tie_word_embeddings=False)
+
+TINIES = {"A": (TINY_A, 0), "B": (TINY_B, 2), "C": (TINY_C, 8), "D": (TINY_D, 11), "E": (TINY_E, 12)}  # config, weight seed
 
 
 def make_folder(tmp_path, raw: dict, seed: int, dtype=torch.bfloat16) -> str:
