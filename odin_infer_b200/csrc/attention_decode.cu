@@ -96,27 +96,24 @@ attn_decode_kernel(const bf16* __restrict__ q, size_t q_stride, int Hq, int Hkv,
         }
     }
 
+    // the page numbers of this split, once, so that the loop's loads do not wait for them
+    constexpr int PG_CAP = 128;
+    __shared__ int s_pg[PG_CAP];
     const int* bt = block_table + (size_t)max(seq, 0) * bt_stride;
-    for (int base = t_lo + warp * KPI; base < t_hi; base += AD_WARPS * KPI) {
-        const int tk = base + kg;
-        const bool valid = tk < t_hi;
-        float kf[EPL], vf[EPL];
-        size_t row = 0;
-        bool have = false;
-        if (valid) {
-            const int page = bt[tk / page_size];
-            if (page >= 0) {
-                row = (((size_t)page * Hkv + kvh) * page_size + (tk % page_size)) * HD + sub * EPL;
-                have = true;
-            }
-        }
-        if (have) {
-            load_bf16<EPL>(k_cache + row, kf);
-            load_bf16<EPL>(v_cache + row, vf);
-        } else {
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) { kf[e] = 0.f; vf[e] = 0.f; }
-        }
+    const int pg0 = t_lo / page_size;
+    const int n_pg = (t_hi > t_lo) ? ((t_hi - 1) / page_size - pg0 + 1) : 0;
+    for (int i = threadIdx.x; i < min(n_pg, PG_CAP); i += AD_WARPS * 32) s_pg[i] = bt[pg0 + i];
+    __syncthreads();
+
+    auto key_row = [&](int tk, size_t& row) -> bool {
+        if (tk >= t_hi) return false;
+        const int pi = tk / page_size - pg0;
+        const int page = (pi < PG_CAP) ? s_pg[pi] : bt[pg0 + pi];
+        if (page < 0) return false;
+        row = (((size_t)page * Hkv + kvh) * page_size + (tk % page_size)) * HD + sub * EPL;
+        return true;
+    };
+    auto absorb = [&](bool have, const float (&kf)[EPL], const float (&vf)[EPL]) {
 #pragma unroll
         for (int h = 0; h < G; ++h) {
             float s = 0.f;
@@ -134,6 +131,25 @@ attn_decode_kernel(const bf16* __restrict__ q, size_t q_stride, int Hq, int Hkv,
                 m[h] = m_new;
             }
         }
+    };
+    // two batches of keys per trip, all four loads issued before the arithmetic
+    for (int base = t_lo + warp * KPI; base < t_hi; base += 2 * AD_WARPS * KPI) {
+        float k0[EPL], v0[EPL], k1[EPL], v1[EPL];
+        size_t r0 = 0, r1 = 0;
+        const bool h0v = key_row(base + kg, r0);
+        const bool h1v = key_row(base + AD_WARPS * KPI + kg, r1);
+        if (h0v) { load_bf16<EPL>(k_cache + r0, k0); load_bf16<EPL>(v_cache + r0, v0); }
+        if (h1v) { load_bf16<EPL>(k_cache + r1, k1); load_bf16<EPL>(v_cache + r1, v1); }
+        if (!h0v) {
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) { k0[e] = 0.f; v0[e] = 0.f; }
+        }
+        if (!h1v) {
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) { k1[e] = 0.f; v1[e] = 0.f; }
+        }
+        absorb(h0v, k0, v0);
+        if (base + AD_WARPS * KPI < t_hi) absorb(h1v, k1, v1);
     }
 
     // merge the lane groups of the warp (lanes that hold the same elements of different keys)

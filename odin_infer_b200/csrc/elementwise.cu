@@ -38,7 +38,30 @@ extern "C" int odin_embed(const void* table, int table_dtype, const int* ids, fl
 // back to x when there is no row gather; out = w * (r * x_new).
 // The sum of squares goes over the columns in an order fixed by the block
 // size alone, so a row's result does not depend on the other rows.
-template <typename TD, typename TO>
+template <typename TD>
+__device__ __forceinline__ float4 load4(const TD* p);
+template <>
+__device__ __forceinline__ float4 load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <>
+__device__ __forceinline__ float4 load4<bf16>(const bf16* p) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&a);
+    u.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
+// VEC: the row length is a multiple of 4 and every pointer is 16-byte aligned, so the
+// row moves in groups of four; the order of the additions per element (x, then the
+// parts in order) and of the sum of squares per thread is the same in both variants.
+template <typename TD, typename TO, bool VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_split,
                                    size_t split_stride, VecRef w, float eps, TO* __restrict__ out,
                                    const int* __restrict__ rows, int d) {
@@ -54,40 +77,76 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
     }
     float* xr = x + (size_t)src * d;
     float ss = 0.f;
-    for (int j = threadIdx.x; j < d; j += blockDim.x) {
-        float v = xr[j];
-        if (delta != nullptr) {
-            for (int sidx = 0; sidx < n_split; ++sidx)
-                v += to_f32(delta[(size_t)sidx * split_stride + (size_t)src * d + j]);
+    if (VEC) {
+        for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
+            float4 v = load4<float>(xr + j);
+            if (delta != nullptr) {
+                for (int sidx = 0; sidx < n_split; ++sidx) {
+                    const float4 dv = load4<TD>(delta + (size_t)sidx * split_stride + (size_t)src * d + j);
+                    v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
+                }
+            }
+            store4(rowbuf + j, v);
+            ss += v.x * v.x; ss += v.y * v.y; ss += v.z * v.z; ss += v.w * v.w;
         }
-        rowbuf[j] = v;
-        ss += v * v;
+    } else {
+        for (int j = threadIdx.x; j < d; j += blockDim.x) {
+            float v = xr[j];
+            if (delta != nullptr) {
+                for (int sidx = 0; sidx < n_split; ++sidx)
+                    v += to_f32(delta[(size_t)sidx * split_stride + (size_t)src * d + j]);
+            }
+            rowbuf[j] = v;
+            ss += v * v;
+        }
     }
     ss = block_sum(ss, red);
     ss /= (float)d;
     ss += eps;
     const float rs = 1.0f / sqrtf(ss);
     const bool write_back = (delta != nullptr) && (rows == nullptr);
-    for (int j = threadIdx.x; j < d; j += blockDim.x) {
-        const float v = rowbuf[j];
-        if (write_back) xr[j] = v;
-        o[j] = from_f32<TO>(w.at(j) * (rs * v));
+    if (VEC) {
+        for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
+            const float4 v = load4<float>(rowbuf + j);
+            if (write_back) store4(xr + j, v);
+            store4(o + j, make_float4(w.at(j) * (rs * v.x), w.at(j + 1) * (rs * v.y), w.at(j + 2) * (rs * v.z),
+                                      w.at(j + 3) * (rs * v.w)));
+        }
+    } else {
+        for (int j = threadIdx.x; j < d; j += blockDim.x) {
+            const float v = rowbuf[j];
+            if (write_back) xr[j] = v;
+            o[j] = from_f32<TO>(w.at(j) * (rs * v));
+        }
     }
 }
 
 template <typename TD, typename TO>
 static int launch_add_rmsnorm(float* x, const void* delta, int n_split, size_t split_stride, VecRef w,
                               float eps, void* out, const int* rows, int n_rows, int d, cudaStream_t s) {
-    const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
     const size_t smem = (size_t)d * sizeof(float);
     if (smem > 200 * 1024) return ODIN_ERR_UNSUPPORTED;
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
+    const bool vec = (d % 4 == 0) && ((((uintptr_t)x) | ((uintptr_t)delta) | ((uintptr_t)out)) % 16 == 0) &&
+                     (split_stride % 4 == 0);
+    if (vec) {
+        const int threads = d >= 4096 ? 512 : (d >= 1024 ? 256 : 128);
+        if (smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO, true>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        add_rmsnorm_kernel<TD, TO, true><<<n_rows, threads, smem, s>>>(x, (const TD*)delta, n_split, split_stride, w,
+                                                                       eps, (TO*)out, rows, d);
+    } else {
+        const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+        if (smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO, false>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        add_rmsnorm_kernel<TD, TO, false><<<n_rows, threads, smem, s>>>(x, (const TD*)delta, n_split, split_stride, w,
+                                                                        eps, (TO*)out, rows, d);
     }
-    add_rmsnorm_kernel<TD, TO><<<n_rows, threads, smem, s>>>(x, (const TD*)delta, n_split, split_stride, w,
-                                                             eps, (TO*)out, rows, d);
     ODIN_LAUNCH_CHECK();
     return 0;
 }
@@ -117,31 +176,42 @@ extern "C" int odin_add_rmsnorm(float* x, const void* delta, int delta_dtype, in
 // -------------------------------------------------------------------- SwiGLU
 // gu: [T, 2I], gate in columns [0, I), up in [I, 2I).  h = g * (1/(1+exp(-g))) * u
 // in that order of products (infer/forward.odin:128-133).
-template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+template <typename TI, typename T>
+__global__ void swiglu_kernel(const TI* __restrict__ gu, int n_split, size_t split_stride, T* __restrict__ out, int I,
+                              size_t total) {
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I;
         const int j = (int)(idx - t * I);
-        float g = to_f32(gu[t * 2 * (size_t)I + j]);
-        const float u = to_f32(gu[t * 2 * (size_t)I + I + j]);
+        float g = 0.f, u = 0.f;
+        for (int s = 0; s < n_split; ++s) {
+            g += to_f32(gu[(size_t)s * split_stride + t * 2 * (size_t)I + j]);
+            u += to_f32(gu[(size_t)s * split_stride + t * 2 * (size_t)I + I + j]);
+        }
         g *= 1.0f / (1.0f + expf(-g));
         g *= u;
         out[idx] = from_f32<T>(g);
     }
 }
 
-extern "C" int odin_swiglu(const void* gu, void* out, int dtype, int T, int I, void* stream) {
+// gu: [n_split][T, 2I] of in_dtype (the parts are added first), out: [T, I] of out_dtype.
+extern "C" int odin_swiglu(const void* gu, int in_dtype, int n_split, long long split_stride, void* out,
+                           int out_dtype, int T, int I, void* stream) {
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t total = (size_t)T * I;
     const int threads = 256;
     size_t blocks = (total + threads - 1) / threads;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    if (dtype == ODIN_BF16)
-        swiglu_kernel<bf16><<<(int)blocks, threads, 0, s>>>((const bf16*)gu, (bf16*)out, I, total);
-    else if (dtype == ODIN_F32)
-        swiglu_kernel<float><<<(int)blocks, threads, 0, s>>>((const float*)gu, (float*)out, I, total);
+    if (in_dtype == ODIN_BF16 && out_dtype == ODIN_BF16)
+        swiglu_kernel<bf16, bf16><<<(int)blocks, threads, 0, s>>>((const bf16*)gu, n_split, (size_t)split_stride,
+                                                                  (bf16*)out, I, total);
+    else if (in_dtype == ODIN_F32 && out_dtype == ODIN_F32)
+        swiglu_kernel<float, float><<<(int)blocks, threads, 0, s>>>((const float*)gu, n_split, (size_t)split_stride,
+                                                                    (float*)out, I, total);
+    else if (in_dtype == ODIN_F32 && out_dtype == ODIN_BF16)
+        swiglu_kernel<float, bf16><<<(int)blocks, threads, 0, s>>>((const float*)gu, n_split, (size_t)split_stride,
+                                                                   (bf16*)out, I, total);
     else
         return ODIN_ERR_UNSUPPORTED;
     ODIN_LAUNCH_CHECK();

@@ -1,5 +1,6 @@
 // Per-head preparation of the fused q|k|v projection, one warp per (token, head):
-//   q heads: RMSNorm over the head (optional), rotation, written back in place;
+//   q heads: RMSNorm over the head (optional), rotation, written to q_out (which may be
+//            the projection itself: in place);
 //   k heads: RMSNorm (optional), rotation, written to the paged key cache;
 //   v heads: copied to the paged value cache.
 // Restates infer/forward.odin:58-85 (norm before rotation, one [hd] weight shared
@@ -14,9 +15,12 @@
 #define HP_WARPS 4
 #define HP_MAX_HD 512
 
-template <typename T>
+// TI: element type of the projection (bfloat16 or 32-bit; n_split 32-bit partial sums of a
+// split product are added first, in order).  T: element type of q_out and of the cache.
+template <typename TI, typename T>
 __global__ void __launch_bounds__(HP_WARPS * 32)
-head_prep_kernel(T* __restrict__ qkv, int Hq, int Hkv, int hd, size_t row_stride, VecRef qw, VecRef kw,
+head_prep_kernel(const TI* qkv, int n_split, size_t split_stride, T* q_out,  // may alias: no restrict
+                 size_t q_out_stride, int Hq, int Hkv, int hd, size_t row_stride, VecRef qw, VecRef kw,
                  int has_norm, float eps, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                  int rot, int table_len, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                  const int* __restrict__ block_table, int bt_stride, T* __restrict__ k_cache,
@@ -30,14 +34,14 @@ head_prep_kernel(T* __restrict__ qkv, int Hq, int Hkv, int hd, size_t row_stride
     const int seq = tok_seq[t];
     if (seq < 0) return;  // padding token
     const int pos = tok_pos[t];
-    T* src = qkv + (size_t)t * row_stride + (size_t)head * hd;
+    const TI* src = qkv + (size_t)t * row_stride + (size_t)head * hd;
 
     const bool is_q = head < Hq;
     const bool is_k = !is_q && head < Hq + Hkv;
     const int kvh = is_q ? 0 : (is_k ? head - Hq : head - Hq - Hkv);
     if (!is_q && !write_kv) return;
 
-    T* dst = src;
+    T* dst = q_out + (size_t)t * q_out_stride + (size_t)head * hd;
     if (!is_q) {
         const int page = block_table[(size_t)seq * bt_stride + pos / page_size];
         if (page < 0) return;
@@ -45,17 +49,17 @@ head_prep_kernel(T* __restrict__ qkv, int Hq, int Hkv, int hd, size_t row_stride
         dst = base + (((size_t)page * Hkv + kvh) * page_size + (pos % page_size)) * hd;
     }
 
-    if (!is_q && !is_k) {  // value head: plain copy
-        for (int j = lane; j < hd; j += 32) dst[j] = src[j];
-        return;
-    }
-
     float* b = buf[warp];
     float ss = 0.f;
     for (int j = lane; j < hd; j += 32) {
-        const float v = to_f32(src[j]);
+        float v = to_f32(src[j]);
+        for (int sp = 1; sp < n_split; ++sp) v += to_f32(src[(size_t)sp * split_stride + j]);
         b[j] = v;
         ss += v * v;
+    }
+    if (!is_q && !is_k) {  // value head: stored as it is
+        for (int j = lane; j < hd; j += 32) dst[j] = from_f32<T>(b[j]);
+        return;
     }
     if (has_norm) {
         ss = warp_sum(ss);
@@ -82,28 +86,32 @@ head_prep_kernel(T* __restrict__ qkv, int Hq, int Hkv, int hd, size_t row_stride
     }
 }
 
-extern "C" int odin_head_prep(void* qkv, int dtype, int T, int Hq, int Hkv, int hd, long long row_stride,
+// qkv: [n_split][T, (Hq + 2 Hkv) hd] of in_dtype (row stride row_stride, parts split_stride
+// elements apart).  q_out: [T, Hq hd] of dtype (row stride q_out_stride); it may be qkv
+// itself when there is one part of the same type (q is then normalised and rotated in place).
+extern "C" int odin_head_prep(const void* qkv, int in_dtype, int n_split, long long split_stride, void* q_out,
+                              long long q_out_stride, int dtype, int T, int Hq, int Hkv, int hd, long long row_stride,
                               const void* q_norm_w, const void* k_norm_w, int w_dtype, int has_norm, float eps,
                               const float* cos_t, const float* sin_t, int rot, int table_len,
                               const int* tok_pos, const int* tok_seq, const int* block_table, int bt_stride,
                               void* k_cache, void* v_cache, int page_size, int write_kv, void* stream) {
     if (T <= 0) return 0;
-    if (hd > HP_MAX_HD || hd <= 0 || (rot & 1) || rot > hd || rot < 0) return ODIN_ERR_UNSUPPORTED;
+    if (hd > HP_MAX_HD || hd <= 0 || (rot & 1) || rot > hd || rot < 0 || n_split < 1) return ODIN_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const int n_heads = Hq + 2 * Hkv;
     dim3 grid(T, (n_heads + HP_WARPS - 1) / HP_WARPS);
     if (grid.y > 65535) return ODIN_ERR_UNSUPPORTED;
     VecRef qw{q_norm_w, w_dtype == ODIN_BF16}, kw{k_norm_w, w_dtype == ODIN_BF16};
-    if (dtype == ODIN_BF16)
-        head_prep_kernel<bf16><<<grid, HP_WARPS * 32, 0, s>>>(
-            (bf16*)qkv, Hq, Hkv, hd, (size_t)row_stride, qw, kw, has_norm, eps, cos_t, sin_t, rot, table_len,
-            tok_pos, tok_seq, block_table, bt_stride, (bf16*)k_cache, (bf16*)v_cache, page_size, write_kv);
-    else if (dtype == ODIN_F32)
-        head_prep_kernel<float><<<grid, HP_WARPS * 32, 0, s>>>(
-            (float*)qkv, Hq, Hkv, hd, (size_t)row_stride, qw, kw, has_norm, eps, cos_t, sin_t, rot, table_len,
-            tok_pos, tok_seq, block_table, bt_stride, (float*)k_cache, (float*)v_cache, page_size, write_kv);
-    else
-        return ODIN_ERR_UNSUPPORTED;
+#define GO(TI, TT)                                                                                                  \
+    head_prep_kernel<TI, TT><<<grid, HP_WARPS * 32, 0, s>>>(                                                         \
+        (const TI*)qkv, n_split, (size_t)split_stride, (TT*)q_out, (size_t)q_out_stride, Hq, Hkv, hd,               \
+        (size_t)row_stride, qw, kw, has_norm, eps, cos_t, sin_t, rot, table_len, tok_pos, tok_seq, block_table,     \
+        bt_stride, (TT*)k_cache, (TT*)v_cache, page_size, write_kv)
+    if (in_dtype == ODIN_BF16 && dtype == ODIN_BF16) GO(bf16, bf16);
+    else if (in_dtype == ODIN_F32 && dtype == ODIN_F32) GO(float, float);
+    else if (in_dtype == ODIN_F32 && dtype == ODIN_BF16) GO(float, bf16);
+    else return ODIN_ERR_UNSUPPORTED;
+#undef GO
     ODIN_LAUNCH_CHECK();
     return 0;
 }

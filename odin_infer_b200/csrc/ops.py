@@ -113,12 +113,14 @@ def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tenso
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out = silu(gate) * up for gate_up = [T, 2I] (gate columns first)."""
+    """out = silu(gate) * up for gate_up = [T, 2I] (gate columns first), or for the sum of
+    its leading parts when gate_up is [parts, T, 2I] (float32 partial sums of a split product)."""
     T, I = out.shape
-    assert gate_up.shape == (T, 2 * I) and gate_up.dtype == out.dtype
-    assert gate_up.is_contiguous() and out.is_contiguous()
+    assert gate_up.is_contiguous() and out.is_contiguous() and tuple(gate_up.shape[-2:]) == (T, 2 * I)
+    n_split, stride = (gate_up.shape[0], T * 2 * I) if gate_up.dim() == 3 else (1, 0)
     _check(_fn("elementwise", "odin_swiglu")(
-        _ptr(gate_up), _ptr(out), c_int(dtype_code(out.dtype)), c_int(T), c_int(I), _stream()), "swiglu")
+        _ptr(gate_up), c_int(dtype_code(gate_up.dtype)), c_int(n_split), c_longlong(stride), _ptr(out),
+        c_int(dtype_code(out.dtype)), c_int(T), c_int(I), _stream()), "swiglu")
 
 
 def cast(src: torch.Tensor, dst: torch.Tensor) -> None:
@@ -190,10 +192,25 @@ def gemm_tc_check() -> None:
 def head_prep(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, q_norm: torch.Tensor | None,
               k_norm: torch.Tensor | None, eps: float, cos: torch.Tensor, sin: torch.Tensor, rotary_dim: int,
               tok_pos: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
-              k_cache: torch.Tensor | None, v_cache: torch.Tensor | None, write_kv: bool = True) -> None:
-    """Per-head RMSNorm and rotation of q (in place) and k, and the cache write of k and v."""
-    T = qkv.shape[0]
-    assert qkv.stride(1) == 1 and qkv.shape[1] == (n_q + 2 * n_kv) * head_dim
+              k_cache: torch.Tensor | None, v_cache: torch.Tensor | None, write_kv: bool = True,
+              q_out: torch.Tensor | None = None) -> torch.Tensor:
+    """Per-head RMSNorm and rotation of q and k, and the cache write of k and v.
+
+    qkv: [T, (n_q + 2 n_kv) head_dim], or float32 partial sums [parts, T, ...] of a split
+    product (added first).  q goes to q_out ([T, n_q head_dim], of the cache's type); without
+    q_out it is written back into qkv (one part only).  Returns the tensor that holds q."""
+    width = (n_q + 2 * n_kv) * head_dim
+    if qkv.dim() == 3:
+        n_split, T = qkv.shape[0], qkv.shape[1]
+        assert qkv.is_contiguous() and qkv.shape[2] == width
+        split_stride, row_stride = T * width, width
+        assert q_out is not None, "partial sums need a separate q_out"
+    else:
+        n_split, T, split_stride, row_stride = 1, qkv.shape[0], 0, qkv.stride(0)
+        assert qkv.stride(1) == 1 and qkv.shape[1] == width
+    if q_out is None:
+        q_out = qkv[:, : n_q * head_dim]
+    assert q_out.stride(1) == 1 and tuple(q_out.shape) == (T, n_q * head_dim)
     assert cos.dtype == torch.float32 and sin.dtype == torch.float32
     assert tok_pos.dtype == torch.int32 and tok_seq.dtype == torch.int32 and block_table.dtype == torch.int32
     has_norm = q_norm is not None
@@ -202,16 +219,18 @@ def head_prep(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, q_norm: tor
         assert q_norm.numel() == head_dim and k_norm.numel() == head_dim
     if write_kv:
         assert k_cache is not None and v_cache is not None
-        assert k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
+        assert k_cache.dtype == q_out.dtype and v_cache.dtype == q_out.dtype
         assert k_cache.is_contiguous() and v_cache.is_contiguous()
         assert tuple(k_cache.shape[1:]) == (n_kv, PAGE, head_dim), "cache layout is [page][kv head][64][hd]"
     _check(_fn("head_prep", "odin_head_prep")(
-        _ptr(qkv), c_int(dtype_code(qkv.dtype)), c_int(T), c_int(n_q), c_int(n_kv), c_int(head_dim),
-        c_longlong(qkv.stride(0)), _ptr(q_norm), _ptr(k_norm),
+        _ptr(qkv), c_int(dtype_code(qkv.dtype)), c_int(n_split), c_longlong(split_stride), _ptr(q_out),
+        c_longlong(q_out.stride(0)), c_int(dtype_code(q_out.dtype)), c_int(T), c_int(n_q), c_int(n_kv),
+        c_int(head_dim), c_longlong(row_stride), _ptr(q_norm), _ptr(k_norm),
         c_int(dtype_code(q_norm.dtype) if has_norm else 0), c_int(1 if has_norm else 0), c_float(eps),
         _ptr(cos), _ptr(sin), c_int(rotary_dim), c_int(cos.shape[0]), _ptr(tok_pos), _ptr(tok_seq),
         _ptr(block_table), c_int(block_table.stride(0)), _ptr(k_cache), _ptr(v_cache), c_int(PAGE),
         c_int(1 if write_kv else 0), _stream()), "head_prep")
+    return q_out
 
 
 def attention_plain(q: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int, head_dim: int,

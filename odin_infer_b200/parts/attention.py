@@ -69,15 +69,17 @@ class GQAttention(Mixer):
 
     def forward(self, rt, step, h, entry):
         T = h.shape[0]
-        qkv = rt.linear(h, self.w_qkv)
+        qkv = rt.linear(h, self.w_qkv, may_split=True)
         k_line, v_line, block_table = step.kv(entry)
         rot = self.pe.rotation() if self.pe is not None else None
         cos, sin, rot_dim = rot if rot is not None else (self._dummy, self._dummy, 0)
         writes = step.writes_cache(entry) and not self.kv_shared
-        ops.head_prep(qkv, self.n_q, 0 if self.kv_shared else self.n_kv, self.hd,
-                      self.q_norm if self.qk_norm else None, self.k_norm if self.qk_norm else None, self.eps,
-                      cos, sin, rot_dim, step.tok_pos, step.tok_seq, block_table, k_line, v_line, write_kv=writes)
-        q = qkv[:, : self.n_q * self.hd]
+        # a product of few tokens may come back as partial sums: they are added here
+        q_out = rt.empty(T, self.n_q * self.hd) if qkv.dim() == 3 else None
+        q = ops.head_prep(qkv, self.n_q, 0 if self.kv_shared else self.n_kv, self.hd,
+                          self.q_norm if self.qk_norm else None, self.k_norm if self.qk_norm else None, self.eps,
+                          cos, sin, rot_dim, step.tok_pos, step.tok_seq, block_table, k_line, v_line,
+                          write_kv=writes, q_out=q_out)
         o = rt.empty(T, self.n_q * self.hd)
         rt.attention(step, q, o, self.n_q, self.n_kv, self.hd, k_line, v_line, block_table, self.window)
         return rt.linear(o, self.w_o, out_dtype=torch.float32, may_split=True)
