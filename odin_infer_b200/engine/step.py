@@ -39,7 +39,8 @@ class StepBatch:
     Per sequence b: seq_slots[b] (its slot: row of the state area), seq_start[b]
     (first token row; n_seqs + 1 entries), seq_len_after[b] (its length once this step
     is done), and one block table row per cache group.  logit_rows: the token rows
-    whose logits are wanted.
+    whose logits are wanted.  Host copies for parts that size their launches:
+    n_seqs, n_tokens, slots, lengths_after, seq_start_host, all_single, max_new.
     """
 
     def __init__(self, cache, entries: list[StepEntry], start_positions: list[int], device,
@@ -118,6 +119,7 @@ class StepBatch:
             r += n
         self.n_seqs = len(entries)
         self.n_tokens = n_tok
+        self.seq_start_host = [int(v) for v in starts[:len(entries)]] + [n_tok]
         self.n_rows = self.n_row_cap
         self.slots = [e.slot for e in entries]
         self.wanted_rows = rows
