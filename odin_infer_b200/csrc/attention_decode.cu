@@ -289,3 +289,50 @@ extern "C" int odin_attention_decode(const void* q, long long q_row_stride, void
     }
 #undef CALL
 }
+
+// ---------------------------------------------------------------------------
+// The variant that allocates nothing (see attention_decode_noalloc.h).
+// ---------------------------------------------------------------------------
+#include <mutex>
+
+#include "attention_decode_noalloc.h"
+
+// The scratch of the no-allocation entry point.  In host code this name is only a
+// handle for cudaGetSymbolAddress, never a device pointer.
+static __device__ __align__(256) float g_noalloc_scratch[ODIN_NOALLOC_SCRATCH_FLOATS];
+
+extern "C" long long odin_attention_decode_noalloc_need(int B, int Hq, int hd, int n_split) {
+    return odin_attention_decode_scratch(B, Hq, hd, n_split);
+}
+
+extern "C" int odin_attention_decode_noalloc(const void* q, long long q_row_stride, void* out, long long out_row_stride,
+                                             int B, int Hq, int Hkv, int hd, const void* k_cache, const void* v_cache,
+                                             int page_size, const int* tok_pos, const int* tok_seq,
+                                             const int* block_table, int bt_stride, int window, int n_split,
+                                             void* stream) {
+    if (B <= 0) return 0;
+    if (Hq <= 0 || hd <= 0 || n_split < 1) return ODIN_ERR_BAD_ARG;
+    if (odin_attention_decode_scratch(B, Hq, hd, n_split) > (long long)ODIN_NOALLOC_SCRATCH_FLOATS)
+        return ODIN_ERR_TOO_LARGE;
+    // once per device, with that device current: the array's address on this device
+    constexpr int MAX_DEVICES = 64;
+    static float* addr[MAX_DEVICES] = {nullptr};
+    static std::mutex mu;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= MAX_DEVICES) return ODIN_ERR_UNSUPPORTED;
+    float* scratch;
+    {
+        std::lock_guard<std::mutex> g(mu);
+        if (addr[dev] == nullptr) {
+            void* p = nullptr;
+            e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+            if (e != cudaSuccess) return (int)e;
+            addr[dev] = static_cast<float*>(p);
+        }
+        scratch = addr[dev];
+    }
+    return odin_attention_decode(q, q_row_stride, out, out_row_stride, B, Hq, Hkv, hd, k_cache, v_cache, page_size,
+                                 tok_pos, tok_seq, block_table, bt_stride, window, scratch, n_split, stream);
+}
