@@ -16,7 +16,8 @@
 //
 // Scratch: partial results [sequence][query head][split] of head_dim + 2 floats, in
 // memory the caller provides.
-#include "common.cuh"
+#include "attn_common.cuh"
+#include <math_constants.h>
 
 namespace {
 
@@ -54,6 +55,8 @@ attn_decode_kernel(const bf16* __restrict__ q, size_t q_stride, int Hq, int Hkv,
                    float scale_log2, float* __restrict__ part_acc, float* __restrict__ part_ml, int n_split) {
     using GE = Geo<HD>;
     constexpr int EPL = GE::EPL, LPK = GE::LPK, KPI = GE::KPI;
+    pdl_trigger();
+    pdl_wait();
     const int split = blockIdx.x;
     const int g_total = Hq / Hkv;
     const int g_parts = (g_total + G - 1) / G;
@@ -204,10 +207,255 @@ attn_decode_kernel(const bf16* __restrict__ q, size_t q_stride, int Hq, int Hkv,
     }
 }
 
+// ---------------------------------------------------------------------------
+// The tensor-core variant (head sizes 64 and 128, up to 16 query heads per kv head).
+//
+// A CTA of 4 warps takes (sequence, kv head, key split).  The query heads of the kv
+// head are the rows of a 16-row MMA tile.  The split's pages stream through a ring of
+// 3 shared-memory stages by TMA (one page of one kv head is a contiguous [64, hd] tile;
+// 128-byte swizzle); of every page warp w takes keys 16w .. 16w+15: S = Q K^T and
+// O += P V with mma.sync m16n8k16, online softmax in registers.  The four warps' partial
+// results are merged through shared memory, then either written as this split's
+// partial or, with one split, normalised and stored as the result.
+// ---------------------------------------------------------------------------
+struct DecodeTcParams {
+    const bf16* q;
+    size_t q_stride;
+    bf16* out;
+    size_t out_stride;
+    int Hq, Hkv;
+    const int* tok_pos;
+    const int* tok_seq;
+    const int* block_table;
+    int bt_stride;
+    int window;
+    float scale_log2;
+    float* part_acc;
+    float* part_ml;
+    int n_split;
+    int* error;
+};
+
+__device__ __forceinline__ uint32_t q_off(int row, int col) {  // a [16 x HD] tile in 64-column sub-tiles of 2 KB
+    const int sub = col >> 6, chunk = (col & 63) >> 3;
+    return (uint32_t)(sub * 2048 + row * 128 + ((chunk ^ (row & 7)) << 4));
+}
+
+template <int HD>
+__global__ void __launch_bounds__(128)
+attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                      const DecodeTcParams p) {
+    using namespace attn;
+    constexpr int TILE = PAGE_T * HD * 2;
+    constexpr int STAGES = 3;
+    constexpr int KB = HD / 16, NB_O = HD / 8;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sK = smem;                       // STAGES tiles; reused for the warps' merge at the end
+    uint8_t* sV = smem + STAGES * TILE;       // STAGES tiles
+    uint8_t* sQ = smem + 2 * STAGES * TILE;   // 16 x HD
+    uint64_t* full = reinterpret_cast<uint64_t*>(sQ + 16 * HD * 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(full + STAGES);
+    float* s_ml = reinterpret_cast<float*>(full + STAGES + 1);  // [4 warps][16 rows][2]
+
+    const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_trigger();
+    pdl_wait();
+    const int seq = p.tok_seq[t];
+    if (seq < 0) return;  // padding row
+    const int g = p.Hq / p.Hkv, h0 = kvh * g;
+    const int pos = p.tok_pos[t];
+    int first = 0;
+    if (p.window > 0 && pos - p.window + 1 > 0) first = pos - p.window + 1;
+    const int p_first = first / PAGE_T, p_last = pos / PAGE_T;
+    const int per = (p_last - p_first + 1 + p.n_split - 1) / p.n_split;
+    const int pa = p_first + split * per, pb = min(p_last + 1, pa + per);  // pages [pa, pb)
+    const int t_lo = first, t_hi = pos + 1;                               // visible keys [t_lo, t_hi)
+    float* my_acc = p.part_acc + (((size_t)t * p.Hq + h0) * p.n_split + split) * HD;
+    float* my_ml = p.part_ml + (((size_t)t * p.Hq + h0) * p.n_split + split) * 2;
+    const size_t head_step_acc = (size_t)p.n_split * HD, head_step_ml = (size_t)p.n_split * 2;
+    if (pa >= pb) {  // nothing for this split: an empty partial
+        for (int idx = threadIdx.x; idx < g * HD; idx += 128) {
+            const int r = idx / HD, d = idx % HD;
+            my_acc[(size_t)r * head_step_acc + d] = 0.f;
+            if (d == 0) { my_ml[(size_t)r * head_step_ml] = NEG_BIG; my_ml[(size_t)r * head_step_ml + 1] = 0.f; }
+        }
+        return;
+    }
+    const int* bt = p.block_table + (size_t)seq * p.bt_stride;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) tc::mbar_init(&full[s], 1);
+        *abort_flag = 0;
+        tc::fence_barrier_init();
+    }
+    for (int idx = threadIdx.x; idx < 16 * (HD / 8); idx += 128) {
+        const int r = idx / (HD / 8), c = idx % (HD / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < g) v = *reinterpret_cast<const uint4*>(p.q + (size_t)t * p.q_stride + (size_t)(h0 + r) * HD + c * 8);
+        *reinterpret_cast<uint4*>(sQ + q_off(r, c * 8)) = v;
+    }
+    __syncthreads();
+    auto issue = [&](int page_idx, int stage) {
+        const int page = bt[page_idx];
+        const int row = (page * p.Hkv + kvh) * PAGE_T;
+        tc::mbar_expect_tx(&full[stage], 2 * TILE);
+#pragma unroll
+        for (int sub = 0; sub < HD / 64; ++sub) {
+            tc::tma_load_2d(sK + stage * TILE + sub * 8192, &map_k, sub * 64, row, &full[stage]);
+            tc::tma_load_2d(sV + stage * TILE + sub * 8192, &map_v, sub * 64, row, &full[stage]);
+        }
+    };
+    if (threadIdx.x == 0)
+        for (int s = 0; s < STAGES && pa + s < pb; ++s) issue(pa + s, s);
+
+    uint32_t qa[KB][4];
+    const uint32_t sQ_u = tc::smem_u32(sQ);
+#pragma unroll
+    for (int kb = 0; kb < KB; ++kb) ldmatrix_x4(qa[kb], sQ_u + q_off(lane & 15, kb * 16 + (lane >> 4) * 8));
+
+    float o[NB_O][4];
+#pragma unroll
+    for (int i = 0; i < NB_O; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+    float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F}, l_run[2] = {0.f, 0.f};
+
+    bool ok = true;
+    for (int pg = pa; pg < pb; ++pg) {
+        const int it = pg - pa, stage = it % STAGES;
+        const uint32_t phase = (it / STAGES) & 1;
+        if (!tc::mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+        const uint32_t sK_u = tc::smem_u32(sK + stage * TILE), sV_u = tc::smem_u32(sV + stage * TILE);
+        if (pg == p_last) {
+            // slots past the sequence's end may hold a stale Inf or NaN; 0 x NaN is NaN: clear those value rows
+            const int valid = t_hi - pg * PAGE_T;
+            if (valid < PAGE_T) {
+                for (int idx = threadIdx.x; idx < (PAGE_T - valid) * (HD / 8); idx += 128) {
+                    const int r = valid + idx / (HD / 8), c = idx % (HD / 8);
+                    *reinterpret_cast<uint4*>(sV + stage * TILE + tile_off(r, c * 8)) = make_uint4(0, 0, 0, 0);
+                }
+                __syncthreads();
+            }
+        }
+        // S = Q K^T for this warp's 16 keys of the page
+        float s[2][4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+            uint32_t b[4];
+            ldmatrix_x4(b, sK_u + tile_off(warp * 16 + (lane & 7) + ((lane >> 4) << 3), kb * 16 + ((lane >> 3) & 1) * 8));
+            mma_bf16(s[0], qa[kb], b[0], b[1]);
+            mma_bf16(s[1], qa[kb], b[2], b[3]);
+        }
+        const int key0 = pg * PAGE_T + warp * 16 + (lane & 3) * 2;
+        float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int tk = key0 + nb * 8 + (j & 1);
+                float v = s[nb][j] * p.scale_log2;
+                if (tk < t_lo || tk >= t_hi) v = -CUDART_INF_F;
+                s[nb][j] = v;
+                mx[j >> 1] = fmaxf(mx[j >> 1], v);
+            }
+        }
+        float corr[2], m_use[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float m_new = fmaxf(m_run[r], mx[r]);
+            m_use[r] = (m_new == -CUDART_INF_F) ? 0.f : m_new;
+            corr[r] = exp2f(m_run[r] - m_use[r]);
+            m_run[r] = m_new;
+            l_run[r] *= corr[r];
+        }
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float pv = exp2f(s[nb][j] - m_use[j >> 1]);
+                s[nb][j] = pv;
+                l_run[j >> 1] += pv;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NB_O; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0];
+            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+        uint32_t pa_frag[4];
+        pa_frag[0] = pack_bf16(s[0][0], s[0][1]);
+        pa_frag[1] = pack_bf16(s[0][2], s[0][3]);
+        pa_frag[2] = pack_bf16(s[1][0], s[1][1]);
+        pa_frag[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+        for (int nb2 = 0; nb2 < NB_O / 2; ++nb2) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, sV_u + tile_off(warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), nb2 * 16 + (lane >> 4) * 8));
+            mma_bf16(o[2 * nb2], pa_frag, b[0], b[1]);
+            mma_bf16(o[2 * nb2 + 1], pa_frag, b[2], b[3]);
+        }
+        __syncthreads();  // everyone is done with this stage
+        if (threadIdx.x == 0 && pg + STAGES < pb) issue(pg + STAGES, stage);
+    }
+    if (threadIdx.x == 0 && (!ok || *abort_flag) && p.error != nullptr) atomicExch(p.error, 1);
+    if (!ok) return;
+
+    // merge the four warps (each saw a quarter of the keys) through shared memory
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+    float* s_o = reinterpret_cast<float*>(sK);  // [4 warps][16 rows][HD]; no copy is in flight any more
+    const int row_a = lane >> 2, col = (lane & 3) * 2;
+#pragma unroll
+    for (int i = 0; i < NB_O; ++i) {
+        float* dst = s_o + ((size_t)warp * 16 + row_a) * HD + i * 8 + col;
+        dst[0] = o[i][0]; dst[1] = o[i][1];
+        dst[8 * HD] = o[i][2]; dst[8 * HD + 1] = o[i][3];
+    }
+    if ((lane & 3) == 0) {
+        s_ml[(warp * 16 + row_a) * 2] = fmaxf(m_run[0], NEG_BIG);
+        s_ml[(warp * 16 + row_a) * 2 + 1] = l_run[0];
+        s_ml[(warp * 16 + row_a + 8) * 2] = fmaxf(m_run[1], NEG_BIG);
+        s_ml[(warp * 16 + row_a + 8) * 2 + 1] = l_run[1];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < g * HD; idx += 128) {
+        const int r = idx / HD, d = idx % HD;
+        float mm = NEG_BIG;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, s_ml[(w * 16 + r) * 2]);
+        float a = 0.f, ll = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float c = exp2f(s_ml[(w * 16 + r) * 2] - mm);
+            a += s_o[((size_t)w * 16 + r) * HD + d] * c;
+            ll += s_ml[(w * 16 + r) * 2 + 1] * c;
+        }
+        if (p.n_split == 1) {
+            p.out[(size_t)t * p.out_stride + (size_t)(h0 + r) * HD + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
+        } else {
+            my_acc[(size_t)r * head_step_acc + d] = a;
+            if (d == 0) { my_ml[(size_t)r * head_step_ml] = mm; my_ml[(size_t)r * head_step_ml + 1] = ll; }
+        }
+    }
+}
+
 // out[t][h][:] = sum_s w_s acc_s / sum_s w_s l_s, w_s = 2^(m_s - max m)
 __global__ void attn_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml, int n_split,
                                     int hd, bf16* __restrict__ out, size_t out_stride, int Hq,
                                     const int* __restrict__ tok_seq) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x / Hq, h = blockIdx.x % Hq;
     if (tok_seq[t] < 0) return;
     const float* ml = part_ml + ((size_t)t * Hq + h) * n_split * 2;
@@ -234,9 +482,9 @@ int launch_decode(const bf16* q, size_t q_stride, bf16* out, size_t out_stride, 
 #define GO(G)                                                                                                      \
     do {                                                                                                           \
         dim3 grid(n_split, Hkv * ((g + G - 1) / G), B);                                                            \
-        attn_decode_kernel<HD, G><<<grid, AD_WARPS * 32, 0, s>>>(q, q_stride, Hq, Hkv, k_cache, v_cache, page_size, \
-                                                                 tok_pos, tok_seq, block_table, bt_stride, window, \
-                                                                 scale_log2, part_acc, part_ml, n_split);          \
+        odin_launch(attn_decode_kernel<HD, G>, grid, dim3(AD_WARPS * 32), 0, s, q, q_stride, Hq, Hkv, k_cache,      \
+                    v_cache, page_size, tok_pos, tok_seq, block_table, bt_stride, window, scale_log2, part_acc,    \
+                    part_ml, n_split);                                                                             \
     } while (0)
     if (g == 1) GO(1);
     else if (g == 2) GO(2);
@@ -244,9 +492,55 @@ int launch_decode(const bf16* q, size_t q_stride, bf16* out, size_t out_stride, 
     else GO(4);
 #undef GO
     ODIN_LAUNCH_CHECK();
-    attn_combine_kernel<<<B * Hq, HD < 128 ? 32 : 128, 0, s>>>(part_acc, part_ml, n_split, HD, out, out_stride, Hq,
-                                                              tok_seq);
+    odin_launch(attn_combine_kernel, dim3(B * Hq), dim3(HD < 128 ? 32 : 128), 0, s, (const float*)part_acc,
+                (const float*)part_ml, n_split, (int)HD, out, out_stride, Hq, tok_seq);
     ODIN_LAUNCH_CHECK();
+    return 0;
+}
+
+
+int* decode_error_flag() {
+    static int* flag = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        if (cudaMalloc(&flag, sizeof(int)) == cudaSuccess) cudaMemset(flag, 0, sizeof(int));
+        else flag = nullptr;
+    });
+    return flag;
+}
+
+template <int HD>
+int launch_decode_tc(const bf16* q, size_t q_stride, bf16* out, size_t out_stride, int B, int Hq, int Hkv,
+                     const bf16* k_cache, const bf16* v_cache, int n_pages, const int* tok_pos, const int* tok_seq,
+                     const int* block_table, int bt_stride, int window, float* part_acc, float* part_ml, int n_split,
+                     cudaStream_t s) {
+    constexpr int SMEM = 6 * attn::PAGE_T * HD * 2 + 16 * HD * 2 + 64 + 4 * 16 * 2 * 4 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    CUtensorMap mk, mv;
+    int rc;
+    const long long rows = (long long)n_pages * Hkv * attn::PAGE_T;
+    if ((rc = attn::cache_map(&mk, k_cache, rows, HD))) return rc;
+    if ((rc = attn::cache_map(&mv, v_cache, rows, HD))) return rc;
+    DecodeTcParams p;
+    p.q = q; p.q_stride = q_stride; p.out = out; p.out_stride = out_stride;
+    p.Hq = Hq; p.Hkv = Hkv; p.tok_pos = tok_pos; p.tok_seq = tok_seq;
+    p.block_table = block_table; p.bt_stride = bt_stride; p.window = window;
+    p.scale_log2 = 1.4426950408889634f / sqrtf((float)HD);
+    p.part_acc = part_acc; p.part_ml = part_ml; p.n_split = n_split;
+    p.error = decode_error_flag();
+    dim3 grid(n_split, Hkv, B);
+    odin_launch(attn_decode_tc_kernel<HD>, grid, dim3(128), (size_t)SMEM, s, mk, mv, p);
+    ODIN_LAUNCH_CHECK();
+    if (n_split > 1) {
+        odin_launch(attn_combine_kernel, dim3(B * Hq), dim3(128), 0, s, (const float*)part_acc, (const float*)part_ml,
+                    n_split, (int)HD, out, out_stride, Hq, tok_seq);
+        ODIN_LAUNCH_CHECK();
+    }
     return 0;
 }
 
@@ -257,6 +551,15 @@ extern "C" long long odin_attention_decode_scratch(int B, int Hq, int hd, int n_
     return (long long)B * Hq * n_split * (hd + 2);
 }
 
+extern "C" int odin_attention_decode_error() {
+    int* f = decode_error_flag();
+    if (f == nullptr) return 0;
+    int v = 0;
+    if (cudaMemcpy(&v, f, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (v) cudaMemset(f, 0, sizeof(int));
+    return v;
+}
+
 // Does the split kernel take this head size?  (Others go to the plain kernel.)
 extern "C" int odin_attention_decode_supported(int hd) {
     return hd == 16 || hd == 32 || hd == 64 || hd == 128 || hd == 256;
@@ -264,17 +567,29 @@ extern "C" int odin_attention_decode_supported(int hd) {
 
 // One query token per row of q ([B, Hq*hd] bfloat16, row stride q_row_stride); row t
 // belongs to sequence tok_seq[t] (row of the block table; negative: padding, skipped)
-// at position tok_pos[t].  scratch: odin_attention_decode_scratch(...) floats.
+// at position tok_pos[t].  n_pages: pages of the cache line (0: unknown, the tensor-core
+// kernel is then not used).  scratch: odin_attention_decode_scratch(...) floats.
 extern "C" int odin_attention_decode(const void* q, long long q_row_stride, void* out, long long out_row_stride, int B,
                                      int Hq, int Hkv, int hd, const void* k_cache, const void* v_cache, int page_size,
-                                     const int* tok_pos, const int* tok_seq, const int* block_table, int bt_stride,
-                                     int window, float* scratch, int n_split, void* stream) {
+                                     int n_pages, const int* tok_pos, const int* tok_seq, const int* block_table,
+                                     int bt_stride, int window, float* scratch, int n_split, void* stream) {
     if (B <= 0) return 0;
     if (Hkv <= 0 || Hq % Hkv != 0 || n_split < 1 || scratch == nullptr) return ODIN_ERR_BAD_ARG;
     if (B > 65535 || Hq > 65535 || n_split > 65535) return ODIN_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     float* part_acc = scratch;
     float* part_ml = scratch + (size_t)B * Hq * n_split * hd;
+    // head sizes 64 and 128 with at most 16 query heads per kv head: the tensor-core kernel
+    if ((hd == 64 || hd == 128) && Hq / Hkv <= 16 && page_size == attn::PAGE_T && n_pages > 0 &&
+        (q_row_stride % 8) == 0 && (((uintptr_t)q) & 15) == 0) {
+        if (hd == 64)
+            return launch_decode_tc<64>((const bf16*)q, (size_t)q_row_stride, (bf16*)out, (size_t)out_row_stride, B, Hq,
+                                        Hkv, (const bf16*)k_cache, (const bf16*)v_cache, n_pages, tok_pos, tok_seq,
+                                        block_table, bt_stride, window, part_acc, part_ml, n_split, s);
+        return launch_decode_tc<128>((const bf16*)q, (size_t)q_row_stride, (bf16*)out, (size_t)out_row_stride, B, Hq,
+                                     Hkv, (const bf16*)k_cache, (const bf16*)v_cache, n_pages, tok_pos, tok_seq,
+                                     block_table, bt_stride, window, part_acc, part_ml, n_split, s);
+    }
 #define CALL(HD)                                                                                                  \
     return launch_decode<HD>((const bf16*)q, (size_t)q_row_stride, (bf16*)out, (size_t)out_row_stride, B, Hq, Hkv, \
                              (const bf16*)k_cache, (const bf16*)v_cache, page_size, tok_pos, tok_seq, block_table, \
@@ -307,7 +622,7 @@ extern "C" long long odin_attention_decode_noalloc_need(int B, int Hq, int hd, i
 
 extern "C" int odin_attention_decode_noalloc(const void* q, long long q_row_stride, void* out, long long out_row_stride,
                                              int B, int Hq, int Hkv, int hd, const void* k_cache, const void* v_cache,
-                                             int page_size, const int* tok_pos, const int* tok_seq,
+                                             int page_size, int n_pages, const int* tok_pos, const int* tok_seq,
                                              const int* block_table, int bt_stride, int window, int n_split,
                                              void* stream) {
     if (B <= 0) return 0;
@@ -334,5 +649,5 @@ extern "C" int odin_attention_decode_noalloc(const void* q, long long q_row_stri
         scratch = addr[dev];
     }
     return odin_attention_decode(q, q_row_stride, out, out_row_stride, B, Hq, Hkv, hd, k_cache, v_cache, page_size,
-                                 tok_pos, tok_seq, block_table, bt_stride, window, scratch, n_split, stream);
+                                 n_pages, tok_pos, tok_seq, block_table, bt_stride, window, scratch, n_split, stream);
 }

@@ -36,7 +36,7 @@ extern "C" {
 
 int odin_attention_decode_noalloc(const void* q, long long q_row_stride, void* out, long long out_row_stride, int B,
                                   int Hq, int Hkv, int hd, const void* k_cache, const void* v_cache, int page_size,
-                                  const int* tok_pos, const int* tok_seq, const int* block_table, int bt_stride,
+                                  int n_pages, const int* tok_pos, const int* tok_seq, const int* block_table, int bt_stride,
                                   int window, int n_split, void* stream);
 
 /* The number of floats a call with these sizes needs (compare with the maximum above). */

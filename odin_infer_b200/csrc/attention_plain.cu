@@ -56,6 +56,8 @@ attention_plain_kernel(const T* __restrict__ q, size_t q_stride, T* __restrict__
                        int page_size, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                        const int* __restrict__ block_table, int bt_stride, int window) {
     __shared__ float qs[AP_WARPS][AP_MAX_HD];
+    pdl_trigger();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * AP_WARPS + warp;
     if (item >= (long long)T_tok * Hq) return;
@@ -133,11 +135,11 @@ extern "C" int odin_attention_plain(const void* q, long long q_row_stride, void*
     const long long blocks = (items + AP_WARPS - 1) / AP_WARPS;
     if (blocks > 2147483647LL) return ODIN_ERR_UNSUPPORTED;
     if (dtype == ODIN_BF16)
-        attention_plain_kernel<bf16><<<(unsigned)blocks, AP_WARPS * 32, 0, s>>>(
+        odin_launch(attention_plain_kernel<bf16>, dim3((unsigned)blocks), dim3(AP_WARPS * 32), 0, s,
             (const bf16*)q, (size_t)q_row_stride, (bf16*)out, (size_t)out_row_stride, T, Hq, Hkv, hd,
             (const bf16*)k_cache, (const bf16*)v_cache, page_size, tok_pos, tok_seq, block_table, bt_stride, window);
     else if (dtype == ODIN_F32)
-        attention_plain_kernel<float><<<(unsigned)blocks, AP_WARPS * 32, 0, s>>>(
+        odin_launch(attention_plain_kernel<float>, dim3((unsigned)blocks), dim3(AP_WARPS * 32), 0, s,
             (const float*)q, (size_t)q_row_stride, (float*)out, (size_t)out_row_stride, T, Hq, Hkv, hd,
             (const float*)k_cache, (const float*)v_cache, page_size, tok_pos, tok_seq, block_table, bt_stride,
             window);

@@ -62,6 +62,49 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     return t;
 }
 
+// ---------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched through odin_launch may start
+// while the kernel before it on the stream is still running; pdl_wait() blocks until
+// that kernel has completed and its memory is visible.  Rules every kernel here keeps:
+//   * pdl_trigger() first, so the next kernel's CTAs can take their places early;
+//   * pdl_wait() before the first read of anything an earlier kernel wrote and before
+//     the first global write (a buffer may be reused memory that an earlier kernel
+//     still reads); only constant data (weights) may be touched before it;
+//   * every kernel launched this way calls pdl_wait(), so completion stays in stream
+//     order.  Set ODIN_PDL=0 in the environment to launch in plain stream order.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+#include <cstdlib>
+#include <cstring>
+
+static inline bool odin_pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = std::getenv("ODIN_PDL");
+        v = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return v != 0;
+}
+
+template <typename... KArgs, typename... Args>
+static inline void odin_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                               Args&&... args) {
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = odin_pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 #define ODIN_LAUNCH_CHECK()                          \
     do {                                             \
         cudaError_t e__ = cudaGetLastError();        \

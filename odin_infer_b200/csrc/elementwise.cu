@@ -10,6 +10,8 @@
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ out, int d, int V) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     const bool ok = (id >= 0 && id < V);
@@ -24,9 +26,9 @@ extern "C" int odin_embed(const void* table, int table_dtype, const int* ids, fl
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = d >= 1024 ? 256 : 128;
     if (table_dtype == ODIN_BF16)
-        embed_kernel<bf16><<<T, threads, 0, s>>>((const bf16*)table, ids, out, d, V);
+        odin_launch(embed_kernel<bf16>, dim3(T), dim3(threads), 0, s, (const bf16*)table, ids, out, d, V);
     else if (table_dtype == ODIN_F32)
-        embed_kernel<float><<<T, threads, 0, s>>>((const float*)table, ids, out, d, V);
+        odin_launch(embed_kernel<float>, dim3(T), dim3(threads), 0, s, (const float*)table, ids, out, d, V);
     else
         return ODIN_ERR_UNSUPPORTED;
     ODIN_LAUNCH_CHECK();
@@ -67,6 +69,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
                                    const int* __restrict__ rows, int d) {
     __shared__ float red[32];
     extern __shared__ float rowbuf[];  // d floats
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     int src = r;
     if (rows != nullptr) src = rows[r];
@@ -135,8 +139,8 @@ static int launch_add_rmsnorm(float* x, const void* delta, int n_split, size_t s
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;
         }
-        add_rmsnorm_kernel<TD, TO, true><<<n_rows, threads, smem, s>>>(x, (const TD*)delta, n_split, split_stride, w,
-                                                                       eps, (TO*)out, rows, d);
+        odin_launch(add_rmsnorm_kernel<TD, TO, true>, dim3(n_rows), dim3(threads), smem, s, x, (const TD*)delta, n_split,
+                    split_stride, w, eps, (TO*)out, rows, d);
     } else {
         const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
         if (smem > 48 * 1024) {
@@ -144,8 +148,8 @@ static int launch_add_rmsnorm(float* x, const void* delta, int n_split, size_t s
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;
         }
-        add_rmsnorm_kernel<TD, TO, false><<<n_rows, threads, smem, s>>>(x, (const TD*)delta, n_split, split_stride, w,
-                                                                        eps, (TO*)out, rows, d);
+        odin_launch(add_rmsnorm_kernel<TD, TO, false>, dim3(n_rows), dim3(threads), smem, s, x, (const TD*)delta, n_split,
+                    split_stride, w, eps, (TO*)out, rows, d);
     }
     ODIN_LAUNCH_CHECK();
     return 0;
@@ -179,6 +183,8 @@ extern "C" int odin_add_rmsnorm(float* x, const void* delta, int delta_dtype, in
 template <typename TI, typename T>
 __global__ void swiglu_kernel(const TI* __restrict__ gu, int n_split, size_t split_stride, T* __restrict__ out, int I,
                               size_t total) {
+    pdl_trigger();
+    pdl_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I;
@@ -204,14 +210,14 @@ extern "C" int odin_swiglu(const void* gu, int in_dtype, int n_split, long long 
     size_t blocks = (total + threads - 1) / threads;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (in_dtype == ODIN_BF16 && out_dtype == ODIN_BF16)
-        swiglu_kernel<bf16, bf16><<<(int)blocks, threads, 0, s>>>((const bf16*)gu, n_split, (size_t)split_stride,
-                                                                  (bf16*)out, I, total);
+        odin_launch(swiglu_kernel<bf16, bf16>, dim3((int)blocks), dim3(threads), 0, s, (const bf16*)gu, n_split,
+                    (size_t)split_stride, (bf16*)out, I, total);
     else if (in_dtype == ODIN_F32 && out_dtype == ODIN_F32)
-        swiglu_kernel<float, float><<<(int)blocks, threads, 0, s>>>((const float*)gu, n_split, (size_t)split_stride,
-                                                                    (float*)out, I, total);
+        odin_launch(swiglu_kernel<float, float>, dim3((int)blocks), dim3(threads), 0, s, (const float*)gu, n_split,
+                    (size_t)split_stride, (float*)out, I, total);
     else if (in_dtype == ODIN_F32 && out_dtype == ODIN_BF16)
-        swiglu_kernel<float, bf16><<<(int)blocks, threads, 0, s>>>((const float*)gu, n_split, (size_t)split_stride,
-                                                                   (bf16*)out, I, total);
+        odin_launch(swiglu_kernel<float, bf16>, dim3((int)blocks), dim3(threads), 0, s, (const float*)gu, n_split,
+                    (size_t)split_stride, (bf16*)out, I, total);
     else
         return ODIN_ERR_UNSUPPORTED;
     ODIN_LAUNCH_CHECK();
@@ -221,6 +227,8 @@ extern "C" int odin_swiglu(const void* gu, int in_dtype, int n_split, long long 
 // ---------------------------------------------------------------------- cast
 template <typename TI, typename TO>
 __global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
+    pdl_trigger();
+    pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
         out[i] = from_f32<TO>(to_f32(in[i]));
 }
@@ -231,9 +239,9 @@ extern "C" int odin_cast(const void* in, int in_dtype, void* out, int out_dtype,
     size_t blocks = ((size_t)n + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (in_dtype == ODIN_F32 && out_dtype == ODIN_BF16)
-        cast_kernel<float, bf16><<<(int)blocks, 256, 0, s>>>((const float*)in, (bf16*)out, (size_t)n);
+        odin_launch(cast_kernel<float, bf16>, dim3((int)blocks), dim3(256), 0, s, (const float*)in, (bf16*)out, (size_t)n);
     else if (in_dtype == ODIN_BF16 && out_dtype == ODIN_F32)
-        cast_kernel<bf16, float><<<(int)blocks, 256, 0, s>>>((const bf16*)in, (float*)out, (size_t)n);
+        odin_launch(cast_kernel<bf16, float>, dim3((int)blocks), dim3(256), 0, s, (const bf16*)in, (float*)out, (size_t)n);
     else
         return ODIN_ERR_UNSUPPORTED;
     ODIN_LAUNCH_CHECK();

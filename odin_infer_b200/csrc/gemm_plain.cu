@@ -19,6 +19,8 @@ __global__ void __launch_bounds__(256) gemm_plain_kernel(const TA* __restrict__ 
                                                          size_t ldw, size_t ldc) {
     __shared__ float As[TK][TM + 4];
     __shared__ float Ws[TK][TN + 4];
+    pdl_trigger();
+    pdl_wait();
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;
     const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
@@ -76,8 +78,8 @@ extern "C" int odin_gemm_plain(const void* A, int a_dtype, const void* W, int w_
     dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM);
     if (grid.y > 65535) return ODIN_ERR_UNSUPPORTED;
 #define GO(TA, TW, TC)                                                                                     \
-    gemm_plain_kernel<TA, TW, TC><<<grid, 256, 0, s>>>((const TA*)A, (const TW*)W, (TC*)C, M, N, K,       \
-                                                      (size_t)lda, (size_t)ldw, (size_t)ldc)
+    odin_launch(gemm_plain_kernel<TA, TW, TC>, grid, dim3(256), 0, s, (const TA*)A, (const TW*)W, (TC*)C, M, N, K, \
+                (size_t)lda, (size_t)ldw, (size_t)ldc)
     const int key = a_dtype * 4 + w_dtype * 2 + c_dtype;
     switch (key) {
         case 0: GO(float, float, float); break;

@@ -105,6 +105,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_trigger();  // the next kernel may take its place; it waits for this one before it touches memory
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) {
@@ -133,12 +134,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            // Weights are constant: in mode 1 (X = weights) the first stages of the first tile
+            // are requested before the wait for the previous kernel, whose output is only Y.
+            int pre = 0;
+            if (MODE == 1 && (long long)blockIdx.x < n_items) {
+                const long long w = blockIdx.x;
+                const int s = (int)(w % p.n_split);
+                const int tx = (int)((w / p.n_split) % p.tiles_x), ty = (int)((w / p.n_split) / p.tiles_x);
+                const int kb0 = s * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                pre = min(C::STAGES, kb1 - kb0);
+                for (int i = 0; i < pre; ++i) {
+                    tc::mbar_expect_tx(&full[i], C::STAGE);
+                    tc::tma_load_2d(smem + i * C::STAGE, &map_x, (kb0 + i) * BK, tx * BM, &full[i]);
+                }
+                pdl_wait();
+                for (int i = 0; i < pre; ++i)
+                    tc::tma_load_2d(smem + i * C::STAGE + C::STAGE_X, &map_y, (kb0 + i) * BK, ty * BN, &full[i]);
+            } else {
+                pdl_wait();
+            }
             for (long long w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
                 const int s = (int)(w % p.n_split);
                 const long long rest = w / p.n_split;
                 const int tx = (int)(rest % p.tiles_x), ty = (int)(rest / p.tiles_x);
                 const int kb0 = s * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
                 for (int kb = kb0; kb < kb1; ++kb) {
+                    if (pre > 0) {  // already requested above
+                        --pre;
+                        if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                        continue;
+                    }
                     if (!tc::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
                     uint8_t* sx = smem + stage * C::STAGE;
                     uint8_t* sy = sx + C::STAGE_X;
@@ -189,6 +214,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     } else {
         // ------------------------------------------------------------ epilogue
         const int quarter = warp & 3;  // the TMEM lanes this warp may read: [32*quarter, +32)
+        pdl_wait();  // the output may be memory that the previous kernel still reads
         uint32_t local = 0;
         bool ok = true;
         for (long long w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++local) {
@@ -343,7 +369,7 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, cu
     }
     const long long items = (long long)p.tiles_x * p.tiles_y * p.n_split;
     const int grid = (int)(items < sm_count() ? items : sm_count());
-    kern<<<grid, 192, C::SMEM, s>>>(mx, my, p);
+    odin_launch(kern, dim3(grid), dim3(192), (size_t)C::SMEM, s, mx, my, p);
     ODIN_LAUNCH_CHECK();
     return 0;
 }

@@ -26,6 +26,8 @@ head_prep_kernel(const TI* qkv, int n_split, size_t split_stride, T* q_out,  // 
                  const int* __restrict__ block_table, int bt_stride, T* __restrict__ k_cache,
                  T* __restrict__ v_cache, int page_size, int write_kv) {
     __shared__ float buf[HP_WARPS][HP_MAX_HD];
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y * HP_WARPS + warp;
@@ -103,10 +105,10 @@ extern "C" int odin_head_prep(const void* qkv, int in_dtype, int n_split, long l
     if (grid.y > 65535) return ODIN_ERR_UNSUPPORTED;
     VecRef qw{q_norm_w, w_dtype == ODIN_BF16}, kw{k_norm_w, w_dtype == ODIN_BF16};
 #define GO(TI, TT)                                                                                                  \
-    head_prep_kernel<TI, TT><<<grid, HP_WARPS * 32, 0, s>>>(                                                         \
+    odin_launch(head_prep_kernel<TI, TT>, grid, dim3(HP_WARPS * 32), 0, s,                                           \
         (const TI*)qkv, n_split, (size_t)split_stride, (TT*)q_out, (size_t)q_out_stride, Hq, Hkv, hd,               \
         (size_t)row_stride, qw, kw, has_norm, eps, cos_t, sin_t, rot, table_len, tok_pos, tok_seq, block_table,     \
-        bt_stride, (TT*)k_cache, (TT*)v_cache, page_size, write_kv)
+        (int)bt_stride, (TT*)k_cache, (TT*)v_cache, page_size, write_kv)
     if (in_dtype == ODIN_BF16 && dtype == ODIN_BF16) GO(bf16, bf16);
     else if (in_dtype == ODIN_F32 && dtype == ODIN_F32) GO(float, float);
     else if (in_dtype == ODIN_F32 && dtype == ODIN_BF16) GO(float, bf16);

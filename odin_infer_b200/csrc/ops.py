@@ -269,8 +269,16 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int, he
     assert scratch.dtype == torch.float32 and scratch.numel() >= attention_decode_scratch(B, n_q, head_dim, n_split)
     _check(_fn("attention_decode", "odin_attention_decode")(
         _ptr(q), c_longlong(q.stride(0)), _ptr(out), c_longlong(out.stride(0)), c_int(B), c_int(n_q), c_int(n_kv),
-        c_int(head_dim), _ptr(k_cache), _ptr(v_cache), c_int(PAGE), _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table),
-        c_int(block_table.stride(0)), c_int(window), _ptr(scratch), c_int(n_split), _stream()), "attention_decode", kernels=2)
+        c_int(head_dim), _ptr(k_cache), _ptr(v_cache), c_int(PAGE), c_int(k_cache.shape[0]), _ptr(tok_pos),
+        _ptr(tok_seq), _ptr(block_table), c_int(block_table.stride(0)), c_int(window), _ptr(scratch), c_int(n_split),
+        _stream()), "attention_decode", kernels=2 if n_split > 1 or head_dim not in (64, 128) else 1)
+
+
+def attention_decode_check() -> None:
+    f = build.load("attention_decode").odin_attention_decode_error
+    f.restype = c_int
+    if f() != 0:
+        raise KernelError("attention_decode: a device-side wait ran out; results are invalid")
 
 
 def attention_prefill_supported(head_dim: int) -> bool:

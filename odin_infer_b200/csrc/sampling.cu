@@ -22,6 +22,8 @@ __global__ void __launch_bounds__(SB) argmax_kernel(const float* __restrict__ lo
                                                     int* __restrict__ out) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    pdl_trigger();
+    pdl_wait();
     const float* row = logits + (size_t)blockIdx.x * ld;
     float best = -CUDART_INF_F;
     int bi = 0x7fffffff;
@@ -55,7 +57,7 @@ __global__ void __launch_bounds__(SB) argmax_kernel(const float* __restrict__ lo
 extern "C" int odin_argmax(const float* logits, long long ld, int B, int V, int* out, void* stream) {
     if (B <= 0) return 0;
     if (V <= 0) return ODIN_ERR_BAD_ARG;
-    argmax_kernel<<<B, SB, 0, (cudaStream_t)stream>>>(logits, (size_t)ld, V, out);
+    odin_launch(argmax_kernel, dim3(B), dim3(SB), 0, (cudaStream_t)stream, logits, (size_t)ld, V, out);
     ODIN_LAUNCH_CHECK();
     return 0;
 }
@@ -87,6 +89,8 @@ __global__ void __launch_bounds__(SB) sample_kernel(const float* __restrict__ lo
     __shared__ float red[32];
     __shared__ float chunk_sum[SB];
     __shared__ int chosen;
+    pdl_trigger();
+    pdl_wait();
     const float* row = logits + (size_t)blockIdx.x * ld;
     const float inv_t = 1.0f / temperature;
     float mx = -CUDART_INF_F;
@@ -170,7 +174,7 @@ extern "C" int odin_sample(const float* logits, long long ld, int B, int V, floa
                            const float* coins, int* out, void* stream) {
     if (B <= 0) return 0;
     if (V <= 0 || !(temperature > 0.f)) return ODIN_ERR_BAD_ARG;
-    sample_kernel<<<B, SB, 0, (cudaStream_t)stream>>>(logits, (size_t)ld, V, temperature, top_p, coins, out);
+    odin_launch(sample_kernel, dim3(B), dim3(SB), 0, (cudaStream_t)stream, logits, (size_t)ld, V, temperature, top_p, coins, out);
     ODIN_LAUNCH_CHECK();
     return 0;
 }
@@ -180,6 +184,8 @@ extern "C" int odin_sample(const float* logits, long long ld, int B, int V, floa
 // caller passes a copy).
 __global__ void repetition_penalty_kernel(float* __restrict__ logits, size_t ld, int V,
                                           const int* __restrict__ recent, int W, float penalty) {
+    pdl_trigger();
+    pdl_wait();
     float* row = logits + (size_t)blockIdx.x * ld;
     const int* rec = recent + (size_t)blockIdx.x * W;
     for (int j = threadIdx.x; j < W; j += blockDim.x) {
@@ -196,7 +202,7 @@ __global__ void repetition_penalty_kernel(float* __restrict__ logits, size_t ld,
 extern "C" int odin_repetition_penalty(float* logits, long long ld, int B, int V, const int* recent, int W,
                                        float penalty, void* stream) {
     if (B <= 0 || W <= 0) return 0;
-    repetition_penalty_kernel<<<B, 128, 0, (cudaStream_t)stream>>>(logits, (size_t)ld, V, recent, W, penalty);
+    odin_launch(repetition_penalty_kernel, dim3(B), dim3(128), 0, (cudaStream_t)stream, logits, (size_t)ld, V, recent, W, penalty);
     ODIN_LAUNCH_CHECK();
     return 0;
 }

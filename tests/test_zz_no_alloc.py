@@ -60,7 +60,7 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice():
         before = torch.cuda.memory_allocated()
         rc = fn(c_void_p(q.data_ptr()), c_longlong(q.stride(0)), c_void_p(out.data_ptr()), c_longlong(out.stride(0)),
                 c_int(B), c_int(n_q), c_int(n_kv), c_int(hd), c_void_p(k.data_ptr()), c_void_p(v.data_ptr()),
-                c_int(PAGE), c_void_p(tok_pos.data_ptr()), c_void_p(tok_seq.data_ptr()), c_void_p(bt.data_ptr()),
+                c_int(PAGE), c_int(k.shape[0]), c_void_p(tok_pos.data_ptr()), c_void_p(tok_seq.data_ptr()), c_void_p(bt.data_ptr()),
                 c_int(bt.stride(0)), c_int(0), c_int(n_split), stream)
         assert rc == 0, f"call {call}: error code {rc}"
         torch.cuda.synchronize()
@@ -73,7 +73,7 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice():
     assert need(c_int(B_big), c_int(64), c_int(128), c_int(16)) > (1 << 20)
     marker = torch.full((4,), 3.0, device=DEV)
     rc = fn(c_void_p(marker.data_ptr()), c_longlong(0), c_void_p(marker.data_ptr()), c_longlong(0), c_int(B_big),
-            c_int(64), c_int(8), c_int(128), c_void_p(0), c_void_p(0), c_int(PAGE), c_void_p(0), c_void_p(0),
+            c_int(64), c_int(8), c_int(128), c_void_p(0), c_void_p(0), c_int(PAGE), c_int(0), c_void_p(0), c_void_p(0),
             c_void_p(0), c_int(0), c_int(0), c_int(16), stream)
     assert rc == -4
     torch.cuda.synchronize()
