@@ -42,16 +42,22 @@ struct GemmParams {
     int K;
     int tiles_x, tiles_y;
     int n_split, kb_per_split, kb_total;
+    int dual_offset;       // DUAL: first row of the second Y tile's matrix half
     int* error;            // set when a wait runs out
 };
 
-template <int BN>
+// DUAL: two Y tiles per stage (rows [j, j+BN) and [dual_offset + j, dual_offset + j + BN) of Y) and
+// two accumulators side by side, for the gate and up halves of a fused SwiGLU matrix.
+template <int BN, bool DUAL = false>
 struct Cfg {
+    static constexpr int NY = DUAL ? 2 : 1;
+    static constexpr int ACC_W = NY * BN;  // accumulator columns per buffer
     static constexpr int STAGE_X = BM * BK * 2;
-    static constexpr int STAGE_Y = BN * BK * 2;
+    static constexpr int STAGE_Y1 = BN * BK * 2;
+    static constexpr int STAGE_Y = NY * STAGE_Y1;
     static constexpr int STAGE = STAGE_X + STAGE_Y;
     static constexpr int STAGES = (196608 / STAGE) > 10 ? 10 : (196608 / STAGE);
-    static constexpr int TMEM_COLS = (ACC_BUFS * BN) < 32 ? 32 : (ACC_BUFS * BN);
+    static constexpr int TMEM_COLS = (ACC_BUFS * ACC_W) < 32 ? 32 : (ACC_BUFS * ACC_W);
     static constexpr int SMEM = STAGES * STAGE + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
@@ -89,11 +95,12 @@ __device__ __forceinline__ void store_vec<bf16>(bf16* dst, const uint32_t* r, in
     }
 }
 
-template <int BN, int MODE, typename TO>
+template <int BN, int MODE, typename TO, bool DUAL = false>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                const GemmParams p) {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, DUAL>;
+    static_assert(!DUAL || MODE == 0, "the SwiGLU epilogue exists for mode 0 only");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE);
@@ -170,6 +177,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     tc::mbar_expect_tx(&full[stage], C::STAGE);
                     tc::tma_load_2d(sx, &map_x, kb * BK, tx * BM, &full[stage]);
                     tc::tma_load_2d(sy, &map_y, kb * BK, ty * BN, &full[stage]);
+                    if (DUAL) tc::tma_load_2d(sy + C::STAGE_Y1, &map_y, kb * BK, p.dual_offset + ty * BN, &full[stage]);
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -193,7 +201,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 const uint32_t acc = local % ACC_BUFS, acc_phase = (local / ACC_BUFS) & 1;
                 if (!tc::mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
                 tc::fence_after_sync();
-                const uint32_t tmem_d = tmem_base + acc * BN;
+                const uint32_t tmem_d = tmem_base + acc * C::ACC_W;
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!tc::mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
                     tc::fence_after_sync();
@@ -204,6 +212,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         // +32 bytes per K step inside the 128-byte swizzle row: +2 in 16-byte units
                         tc::umma_bf16(tmem_d, dx + 2 * k, dy + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                    }
+                    if (DUAL) {
+                        const uint64_t dy2 = tc::make_smem_desc_sw128(ax + C::STAGE_X + C::STAGE_Y1);
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k)
+                            tc::umma_bf16(tmem_d + BN, dx + 2 * k, dy2 + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     }
                     tc::umma_commit(&empty[stage]);
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
@@ -230,8 +244,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += CH) {
                 uint32_t r[32];
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + c0;
-                if (CH == 32) {
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * C::ACC_W + c0;
+                if (DUAL) {
+                    // h = gate * sigmoid(gate) * up (infer/forward.odin:128-133), both halves from TMEM
+                    uint32_t u[32];
+                    tc::tmem_ld32(taddr, r);
+                    tc::tmem_ld32(taddr + BN, u);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int q = 0; q < 32; ++q) {
+                        float g = __uint_as_float(r[q]);
+                        g *= 1.0f / (1.0f + __expf(-g));
+                        r[q] = __float_as_uint(g * __uint_as_float(u[q]));
+                    }
+                } else if (CH == 32) {
                     tc::tmem_ld32(taddr, r);
                 } else {
                     uint32_t r16[16];
@@ -357,10 +383,10 @@ int sm_count() {
     return n;
 }
 
-template <int BN, int MODE, typename TO>
+template <int BN, int MODE, typename TO, bool DUAL = false>
 int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, cudaStream_t s) {
-    using C = Cfg<BN>;
-    auto kern = gemm_tc_kernel<BN, MODE, TO>;
+    using C = Cfg<BN, DUAL>;
+    auto kern = gemm_tc_kernel<BN, MODE, TO, DUAL>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
@@ -411,6 +437,7 @@ extern "C" int odin_gemm_tc(const void* A, const void* W, void* C, int c_dtype, 
     p.kb_per_split = (p.kb_total + n_split - 1) / n_split;
     if ((p.kb_total + p.kb_per_split - 1) / p.kb_per_split != n_split) return ODIN_ERR_BAD_ARG;  // an empty part
     p.n_split = n_split;
+    p.dual_offset = 0;
     p.error = error_flag();
     CUtensorMap mx, my;
     int rc;
@@ -431,6 +458,39 @@ extern "C" int odin_gemm_tc(const void* A, const void* W, void* C, int c_dtype, 
         return mode == 0 ? dispatch_bn<0, float>(bn, mx, my, p, s) : dispatch_bn<1, float>(bn, mx, my, p, s);
     if (c_dtype == ODIN_BF16)
         return mode == 0 ? dispatch_bn<0, bf16>(bn, mx, my, p, s) : dispatch_bn<1, bf16>(bn, mx, my, p, s);
+    return ODIN_ERR_UNSUPPORTED;
+}
+
+// C[M, I] = silu(A Wg^T) * (A Wu^T) for W = [Wg; Wu] of shape [2 I, K]: the gate and up products
+// accumulate side by side in tensor memory and the SwiGLU is applied as they are read back, so
+// the [M, 2 I] intermediate never exists.  For many tokens (mode 0, tiles of 128 output columns).
+extern "C" int odin_gemm_tc_swiglu(const void* A, const void* W, void* C, int c_dtype, int M, int I, int K,
+                                   long long lda, long long ldw, long long ldc, void* stream) {
+    if (M <= 0 || I <= 0) return 0;
+    if (K <= 0) return ODIN_ERR_BAD_ARG;
+    if ((lda % 8) || (ldw % 8) || (K % 8) || (((uintptr_t)A) & 15) || (((uintptr_t)W) & 15)) return ODIN_ERR_UNSUPPORTED;
+    constexpr int BN = 128;
+    GemmParams p;
+    p.out = C;
+    p.ldc = ldc;
+    p.split_stride = 0;
+    p.K = K;
+    p.kb_total = (K + BK - 1) / BK;
+    p.kb_per_split = p.kb_total;
+    p.n_split = 1;
+    p.dual_offset = I;
+    p.error = error_flag();
+    p.rows_x = M;
+    p.rows_y = I;
+    CUtensorMap mx, my;
+    int rc;
+    if ((rc = make_map(&mx, A, M, K, lda, BM))) return rc;
+    if ((rc = make_map(&my, W, 2LL * I, K, ldw, BN))) return rc;
+    p.tiles_x = (M + BM - 1) / BM;
+    p.tiles_y = (I + BN - 1) / BN;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (c_dtype == ODIN_BF16) return launch<BN, 0, bf16, true>(mx, my, p, s);
+    if (c_dtype == ODIN_F32) return launch<BN, 0, float, true>(mx, my, p, s);
     return ODIN_ERR_UNSUPPORTED;
 }
 

@@ -181,6 +181,19 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, bn: 
         c_longlong(stride), _stream()), "gemm_tc")
 
 
+def gemm_tc_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, I] = silu(a Wg^T) * (a Wu^T) for w_gate_up = [Wg; Wu] ([2 I, K]) in one tcgen05 kernel."""
+    M, K = a.shape
+    I = out.shape[1]
+    if not gemm_tc_supported(a, w_gate_up):
+        raise KernelError("gemm_tc_swiglu: operands must be bfloat16 with 16-byte aligned rows")
+    assert w_gate_up.shape == (2 * I, K) and out.shape[0] == M and out.stride(1) == 1
+    _check(_fn("gemm_tc", "odin_gemm_tc_swiglu")(
+        _ptr(a), _ptr(w_gate_up), _ptr(out), c_int(dtype_code(out.dtype)), c_int(M), c_int(I), c_int(K),
+        c_longlong(a.stride(0)), c_longlong(w_gate_up.stride(0)), c_longlong(out.stride(0)), _stream()),
+        "gemm_tc_swiglu")
+
+
 def gemm_tc_check() -> None:
     """Raise if a tensor-core kernel gave up a bounded wait since the last check (synchronises)."""
     f = build.load("gemm_tc").odin_gemm_tc_error

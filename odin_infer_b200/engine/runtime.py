@@ -76,6 +76,18 @@ class Runtime:
         ops.gemm_plain(a, w, out)
         return out
 
+    def gated_linear(self, a: torch.Tensor, w_gate_up: torch.Tensor, inner: int) -> torch.Tensor:
+        """silu(a Wg^T) * (a Wu^T) for w_gate_up = [Wg; Wu]: one kernel with the SwiGLU in its
+        epilogue for many bfloat16 tokens, else the product followed by the SwiGLU kernel
+        (which also adds the partial sums of a split product)."""
+        M = a.shape[0]
+        act = self.empty(M, inner)
+        if M > 128 and ops.gemm_tc_supported(a, w_gate_up):
+            ops.gemm_tc_swiglu(a, w_gate_up, act)
+            return act
+        ops.swiglu(self.linear(a, w_gate_up, may_split=True), act)
+        return act
+
     # ---- attention over the cache ---------------------------------------
     def attention(self, step, q, out, n_q, n_kv, head_dim, k_line, v_line, block_table, window) -> None:
         """bfloat16: one token per sequence goes to the split-key kernel, prompts (and pieces

@@ -33,7 +33,5 @@ class SwiGLU(FeedForward):
         return {"elementwise", "gemm_plain"}
 
     def forward(self, rt, step, h):
-        gu = rt.linear(h, self.w_gate_up, may_split=True)
-        act = rt.empty(h.shape[0], self.inner)
-        ops.swiglu(gu, act)
+        act = rt.gated_linear(h, self.w_gate_up, self.inner)
         return rt.linear(act, self.w_down, out_dtype=torch.float32, may_split=True)

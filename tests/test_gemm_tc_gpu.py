@@ -99,3 +99,28 @@ def test_refuses_what_it_cannot_do():
     assert not ops.gemm_tc_supported(a, w)
     with pytest.raises(ops.KernelError):
         ops.gemm_tc(a, w, torch.empty(4, 16, device=DEV, dtype=torch.bfloat16), 1, 16)
+
+
+@pytest.mark.parametrize("shape", [(129, 128, 64), (300, 200, 96), (2048, 1024, 512), (500, 333 * 8, 72)])
+def test_fused_swiglu_product(shape):
+    """The gate and up products with the SwiGLU in the epilogue against the two-step computation."""
+    from odin_infer_b200.csrc import ops
+    M, I, K = shape
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    w = (torch.randn(2 * I, K, device=DEV) / math.sqrt(K)).bfloat16()
+    out = torch.full((M, I), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops.gemm_tc_swiglu(a, w, out)
+    ops.gemm_tc_check()
+    g = a.double() @ w[:I].double().t()
+    u = a.double() @ w[I:].double().t()
+    close(out, g * torch.sigmoid(g) * u, 6e-3, "fused swiglu")
+    # structured: gate rows all equal, up rows count the column: out = silu(c) * j-dependent value
+    w2 = torch.zeros(2 * I, K, device=DEV)
+    w2[:I, 0] = 1.0
+    w2[I:, 1] = torch.arange(I, device=DEV, dtype=torch.float32) % 13
+    a2 = torch.zeros(M, K, device=DEV)
+    a2[:, 0] = 2.0
+    a2[:, 1] = (torch.arange(M, device=DEV) % 5).float()
+    ops.gemm_tc_swiglu(a2.bfloat16(), w2.bfloat16(), out)
+    ref = (2.0 * torch.sigmoid(torch.tensor(2.0))).item() * (a2[:, 1:2].double() * w2[I:, 1].double()[None, :])
+    close(out, ref, 5e-3, "fused swiglu structured")
