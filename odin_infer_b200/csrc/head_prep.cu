@@ -88,6 +88,118 @@ head_prep_kernel(const TI* qkv, int n_split, size_t split_stride, T* q_out,  // 
     }
 }
 
+
+// The common case with a bfloat16 cache (full rotary, head size 64 or 128): each lane holds
+// VEC = hd/32 consecutive elements in registers, the rotation partner (i +- hd/2) lives in
+// lane ^ 16, and rows move with vector loads and stores.  The input is bfloat16, or 32-bit
+// partial sums of a split product that are added first, in order.  Same arithmetic as above.
+template <int VEC>
+__device__ __forceinline__ void load_vec(const bf16* p, float (&v)[VEC]) {
+    if (VEC == 4) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        v[0] = a.x; v[1] = a.y; v[2 % VEC] = b.x; v[3 % VEC] = b.y;
+    } else {
+        const uint32_t raw = *reinterpret_cast<const uint32_t*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw));
+        v[0] = a.x; v[1] = a.y;
+    }
+}
+template <int VEC>
+__device__ __forceinline__ void load_vec(const float* p, float (&v)[VEC]) {
+    if (VEC == 4) {
+        const float4 a = *reinterpret_cast<const float4*>(p);
+        v[0] = a.x; v[1] = a.y; v[2 % VEC] = a.z; v[3 % VEC] = a.w;
+    } else {
+        const float2 a = *reinterpret_cast<const float2*>(p);
+        v[0] = a.x; v[1] = a.y;
+    }
+}
+template <int VEC>
+__device__ __forceinline__ void store_vec_bf16(bf16* p, const float (&o)[VEC]) {
+    if (VEC == 4) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(o[0], o[1]), b = __floats2bfloat162_rn(o[2 % VEC], o[3 % VEC]);
+        uint2 u;
+        u.x = *reinterpret_cast<uint32_t*>(&a);
+        u.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = u;
+    } else {
+        __nv_bfloat162 a = __floats2bfloat162_rn(o[0], o[1]);
+        *reinterpret_cast<uint32_t*>(p) = *reinterpret_cast<uint32_t*>(&a);
+    }
+}
+
+template <int VEC, typename TI>
+__global__ void __launch_bounds__(HP_WARPS * 32)
+head_prep_fast_kernel(const TI* qkv, int n_split, size_t split_stride, bf16* q_out, size_t q_out_stride, int Hq,
+                      int Hkv, size_t row_stride, VecRef qw, VecRef kw, int has_norm, float eps,
+                      const float* __restrict__ cos_t, const float* __restrict__ sin_t, int table_len,
+                      const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                      const int* __restrict__ block_table, int bt_stride, bf16* __restrict__ k_cache,
+                      bf16* __restrict__ v_cache, int page_size, int write_kv) {
+    constexpr int HD = VEC * 32, HALF = HD / 2;
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.y * HP_WARPS + warp;
+    if (head >= Hq + 2 * Hkv) return;
+    const int seq = tok_seq[t];
+    if (seq < 0) return;
+    const int pos = tok_pos[t];
+    const bool is_q = head < Hq;
+    const bool is_k = !is_q && head < Hq + Hkv;
+    if (!is_q && !write_kv) return;
+    const int kvh = is_q ? 0 : (is_k ? head - Hq : head - Hq - Hkv);
+    const TI* src = qkv + (size_t)t * row_stride + (size_t)head * HD + lane * VEC;
+    bf16* dst = q_out + (size_t)t * q_out_stride + (size_t)head * HD + lane * VEC;
+    if (!is_q) {
+        const int page = block_table[(size_t)seq * bt_stride + pos / page_size];
+        if (page < 0) return;
+        dst = (is_k ? k_cache : v_cache) + (((size_t)page * Hkv + kvh) * page_size + (pos % page_size)) * HD + lane * VEC;
+    }
+    float v[VEC];
+    load_vec<VEC>(src, v);
+    for (int sp = 1; sp < n_split; ++sp) {
+        float w2[VEC];
+        load_vec<VEC>(src + (size_t)sp * split_stride, w2);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) v[e] += w2[e];
+    }
+    if (!is_q && !is_k) {  // value head: stored as it is
+        store_vec_bf16<VEC>(dst, v);
+        return;
+    }
+    if (has_norm) {
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) ss += v[e] * v[e];
+        ss = warp_sum(ss);
+        ss /= (float)HD;
+        ss += eps;
+        const float r = 1.0f / sqrtf(ss);
+        const VecRef& w = is_q ? qw : kw;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) v[e] = w.at(lane * VEC + e) * (r * v[e]);
+    }
+    float o[VEC];
+    const bool in_table = (pos >= 0 && pos < table_len);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[e], 16);
+        if (in_table) {
+            const int i = (lane & 15) * VEC + e;
+            const float c = cos_t[(size_t)pos * HALF + i], sn = sin_t[(size_t)pos * HALF + i];
+            // first half: x c - y s with (x, y) = (mine, other); second half: x s + y c with (x, y) = (other, mine)
+            o[e] = (lane < 16) ? (v[e] * c - other * sn) : (other * sn + v[e] * c);
+        } else {
+            o[e] = v[e];
+        }
+    }
+    store_vec_bf16<VEC>(dst, o);
+}
+
 // qkv: [n_split][T, (Hq + 2 Hkv) hd] of in_dtype (row stride row_stride, parts split_stride
 // elements apart).  q_out: [T, Hq hd] of dtype (row stride q_out_stride); it may be qkv
 // itself when there is one part of the same type (q is then normalised and rotated in place).
@@ -104,6 +216,22 @@ extern "C" int odin_head_prep(const void* qkv, int in_dtype, int n_split, long l
     dim3 grid(T, (n_heads + HP_WARPS - 1) / HP_WARPS);
     if (grid.y > 65535) return ODIN_ERR_UNSUPPORTED;
     VecRef qw{q_norm_w, w_dtype == ODIN_BF16}, kw{k_norm_w, w_dtype == ODIN_BF16};
+    const bool fast_in = (in_dtype == ODIN_BF16 && n_split == 1) || in_dtype == ODIN_F32;
+    if (fast_in && dtype == ODIN_BF16 && rot == hd && (hd == 64 || hd == 128) && (row_stride % 4) == 0 &&
+        (split_stride % 4) == 0 && (q_out_stride % 4) == 0 && ((((uintptr_t)qkv) | ((uintptr_t)q_out)) & 15) == 0) {
+#define FAST(VEC, TI)                                                                                              \
+    odin_launch(head_prep_fast_kernel<VEC, TI>, grid, dim3(HP_WARPS * 32), 0, s, (const TI*)qkv, n_split,           \
+                (size_t)split_stride, (bf16*)q_out, (size_t)q_out_stride, Hq, Hkv, (size_t)row_stride, qw, kw,     \
+                has_norm, eps, cos_t, sin_t, table_len, tok_pos, tok_seq, block_table, bt_stride, (bf16*)k_cache,  \
+                (bf16*)v_cache, page_size, write_kv)
+        if (hd == 128 && in_dtype == ODIN_BF16) FAST(4, bf16);
+        else if (hd == 128) FAST(4, float);
+        else if (in_dtype == ODIN_BF16) FAST(2, bf16);
+        else FAST(2, float);
+#undef FAST
+        ODIN_LAUNCH_CHECK();
+        return 0;
+    }
 #define GO(TI, TT)                                                                                                  \
     odin_launch(head_prep_kernel<TI, TT>, grid, dim3(HP_WARPS * 32), 0, s,                                           \
         (const TI*)qkv, n_split, (size_t)split_stride, (TT*)q_out, (size_t)q_out_stride, Hq, Hkv, hd,               \
