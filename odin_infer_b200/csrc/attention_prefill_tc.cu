@@ -1,0 +1,391 @@
+// Causal grouped-query attention of prompts on the 5th-generation tensor cores.
+//
+// A CTA of 320 threads takes 128 consecutive query tokens of one sequence and one
+// query head and walks over the sequence's cache pages (64 keys each):
+//   warp 0      TMA producer: K and V page tiles, two stages;
+//   warp 1      allocates tensor memory and issues the MMAs (one thread):
+//               S = Q K^T (tcgen05.mma M128 N64, K and Q both K-major), then
+//               O += P V (M128 N=head_dim, P read from tensor memory, V MN-major exactly
+//               as the cache stores it), accumulators S and O in TMEM;
+//   warps 2..9  two threads per query row (32 keys of the page each; the row maximum is
+//               exchanged through shared memory): read S from TMEM, mask, online
+//               softmax in 32-bit registers (exponentials as ex2 of one fused
+//               multiply-add), write P as packed bfloat16 back into the columns of the S
+//               buffer just read, rescale O in TMEM only when the row maximum ran ahead
+//               of the scaling maximum by more than 2^8, and at the end normalise and store.
+// S has two buffers in TMEM and K and V have barriers of their own, so the scores of the
+// next two pages are computed while the softmax of the current one runs; two CTAs share
+// an SM (96 KB of shared memory and 256 TMEM columns each) and fill each other's gaps.
+//
+// Arithmetic as infer/forward.odin:88-115 (scale 1/sqrt(hd), causal bound t <= pos,
+// maximum-subtracted softmax, weighted sum of values), in 32-bit except the bfloat16
+// operands of the two products.  Every wait is bounded.
+#include "attn_common.cuh"
+#include <math_constants.h>
+
+namespace {
+
+using namespace attn;
+
+constexpr int BQT = 128;  // query rows per CTA
+
+struct PrefillTcParams {
+    const bf16* q;
+    size_t q_stride;
+    bf16* out;
+    size_t out_stride;
+    int Hq, Hkv;
+    const int* seq_start;
+    const int* seq_len_after;
+    const int* block_table;
+    int bt_stride;
+    int window;
+    float scale_log2;
+    int* error;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// How far (in powers of two) a row's maximum may run ahead of the one its sums are scaled
+// by before the accumulated O is rescaled.  Probabilities then reach at most 2^8, which
+// bfloat16 and the 32-bit sums hold without loss; most pages need no rescaling at all.
+constexpr float RESCALE_LAG = 8.0f;
+
+template <int HD>
+__global__ void __launch_bounds__(320, 2)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       const PrefillTcParams p) {
+    constexpr int NSUB = HD / 64;                 // 64-column sub-tiles of a row of head_dim
+    constexpr int Q_SUB = BQT * 128;              // bytes of one [128 x 64] sub-tile of Q
+    constexpr int KV_SUB = PAGE_T * 128;          // bytes of one [64 x 64] sub-tile of K or V
+    constexpr int KV_TILE = NSUB * KV_SUB;
+    constexpr int TMEM_COLS = (128 + HD) <= 256 ? 256 : 512;
+    constexpr uint32_t S_COL = 0, O_COL = 128;    // S has two buffers of 64 columns
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sQ = smem;
+    uint8_t* sK = sQ + NSUB * Q_SUB;      // 2 stages
+    uint8_t* sV = sK + 2 * KV_TILE;       // 2 stages
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * KV_TILE);
+    uint64_t* k_full = bars;           // [2] K page landed
+    uint64_t* k_empty = bars + 2;      // [2] the S product that read it is done
+    uint64_t* v_full = bars + 4;       // [2]
+    uint64_t* v_empty = bars + 6;      // [2] the P V product that read it is done
+    uint64_t* s_full = bars + 8;       // [2] scores complete in S buffer b
+    uint64_t* p_full = bars + 10;      // P written over the S buffer, O rescaled if need be
+    uint64_t* pv_done = bars + 11;     // P V complete: O is stable
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* s_max = reinterpret_cast<float*>(bars + 14);  // [2 buffers][2 halves][128 rows]: the pair's exchange
+
+    pdl_trigger();
+    pdl_wait();
+    if ((uint32_t)(smem - smem_raw) > 896u) {  // the shared-memory window is less aligned than assumed
+        if (threadIdx.x == 0 && p.error != nullptr) atomicExch(p.error, 2);
+        return;
+    }
+    // grid (heads, sequences, tiles): the tile number is the slowest index and runs backwards,
+    // so every head's heaviest (latest) tiles start first and the light ones fill the end
+    const int seq = blockIdx.y, h = blockIdx.x;
+    const int tok0 = p.seq_start[seq], n_new = p.seq_start[seq + 1] - tok0;
+    const int n_tiles = (n_new + BQT - 1) / BQT;
+    const int tile = (int)gridDim.z - 1 - (int)blockIdx.z;
+    if (tile >= n_tiles) return;
+    const int q0 = tile * BQT;
+    const int rows = min(BQT, n_new - q0);
+    const int len_after = p.seq_len_after[seq];
+    const int pos0 = len_after - n_new + q0;
+    const int kvh = h / (p.Hq / p.Hkv);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    int first_key = 0;
+    if (p.window > 0 && pos0 - p.window + 1 > 0) first_key = pos0 - p.window + 1;
+    const int page_a = first_key / PAGE_T, page_b = (pos0 + rows - 1) / PAGE_T;  // inclusive
+    const int n_pages = page_b - page_a + 1;
+    const int* bt = p.block_table + (size_t)seq * p.bt_stride;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 10; ++i) tc::mbar_init(&bars[i], 1);
+        tc::mbar_init(p_full, 8);   // one arrival per softmax warp
+        tc::mbar_init(pv_done, 1);
+        *abort_flag = 0;
+        tc::fence_barrier_init();
+    }
+    if (warp == 1) tc::tmem_alloc(tmem_slot, TMEM_COLS);
+    // Q: [128 x HD] in 64-column sub-tiles, each row's 16-byte chunks XOR-swizzled with the row
+    for (int idx = threadIdx.x; idx < BQT * (HD / 8); idx += 320) {
+        const int r = idx / (HD / 8), c = idx % (HD / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < rows) v = *reinterpret_cast<const uint4*>(p.q + (size_t)(tok0 + q0 + r) * p.q_stride + (size_t)h * HD + c * 8);
+        *reinterpret_cast<uint4*>(sQ + (c >> 3) * Q_SUB + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = v;
+    }
+    tc::fence_proxy_async();
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------- producer
+        if (lane == 0) {
+            for (int it = 0; it < n_pages; ++it) {
+                const int stage = it & 1;
+                const uint32_t par = ((it >> 1) & 1) ^ 1;
+                const int page = bt[page_a + it];
+                const int row = (page * p.Hkv + kvh) * PAGE_T;
+                if (!tc::mbar_wait(&k_empty[stage], par, abort_flag)) break;
+                tc::mbar_expect_tx(&k_full[stage], KV_TILE);
+#pragma unroll
+                for (int sub = 0; sub < NSUB; ++sub)
+                    tc::tma_load_2d(sK + stage * KV_TILE + sub * KV_SUB, &map_k, sub * 64, row, &k_full[stage]);
+                if (!tc::mbar_wait(&v_empty[stage], par, abort_flag)) break;
+                tc::mbar_expect_tx(&v_full[stage], KV_TILE);
+#pragma unroll
+                for (int sub = 0; sub < NSUB; ++sub)
+                    tc::tma_load_2d(sV + stage * KV_TILE + sub * KV_SUB, &map_v, sub * 64, row, &v_full[stage]);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = tc::make_idesc_bf16(BQT, PAGE_T);
+            constexpr uint32_t idesc_o = tc::make_idesc_bf16_b_mn(BQT, HD);
+            const uint32_t q_u = tc::smem_u32(sQ);
+            // scores of page `it` into S buffer it & 1; frees the K stage when done
+            auto issue_s = [&](int it) -> bool {
+                const int stage = it & 1;
+                if (!tc::mbar_wait(&k_full[stage], (it >> 1) & 1, abort_flag)) return false;
+                tc::fence_after_sync();
+                const uint32_t k_u = tc::smem_u32(sK + stage * KV_TILE);
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint64_t a = tc::make_smem_desc_sw128(q_u + (k >> 2) * Q_SUB + (k & 3) * 32);
+                    const uint64_t b = tc::make_smem_desc_sw128(k_u + (k >> 2) * KV_SUB + (k & 3) * 32);
+                    tc::umma_bf16(tmem_base + S_COL + stage * PAGE_T, a, b, idesc_s, k > 0 ? 1u : 0u);
+                }
+                tc::umma_commit(&s_full[stage]);
+                tc::umma_commit(&k_empty[stage]);
+                return true;
+            };
+            bool ok = issue_s(0);
+            if (ok && n_pages > 1) ok = issue_s(1);
+            for (int it = 0; it < n_pages && ok; ++it) {
+                const int stage = it & 1;
+                if (!tc::mbar_wait(p_full, it & 1, abort_flag)) { ok = false; break; }
+                if (!tc::mbar_wait(&v_full[stage], (it >> 1) & 1, abort_flag)) { ok = false; break; }
+                tc::fence_after_sync();
+                const uint32_t v_u = tc::smem_u32(sV + stage * KV_TILE);
+#pragma unroll
+                for (int j = 0; j < PAGE_T / 16; ++j) {
+                    // P: 16 keys = 8 packed columns of the S buffer that the softmax overwrote.
+                    // V as stored: rows are keys (the MMA's K), head_dim contiguous (its N): MN-major.
+                    // 16 keys further = 16 rows of 128 bytes; 64-column sub-tiles KV_SUB apart; 8-key groups 1 KB apart.
+                    const uint64_t b = tc::make_smem_desc_sw128_mn(v_u + j * 2048, KV_SUB, 1024);
+                    tc::umma_bf16_ts(tmem_base + O_COL, tmem_base + S_COL + stage * PAGE_T + j * 8, b, idesc_o,
+                                     (it > 0 || j > 0) ? 1u : 0u);
+                }
+                tc::umma_commit(&v_empty[stage]);
+                tc::umma_commit(pv_done);
+                if (it + 2 < n_pages) ok = issue_s(it + 2);  // its S buffer was read before p_full(it)
+            }
+        }
+    } else {
+        // ---------------------------- softmax: two threads per query row, 32 keys of a page each
+        const int quarter = warp & 3;                 // the TMEM lanes this warp may touch
+        const int half = (warp - 2) >> 2;             // warps 2..5: keys 0..31 of a page, warps 6..9: keys 32..63
+        const int row = quarter * 32 + lane;
+        const int pos = pos0 + row;
+        const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+        const float scale = p.scale_log2;
+        float m_run = -CUDART_INF_F;   // the maximum that the sums and O are scaled by (in log2 units)
+        float l_run = 0.f;             // this thread's share of the row's sum
+        bool ok = true;
+        for (int it = 0; it < n_pages; ++it) {
+            const int pg = page_a + it, stage = it & 1;
+            if (!tc::mbar_wait(&s_full[stage], (it >> 1) & 1, abort_flag)) { ok = false; break; }
+            tc::fence_after_sync();
+            uint32_t sr[32];
+            tc::tmem_ld32(tmem_base + lane_addr + S_COL + stage * PAGE_T + half * 32, sr);
+            tc::tmem_ld_wait();
+            const int key0 = pg * PAGE_T + half * 32;
+            if ((pg * PAGE_T + PAGE_T - 1 > pos0) || p.window > 0) {  // a page on the diagonal or at the window's edge
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    const int t = key0 + c;
+                    if (t > pos || (p.window > 0 && t <= pos - p.window)) sr[c] = 0xff800000u;  // -inf
+                }
+            }
+            float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+            for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c]));
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // the row's maximum over both halves: exchange through shared memory within the warp pair
+            s_max[(it & 1) * 256 + half * 128 + row] = mx;
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+            mx = fmaxf(mx, s_max[(it & 1) * 256 + (half ^ 1) * 128 + row]) * scale;
+            // move the scaling maximum only when the row's maximum ran ahead by more than the lag
+            float corr = 1.0f;
+            if (mx > m_run + RESCALE_LAG) {
+                corr = ex2(m_run - mx);   // m_run = -inf gives 0
+                m_run = mx;
+            }
+            const float neg_m = (m_run == -CUDART_INF_F) ? 0.f : -m_run;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                const float pv = ex2(fmaf(__uint_as_float(sr[c]), scale, neg_m));
+                sr[c] = __float_as_uint(pv);
+                sum4[c & 3] += pv;
+            }
+            l_run = l_run * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            // P: this thread's 32 keys as 16 packed words, written over the S buffer's columns
+            {
+                uint32_t pk[16];
+#pragma unroll
+                for (int c = 0; c < 16; ++c) pk[c] = pack_bf16(__uint_as_float(sr[2 * c]), __uint_as_float(sr[2 * c + 1]));
+                tc::tmem_st16(tmem_base + lane_addr + S_COL + stage * PAGE_T + half * 16, pk);
+            }
+            if (it > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+                // O is touched only when the scaling maximum moved; the previous P V must be over first.
+                // Each thread of the pair rescales half of the row's columns.
+                if (!tc::mbar_wait(pv_done, (it - 1) & 1, abort_flag)) { ok = false; break; }
+                tc::fence_after_sync();
+#pragma unroll 1
+                for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 32) {
+                    uint32_t o[32];
+                    tc::tmem_ld32(tmem_base + lane_addr + O_COL + c0, o);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * corr);
+                    tc::tmem_st32(tmem_base + lane_addr + O_COL + c0, o);
+                }
+            }
+            tc::tmem_st_wait();
+            if (pg == page_b) {
+                // Slots of the last page past the sequence's end may hold a stale Inf or NaN, and
+                // 0 x NaN is NaN: clear those value rows (their probabilities are exactly 0).
+                const int valid = len_after - pg * PAGE_T;
+                if (valid < PAGE_T) {
+                    tc::mbar_wait(&v_full[stage], (it >> 1) & 1, abort_flag);  // the tile must have landed before it is patched
+                    for (int idx = threadIdx.x - 64; idx < (PAGE_T - valid) * NSUB * 8; idx += 256) {
+                        const int r = valid + idx / (NSUB * 8), rest = idx % (NSUB * 8);
+                        *reinterpret_cast<uint4*>(sV + stage * KV_TILE + (rest >> 3) * KV_SUB + r * 128 + ((rest & 7) << 4)) =
+                            make_uint4(0, 0, 0, 0);
+                    }
+                    tc::fence_proxy_async();
+                }
+            }
+            tc::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(p_full);
+        }
+        if (ok && tc::mbar_wait(pv_done, (n_pages - 1) & 1, abort_flag)) {
+            tc::fence_after_sync();
+            // the row's sum is the pair's two shares
+            s_max[half * 128 + row] = l_run;
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+            const float l_all = l_run + s_max[(half ^ 1) * 128 + row];
+            const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
+            bf16* dst = p.out + (size_t)(tok0 + q0 + row) * p.out_stride + (size_t)h * HD;
+#pragma unroll 1
+            for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 32) {
+                uint32_t o[32];
+                tc::tmem_ld32(tmem_base + lane_addr + O_COL + c0, o);
+                tc::tmem_ld_wait();
+                if (row < rows) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint4 u;
+                        u.x = pack_bf16(__uint_as_float(o[8 * c + 0]) * inv, __uint_as_float(o[8 * c + 1]) * inv);
+                        u.y = pack_bf16(__uint_as_float(o[8 * c + 2]) * inv, __uint_as_float(o[8 * c + 3]) * inv);
+                        u.z = pack_bf16(__uint_as_float(o[8 * c + 4]) * inv, __uint_as_float(o[8 * c + 5]) * inv);
+                        u.w = pack_bf16(__uint_as_float(o[8 * c + 6]) * inv, __uint_as_float(o[8 * c + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c0 + 8 * c) = u;
+                    }
+                }
+            }
+        }
+    }
+
+    tc::fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag && p.error != nullptr) atomicExch(p.error, 1);
+    if (warp == 1) {
+        tc::fence_after_sync();
+        tc::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+int* tc_error_flag() {
+    static int* flag = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        if (cudaMalloc(&flag, sizeof(int)) == cudaSuccess) cudaMemset(flag, 0, sizeof(int));
+        else flag = nullptr;
+    });
+    return flag;
+}
+
+template <int HD>
+int launch_prefill_tc(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillTcParams& p, int n_seqs, int max_new,
+                      cudaStream_t s) {
+    // tiles + barriers + slack for the 1 KB alignment; two CTAs of head size 128 just fit an SM's 228 KB
+    constexpr int SMEM = (HD / 64) * BQT * 128 + 4 * PAGE_T * HD * 2 + 128 + 2048 + 896;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(p.Hq, n_seqs, (max_new + BQT - 1) / BQT);
+    odin_launch(attn_prefill_tc_kernel<HD>, grid, dim3(320), (size_t)SMEM, s, mk, mv, p);
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}
+
+}  // namespace
+
+// Same arguments as odin_attention_prefill; the output rows must be 16-byte aligned.
+extern "C" int odin_attention_prefill_tc(const void* q, long long q_row_stride, void* out, long long out_row_stride,
+                                         int n_seqs, int max_new, int Hq, int Hkv, int hd, const void* k_cache,
+                                         const void* v_cache, int n_pages, const int* seq_start,
+                                         const int* seq_len_after, const int* block_table, int bt_stride, int window,
+                                         void* stream) {
+    if (n_seqs <= 0 || max_new <= 0) return 0;
+    if (Hkv <= 0 || Hq % Hkv != 0) return ODIN_ERR_BAD_ARG;
+    if (n_seqs > 65535 || (max_new + BQT - 1) / BQT > 65535) return ODIN_ERR_UNSUPPORTED;
+    if ((q_row_stride % 8) || (((uintptr_t)q) & 15) || (out_row_stride % 8) || (((uintptr_t)out) & 15))
+        return ODIN_ERR_UNSUPPORTED;
+    CUtensorMap mk, mv;
+    int rc;
+    const long long rows = (long long)n_pages * Hkv * PAGE_T;
+    if ((rc = cache_map(&mk, k_cache, rows, hd))) return rc;
+    if ((rc = cache_map(&mv, v_cache, rows, hd))) return rc;
+    PrefillTcParams p;
+    p.q = (const bf16*)q; p.q_stride = (size_t)q_row_stride;
+    p.out = (bf16*)out; p.out_stride = (size_t)out_row_stride;
+    p.Hq = Hq; p.Hkv = Hkv;
+    p.seq_start = seq_start; p.seq_len_after = seq_len_after;
+    p.block_table = block_table; p.bt_stride = bt_stride;
+    p.window = window;
+    p.scale_log2 = 1.4426950408889634f / sqrtf((float)hd);
+    p.error = tc_error_flag();
+    cudaStream_t s = (cudaStream_t)stream;
+    if (hd == 64) return launch_prefill_tc<64>(mk, mv, p, n_seqs, max_new, s);
+    if (hd == 128) return launch_prefill_tc<128>(mk, mv, p, n_seqs, max_new, s);
+    return ODIN_ERR_UNSUPPORTED;
+}
+
+extern "C" int odin_attention_prefill_tc_error() {
+    int* f = tc_error_flag();
+    if (f == nullptr) return 0;
+    int v = 0;
+    if (cudaMemcpy(&v, f, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (v) cudaMemset(f, 0, sizeof(int));
+    return v;
+}

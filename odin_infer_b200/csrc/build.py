@@ -33,7 +33,7 @@ GROUPS = {
     "sampling": ["sampling.cu"],
     "gemm_tc": ["gemm_tc.cu"],
     "attention_decode": ["attention_decode.cu"],
-    "attention_prefill": ["attention_prefill.cu"],
+    "attention_prefill": ["attention_prefill.cu", "attention_prefill_tc.cu"],
 }
 HEADERS = ["common.cuh"]
 

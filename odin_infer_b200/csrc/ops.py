@@ -300,15 +300,18 @@ def attention_prefill_supported(head_dim: int) -> bool:
 
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new: int, n_q: int, n_kv: int,
                       head_dim: int, k_cache: torch.Tensor, v_cache: torch.Tensor, seq_start: torch.Tensor,
-                      seq_len_after: torch.Tensor, block_table: torch.Tensor, window: int = 0) -> None:
+                      seq_len_after: torch.Tensor, block_table: torch.Tensor, window: int = 0,
+                      variant: str = "tc") -> None:
     """Flash attention of each sequence's new tokens (rows seq_start[b]..seq_start[b+1] of q) over its
-    bfloat16 cache, which already holds this step's keys and values."""
+    bfloat16 cache, which already holds this step's keys and values.  variant "tc": tcgen05.mma with
+    accumulators in tensor memory (128 query rows per CTA); "mma": mma.sync (64 rows per CTA)."""
     T = q.shape[0]
     assert q.dtype == out.dtype == k_cache.dtype == torch.bfloat16
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == n_q * head_dim and out.shape == (T, n_q * head_dim)
     assert tuple(k_cache.shape[1:]) == (n_kv, PAGE, head_dim) and k_cache.is_contiguous() and v_cache.is_contiguous()
     assert seq_start.dtype == torch.int32 and seq_len_after.dtype == torch.int32 and block_table.dtype == torch.int32
-    _check(_fn("attention_prefill", "odin_attention_prefill")(
+    name = {"tc": "odin_attention_prefill_tc", "mma": "odin_attention_prefill"}[variant]
+    _check(_fn("attention_prefill", name)(
         _ptr(q), c_longlong(q.stride(0)), _ptr(out), c_longlong(out.stride(0)), c_int(n_seqs), c_int(max_new),
         c_int(n_q), c_int(n_kv), c_int(head_dim), _ptr(k_cache), _ptr(v_cache), c_int(k_cache.shape[0]),
         _ptr(seq_start), _ptr(seq_len_after), _ptr(block_table), c_int(block_table.stride(0)), c_int(window),
@@ -316,10 +319,13 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new: 
 
 
 def attention_prefill_check() -> None:
-    f = build.load("attention_prefill").odin_attention_prefill_error
-    f.restype = c_int
-    if f() != 0:
-        raise KernelError("attention_prefill: a device-side wait ran out; results are invalid")
+    for name in ("odin_attention_prefill_error", "odin_attention_prefill_tc_error"):
+        f = getattr(build.load("attention_prefill"), name)
+        f.restype = c_int
+        code = f()
+        if code != 0:
+            raise KernelError(f"attention_prefill ({name}): a device-side wait ran out or the kernel refused to run "
+                              f"(code {code}); results are invalid")
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
