@@ -228,6 +228,8 @@ def main() -> int:
     tps, ms_step, mean_ctx, launches = run_decode(engine, args.batch, args.steps, warmup, vocab)
     clocks = sampler.stop()
     ops.gemm_tc_check()
+    ops.attention_prefill_check()
+    ops.attention_decode_check()
 
     bytes_step = decode_bytes(cfg_raw, n_layers, args.batch, mean_ctx)
     achieved = bytes_step / (ms_step / 1e3) / 1e9
@@ -269,6 +271,8 @@ def main() -> int:
             pts[f"decode_b{b}_hbm_frac"] = round(decode_bytes(cfg_raw, n_layers, b, c) / (m / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
         out["points"] = pts
         ops.gemm_tc_check()
+        ops.attention_prefill_check()
+        ops.attention_decode_check()
     print(json.dumps(out))
     return 0
 

@@ -44,6 +44,20 @@ struct PrefillTcParams {
     int* error;
 };
 
+// The first wait that runs out records who it was: [which wait, head, sequence, tile, iteration,
+// pages of the tile, thread].  Waits: 1 producer on a free K stage, 2 producer on a free V stage,
+// 3 MMA on a landed K tile, 4 MMA on P, 5 MMA on a landed V tile, 6 softmax on scores, 7 softmax on the
+// previous P V (rescaling), 8 softmax on the last P V.
+__device__ __noinline__ void report_attn(int* err, int what, int it, int n_pages) {
+    if (err == nullptr) return;
+    atomicOr(&err[7], 1 << what);           // every kind of wait that ran out
+    atomicMax(&err[8 + what], it + 1);       // and the latest iteration it happened in
+    if (atomicCAS(err, 0, what) == 0) {
+        err[1] = (int)blockIdx.x; err[2] = (int)blockIdx.y; err[3] = (int)blockIdx.z; err[4] = it; err[5] = n_pages;
+        err[6] = (int)threadIdx.x;
+    }
+}
+
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -77,11 +91,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     uint64_t* v_full = bars + 4;       // [2]
     uint64_t* v_empty = bars + 6;      // [2] the P V product that read it is done
     uint64_t* s_full = bars + 8;       // [2] scores complete in S buffer b
-    uint64_t* p_full = bars + 10;      // P written over the S buffer, O rescaled if need be
-    uint64_t* pv_done = bars + 11;     // P V complete: O is stable
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+    // Every barrier completes once per use of ITS buffer or stage, and nobody can get two
+    // completions ahead of its waiter: a parity wait cannot tell a phase from the one after next.
+    uint64_t* p_full = bars + 10;      // [2] P written over S buffer b, O rescaled if need be
+    uint64_t* pv_done = bars + 12;     // [2] the P V product of an iteration with buffer b is complete
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    float* s_max = reinterpret_cast<float*>(bars + 14);  // [2 buffers][2 halves][128 rows]: the pair's exchange
+    float* s_max = reinterpret_cast<float*>(bars + 16);  // [2 buffers][2 halves][128 rows]: the pair's exchange
 
     pdl_trigger();
     pdl_wait();
@@ -111,8 +127,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < 10; ++i) tc::mbar_init(&bars[i], 1);
-        tc::mbar_init(p_full, 8);   // one arrival per softmax warp
-        tc::mbar_init(pv_done, 1);
+        tc::mbar_init(&p_full[0], 8);   // one arrival per softmax warp
+        tc::mbar_init(&p_full[1], 8);
+        tc::mbar_init(&pv_done[0], 1);
+        tc::mbar_init(&pv_done[1], 1);
         *abort_flag = 0;
         tc::fence_barrier_init();
     }
@@ -138,12 +156,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 const uint32_t par = ((it >> 1) & 1) ^ 1;
                 const int page = bt[page_a + it];
                 const int row = (page * p.Hkv + kvh) * PAGE_T;
-                if (!tc::mbar_wait(&k_empty[stage], par, abort_flag)) break;
+                if (!tc::mbar_wait(&k_empty[stage], par, abort_flag)) { report_attn(p.error, 1, it, n_pages); break; }
                 tc::mbar_expect_tx(&k_full[stage], KV_TILE);
 #pragma unroll
                 for (int sub = 0; sub < NSUB; ++sub)
                     tc::tma_load_2d(sK + stage * KV_TILE + sub * KV_SUB, &map_k, sub * 64, row, &k_full[stage]);
-                if (!tc::mbar_wait(&v_empty[stage], par, abort_flag)) break;
+                if (!tc::mbar_wait(&v_empty[stage], par, abort_flag)) { report_attn(p.error, 2, it, n_pages); break; }
                 tc::mbar_expect_tx(&v_full[stage], KV_TILE);
 #pragma unroll
                 for (int sub = 0; sub < NSUB; ++sub)
@@ -159,7 +177,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             // scores of page `it` into S buffer it & 1; frees the K stage when done
             auto issue_s = [&](int it) -> bool {
                 const int stage = it & 1;
-                if (!tc::mbar_wait(&k_full[stage], (it >> 1) & 1, abort_flag)) return false;
+                if (!tc::mbar_wait(&k_full[stage], (it >> 1) & 1, abort_flag)) { report_attn(p.error, 3, it, n_pages); return false; }
                 tc::fence_after_sync();
                 const uint32_t k_u = tc::smem_u32(sK + stage * KV_TILE);
 #pragma unroll
@@ -176,8 +194,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             if (ok && n_pages > 1) ok = issue_s(1);
             for (int it = 0; it < n_pages && ok; ++it) {
                 const int stage = it & 1;
-                if (!tc::mbar_wait(p_full, it & 1, abort_flag)) { ok = false; break; }
-                if (!tc::mbar_wait(&v_full[stage], (it >> 1) & 1, abort_flag)) { ok = false; break; }
+                if (!tc::mbar_wait(&p_full[stage], (it >> 1) & 1, abort_flag)) { report_attn(p.error, 4, it, n_pages); ok = false; break; }
+                if (!tc::mbar_wait(&v_full[stage], (it >> 1) & 1, abort_flag)) { report_attn(p.error, 5, it, n_pages); ok = false; break; }
                 tc::fence_after_sync();
                 const uint32_t v_u = tc::smem_u32(sV + stage * KV_TILE);
 #pragma unroll
@@ -190,7 +208,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                                      (it > 0 || j > 0) ? 1u : 0u);
                 }
                 tc::umma_commit(&v_empty[stage]);
-                tc::umma_commit(pv_done);
+                tc::umma_commit(&pv_done[stage]);
                 if (it + 2 < n_pages) ok = issue_s(it + 2);  // its S buffer was read before p_full(it)
             }
         }
@@ -207,7 +225,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         bool ok = true;
         for (int it = 0; it < n_pages; ++it) {
             const int pg = page_a + it, stage = it & 1;
-            if (!tc::mbar_wait(&s_full[stage], (it >> 1) & 1, abort_flag)) { ok = false; break; }
+            if (!tc::mbar_wait(&s_full[stage], (it >> 1) & 1, abort_flag)) { report_attn(p.error, 6, it, n_pages); ok = false; break; }
             tc::fence_after_sync();
             uint32_t sr[32];
             tc::tmem_ld32(tmem_base + lane_addr + S_COL + stage * PAGE_T + half * 32, sr);
@@ -253,7 +271,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             if (it > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
                 // O is touched only when the scaling maximum moved; the previous P V must be over first.
                 // Each thread of the pair rescales half of the row's columns.
-                if (!tc::mbar_wait(pv_done, (it - 1) & 1, abort_flag)) { ok = false; break; }
+                if (!tc::mbar_wait(&pv_done[(it - 1) & 1], ((it - 1) >> 1) & 1, abort_flag)) { report_attn(p.error, 7, it, n_pages); ok = false; break; }
                 tc::fence_after_sync();
 #pragma unroll 1
                 for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 32) {
@@ -282,9 +300,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             }
             tc::fence_before_sync();
             __syncwarp();
-            if (lane == 0) tc::mbar_arrive(p_full);
+            if (lane == 0) tc::mbar_arrive(&p_full[stage]);
         }
-        if (ok && tc::mbar_wait(pv_done, (n_pages - 1) & 1, abort_flag)) {
+        if (ok && !tc::mbar_wait(&pv_done[(n_pages - 1) & 1], ((n_pages - 1) >> 1) & 1, abort_flag)) { report_attn(p.error, 8, n_pages, n_pages); ok = false; }
+        if (ok) {
             tc::fence_after_sync();
             // the row's sum is the pair's two shares
             s_max[half * 128 + row] = l_run;
@@ -314,7 +333,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 
     tc::fence_before_sync();
     __syncthreads();
-    if (threadIdx.x == 0 && *abort_flag && p.error != nullptr) atomicExch(p.error, 1);
+    if (threadIdx.x == 0 && *abort_flag && p.error != nullptr) atomicCAS(p.error, 0, 99);
     if (warp == 1) {
         tc::fence_after_sync();
         tc::tmem_dealloc(tmem_base, TMEM_COLS);
@@ -325,7 +344,7 @@ int* tc_error_flag() {
     static int* flag = nullptr;
     static std::once_flag once;
     std::call_once(once, [] {
-        if (cudaMalloc(&flag, sizeof(int)) == cudaSuccess) cudaMemset(flag, 0, sizeof(int));
+        if (cudaMalloc(&flag, 32 * sizeof(int)) == cudaSuccess) cudaMemset(flag, 0, 32 * sizeof(int));
         else flag = nullptr;
     });
     return flag;
@@ -335,7 +354,7 @@ template <int HD>
 int launch_prefill_tc(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillTcParams& p, int n_seqs, int max_new,
                       cudaStream_t s) {
     // tiles + barriers + slack for the 1 KB alignment; two CTAs of head size 128 just fit an SM's 228 KB
-    constexpr int SMEM = (HD / 64) * BQT * 128 + 4 * PAGE_T * HD * 2 + 128 + 2048 + 896;
+    constexpr int SMEM = (HD / 64) * BQT * 128 + 4 * PAGE_T * HD * 2 + 128 + 2048 + 896;  // (barriers 128, exchange 2048, alignment 896)
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -381,11 +400,18 @@ extern "C" int odin_attention_prefill_tc(const void* q, long long q_row_stride, 
     return ODIN_ERR_UNSUPPORTED;
 }
 
+extern "C" int odin_attention_prefill_tc_error_detail(int* out8) {
+    int* f = tc_error_flag();
+    if (f == nullptr) return 0;
+    if (cudaMemcpy(out8, f, 32 * sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    return out8[0];
+}
+
 extern "C" int odin_attention_prefill_tc_error() {
     int* f = tc_error_flag();
     if (f == nullptr) return 0;
     int v = 0;
     if (cudaMemcpy(&v, f, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-    if (v) cudaMemset(f, 0, sizeof(int));
+    if (v) cudaMemset(f, 0, 32 * sizeof(int));
     return v;
 }

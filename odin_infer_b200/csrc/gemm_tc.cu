@@ -61,6 +61,17 @@ struct Cfg {
     static constexpr int SMEM = STAGES * STAGE + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
+// The first wait that runs out records who it was: [which wait, block, work item, K block, stage or
+// accumulator, mode, tile width, grid size].  Waits: 1 producer on a free stage, 2 MMA on a free
+// accumulator, 3 MMA on a landed stage, 4 epilogue on a complete accumulator.
+__device__ __noinline__ void report(int* err, int what, int item, int kb, int slot, int mode, int bn) {
+    if (err == nullptr) return;
+    if (atomicCAS(err, 0, what) == 0) {
+        err[1] = (int)blockIdx.x; err[2] = item; err[3] = kb; err[4] = slot; err[5] = mode; err[6] = bn;
+        err[7] = (int)gridDim.x;
+    }
+}
+
 template <typename TO>
 __device__ __forceinline__ void store_vec(TO* dst, const uint32_t* r, int n);
 
@@ -171,7 +182,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                         continue;
                     }
-                    if (!tc::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+                    if (!tc::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { report(p.error, 1, (int)w, kb, stage, MODE, BN); ok = false; break; }
                     uint8_t* sx = smem + stage * C::STAGE;
                     uint8_t* sy = sx + C::STAGE_X;
                     tc::mbar_expect_tx(&full[stage], C::STAGE);
@@ -195,15 +206,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             uint32_t stage = 0, phase = 0;
             uint32_t local = 0;
             bool ok = true;
+            pdl_wait();  // nothing can be multiplied before the previous kernel's output exists: sleep, do not spin
             for (long long w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++local) {
                 const int s = (int)(w % p.n_split);
                 const int kb0 = s * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
                 const uint32_t acc = local % ACC_BUFS, acc_phase = (local / ACC_BUFS) & 1;
-                if (!tc::mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+                if (!tc::mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { report(p.error, 2, (int)w, -1, (int)acc, MODE, BN); ok = false; break; }
                 tc::fence_after_sync();
                 const uint32_t tmem_d = tmem_base + acc * C::ACC_W;
                 for (int kb = kb0; kb < kb1; ++kb) {
-                    if (!tc::mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+                    if (!tc::mbar_wait(&full[stage], phase, abort_flag)) { report(p.error, 3, (int)w, kb, stage, MODE, BN); ok = false; break; }
                     tc::fence_after_sync();
                     const uint32_t ax = tc::smem_u32(smem + stage * C::STAGE);
                     const uint64_t dx = tc::make_smem_desc_sw128(ax);
@@ -236,7 +248,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             const long long rest = w / p.n_split;
             const int tx = (int)(rest % p.tiles_x), ty = (int)(rest / p.tiles_x);
             const uint32_t acc = local % ACC_BUFS, acc_phase = (local / ACC_BUFS) & 1;
-            if (!tc::mbar_wait(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+            if (!tc::mbar_wait(&acc_full[acc], acc_phase, abort_flag)) { if (threadIdx.x == 64) report(p.error, 4, (int)w, -1, (int)acc, MODE, BN); ok = false; break; }
             tc::fence_after_sync();
             const int i = tx * BM + quarter * 32 + lane;  // row of X
             TO* out = reinterpret_cast<TO*>(p.out) + (size_t)s * p.split_stride;
@@ -292,7 +304,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
     tc::fence_before_sync();
     __syncthreads();
-    if (threadIdx.x == 0 && *abort_flag && p.error != nullptr) atomicExch(p.error, 1);
+    if (threadIdx.x == 0 && *abort_flag && p.error != nullptr) atomicCAS(p.error, 0, 99);
     if (warp == 1) {
         tc::fence_after_sync();
         tc::tmem_dealloc(tmem_base, C::TMEM_COLS);
@@ -366,7 +378,7 @@ int* error_flag() {
     static int* flag = nullptr;
     static std::once_flag once;
     std::call_once(once, [] {
-        if (cudaMalloc(&flag, sizeof(int)) == cudaSuccess) cudaMemset(flag, 0, sizeof(int));
+        if (cudaMalloc(&flag, 8 * sizeof(int)) == cudaSuccess) cudaMemset(flag, 0, 8 * sizeof(int));
         else flag = nullptr;
     });
     return flag;
@@ -512,4 +524,12 @@ extern "C" int odin_gemm_tc_error() {
     if (cudaMemcpy(&v, f, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
     if (v) cudaMemset(f, 0, sizeof(int));
     return v;
+}
+
+// The same, with the details of the first wait that ran out (8 ints, see `report`); does not clear.
+extern "C" int odin_gemm_tc_error_detail(int* out8) {
+    int* f = error_flag();
+    if (f == nullptr) return 0;
+    if (cudaMemcpy(out8, f, 8 * sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    return out8[0];
 }

@@ -196,10 +196,15 @@ def gemm_tc_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) 
 
 def gemm_tc_check() -> None:
     """Raise if a tensor-core kernel gave up a bounded wait since the last check (synchronises)."""
-    f = build.load("gemm_tc").odin_gemm_tc_error
+    lib = build.load("gemm_tc")
+    detail = (c_int * 8)()
+    lib.odin_gemm_tc_error_detail.restype = c_int
+    lib.odin_gemm_tc_error_detail(detail)
+    f = lib.odin_gemm_tc_error
     f.restype = c_int
     if f() != 0:
-        raise KernelError("gemm_tc: a device-side wait ran out (pipeline stalled); results are invalid")
+        raise KernelError("gemm_tc: a device-side wait ran out (pipeline stalled); results are invalid "
+                          f"[wait, block, item, k block, slot, mode, tile, grid] = {list(detail)}")
 
 
 def head_prep(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, q_norm: torch.Tensor | None,
@@ -319,13 +324,16 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new: 
 
 
 def attention_prefill_check() -> None:
+    detail = (c_int * 32)()
+    build.load("attention_prefill").odin_attention_prefill_tc_error_detail(detail)
     for name in ("odin_attention_prefill_error", "odin_attention_prefill_tc_error"):
         f = getattr(build.load("attention_prefill"), name)
         f.restype = c_int
         code = f()
         if code != 0:
             raise KernelError(f"attention_prefill ({name}): a device-side wait ran out or the kernel refused to run "
-                              f"(code {code}); results are invalid")
+                              f"(code {code}); results are invalid; [wait, head, sequence, tile, iteration, pages, thread] = "
+                              f"{list(detail)[:7]}; kinds that ran out (bit mask) {detail[7]:#x}, their last iterations + 1: {list(detail)[9:17]}")
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

@@ -48,15 +48,30 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Each try_wait suspends for a hardware-defined time before it gives up, so this
-// many tries are seconds, far beyond any legitimate wait of these kernels.
-#define TC_WAIT_LIMIT (1u << 22)
+// A wait gives up after TC_WAIT_SECONDS of wall-clock time (%globaltimer), checked every 256
+// tries.  How long one try_wait suspends is up to the hardware (about 4 us on an idle SM, far
+// less on a busy one), so a limit on the number of tries alone would mean anything between a
+// fraction of a second and a quarter of a minute; legitimate waits of these kernels are
+// microseconds (no role spins across a kernel boundary: each calls pdl_wait() first).
+#define TC_WAIT_SECONDS 4ull
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 // Returns false if the wait ran out or another role aborted.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < TC_WAIT_LIMIT; ++i) {
+    unsigned long long t0 = 0;  // the timer is read only once a wait has already lasted a while
+    for (uint32_t i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 63) == 63 && *abort_flag) return false;
+        if ((i & 255) == 255) {
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > TC_WAIT_SECONDS * 1000000000ull) break;
+        }
     }
     *abort_flag = 1;
     return false;

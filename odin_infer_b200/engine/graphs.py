@@ -26,7 +26,7 @@ def bucket_for(n: int) -> int | None:
 class DecodeGraphs:
     def __init__(self, rt, model, cache):
         self.rt, self.model, self.cache = rt, model, cache
-        self._graphs: dict[int, tuple] = {}
+        self._graphs: dict[tuple, tuple] = {}
         self.last_h2d_bytes = 0
 
     def run(self, entries: list[StepEntry], starts: list[int]) -> torch.Tensor | None:
@@ -35,9 +35,13 @@ class DecodeGraphs:
         bucket = bucket_for(len(entries))
         if bucket is None:
             return NotImplemented
+        # kernels whose launch shape follows the longest context (decode attention's key splits)
+        # make a graph valid for a class of context lengths only: the class is part of the key
+        longest = max(s + 1 for s in starts)
+        bucket = (bucket, self.rt.context_class(longest))
         hit = self._graphs.get(bucket)
         if hit is None:
-            batch = StepBatch(self.cache, entries, starts, self.rt.device, pad_rows_to=bucket, pad_seqs_to=bucket,
+            batch = StepBatch(self.cache, entries, starts, self.rt.device, pad_rows_to=bucket[0], pad_seqs_to=bucket[0],
                               all_rows_wanted=True)
             # once eagerly: first-use set-up of the kernels (function attributes, tensor maps,
             # error flags, the allocator's pools) must not fall into the capture
