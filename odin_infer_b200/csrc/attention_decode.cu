@@ -261,9 +261,11 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_trigger();
-    pdl_wait();
+    // The step's tables are written before the step starts, and of the cache the kernel before
+    // this one writes only the newest key and value (in the last page): tables and the older
+    // pages are fetched before the wait for that kernel, the query and the last page after it.
     const int seq = p.tok_seq[t];
-    if (seq < 0) return;  // padding row
+    if (seq < 0) { pdl_wait(); return; }  // padding row
     const int g = p.Hq / p.Hkv, h0 = kvh * g;
     const int pos = p.tok_pos[t];
     int first = 0;
@@ -276,6 +278,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     float* my_ml = p.part_ml + (((size_t)t * p.Hq + h0) * p.n_split + split) * 2;
     const size_t head_step_acc = (size_t)p.n_split * HD, head_step_ml = (size_t)p.n_split * 2;
     if (pa >= pb) {  // nothing for this split: an empty partial
+        pdl_wait();
         for (int idx = threadIdx.x; idx < g * HD; idx += 128) {
             const int r = idx / HD, d = idx % HD;
             my_acc[(size_t)r * head_step_acc + d] = 0.f;
@@ -285,18 +288,6 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     }
     const int* bt = p.block_table + (size_t)seq * p.bt_stride;
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) tc::mbar_init(&full[s], 1);
-        *abort_flag = 0;
-        tc::fence_barrier_init();
-    }
-    for (int idx = threadIdx.x; idx < 16 * (HD / 8); idx += 128) {
-        const int r = idx / (HD / 8), c = idx % (HD / 8);
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < g) v = *reinterpret_cast<const uint4*>(p.q + (size_t)t * p.q_stride + (size_t)(h0 + r) * HD + c * 8);
-        *reinterpret_cast<uint4*>(sQ + q_off(r, c * 8)) = v;
-    }
-    __syncthreads();
     auto issue = [&](int page_idx, int stage) {
         const int page = bt[page_idx];
         const int row = (page * p.Hkv + kvh) * PAGE_T;
@@ -307,8 +298,22 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
             tc::tma_load_2d(sV + stage * TILE + sub * 8192, &map_v, sub * 64, row, &full[stage]);
         }
     };
-    if (threadIdx.x == 0)
-        for (int s = 0; s < STAGES && pa + s < pb; ++s) issue(pa + s, s);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) tc::mbar_init(&full[s], 1);
+        *abort_flag = 0;
+        tc::fence_barrier_init();
+        for (int s = 0; s < STAGES && pa + s < pb; ++s)
+            if (pa + s != p_last) issue(pa + s, s);
+    }
+    pdl_wait();
+    for (int idx = threadIdx.x; idx < 16 * (HD / 8); idx += 128) {
+        const int r = idx / (HD / 8), c = idx % (HD / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < g) v = *reinterpret_cast<const uint4*>(p.q + (size_t)t * p.q_stride + (size_t)(h0 + r) * HD + c * 8);
+        *reinterpret_cast<uint4*>(sQ + q_off(r, c * 8)) = v;
+    }
+    if (threadIdx.x == 0 && p_last >= pa && p_last < pb && p_last - pa < STAGES) issue(p_last, p_last - pa);
+    __syncthreads();
 
     uint32_t qa[KB][4];
     const uint32_t sQ_u = tc::smem_u32(sQ);

@@ -69,7 +69,9 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 //   * pdl_trigger() first, so the next kernel's CTAs can take their places early;
 //   * pdl_wait() before the first read of anything an earlier kernel wrote and before
 //     the first global write (a buffer may be reused memory that an earlier kernel
-//     still reads); only constant data (weights) may be touched before it;
+//     still reads); before it a kernel may touch only what no kernel of the step writes:
+//     weights and constant tables, the step's integer tables (the host copies them to the
+//     device before the step's first kernel), and the cache as earlier steps left it;
 //   * every kernel launched this way calls pdl_wait(), so completion stays in stream
 //     order.  Set ODIN_PDL=0 in the environment to launch in plain stream order.
 // ---------------------------------------------------------------------------

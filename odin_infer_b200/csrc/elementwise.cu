@@ -60,20 +60,30 @@ __device__ __forceinline__ void store4(bf16* p, float4 v) {
     *reinterpret_cast<uint2*>(p) = u;
 }
 
+// Four consecutive weights (the index a multiple of 4, the vector 16-byte aligned).
+__device__ __forceinline__ float4 load4w(const VecRef& w, int j) {
+    return w.is_bf16 ? load4<bf16>((const bf16*)w.p + j) : load4<float>((const float*)w.p + j);
+}
+
 // VEC: the row length is a multiple of 4 and every pointer is 16-byte aligned, so the
 // row moves in groups of four; the order of the additions per element (x, then the
 // parts in order) and of the sum of squares per thread is the same in both variants.
+// The loads of a group are issued together (eight parts at a time), so that a row costs
+// one trip to memory and not one per part; the weights of the first group and the row
+// number, which no earlier kernel writes, are fetched before the wait for that kernel.
 template <typename TD, typename TO, bool VEC>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_split,
+__global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_split,
                                    size_t split_stride, VecRef w, float eps, TO* __restrict__ out,
                                    const int* __restrict__ rows, int d) {
     __shared__ float red[32];
     extern __shared__ float rowbuf[];  // d floats
     pdl_trigger();
-    pdl_wait();
     const int r = blockIdx.x;
     int src = r;
     if (rows != nullptr) src = rows[r];
+    float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (VEC && (int)threadIdx.x * 4 < d) w0 = load4w(w, threadIdx.x * 4);
+    pdl_wait();
     TO* o = out + (size_t)r * d;
     if (src < 0) {
         for (int j = threadIdx.x; j < d; j += blockDim.x) o[j] = from_f32<TO>(0.f);
@@ -85,9 +95,15 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
         for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
             float4 v = load4<float>(xr + j);
             if (delta != nullptr) {
-                for (int sidx = 0; sidx < n_split; ++sidx) {
-                    const float4 dv = load4<TD>(delta + (size_t)sidx * split_stride + (size_t)src * d + j);
-                    v.x += dv.x; v.y += dv.y; v.z += dv.z; v.w += dv.w;
+                const TD* dp = delta + (size_t)src * d + j;
+                for (int s0 = 0; s0 < n_split; s0 += 8) {
+                    float4 dv[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        if (s0 + u < n_split) dv[u] = load4<TD>(dp + (size_t)(s0 + u) * split_stride);
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        if (s0 + u < n_split) { v.x += dv[u].x; v.y += dv[u].y; v.z += dv[u].z; v.w += dv[u].w; }
                 }
             }
             store4(rowbuf + j, v);
@@ -113,8 +129,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__
         for (int j = threadIdx.x * 4; j < d; j += blockDim.x * 4) {
             const float4 v = load4<float>(rowbuf + j);
             if (write_back) store4(xr + j, v);
-            store4(o + j, make_float4(w.at(j) * (rs * v.x), w.at(j + 1) * (rs * v.y), w.at(j + 2) * (rs * v.z),
-                                      w.at(j + 3) * (rs * v.w)));
+            const float4 wv = (j == (int)threadIdx.x * 4) ? w0 : load4w(w, j);
+            store4(o + j, make_float4(wv.x * (rs * v.x), wv.y * (rs * v.y), wv.z * (rs * v.z), wv.w * (rs * v.w)));
         }
     } else {
         for (int j = threadIdx.x; j < d; j += blockDim.x) {
@@ -130,10 +146,10 @@ static int launch_add_rmsnorm(float* x, const void* delta, int n_split, size_t s
                               float eps, void* out, const int* rows, int n_rows, int d, cudaStream_t s) {
     const size_t smem = (size_t)d * sizeof(float);
     if (smem > 200 * 1024) return ODIN_ERR_UNSUPPORTED;
-    const bool vec = (d % 4 == 0) && ((((uintptr_t)x) | ((uintptr_t)delta) | ((uintptr_t)out)) % 16 == 0) &&
+    const bool vec = (d % 4 == 0) && ((((uintptr_t)x) | ((uintptr_t)delta) | ((uintptr_t)out) | ((uintptr_t)w.p)) % 16 == 0) &&
                      (split_stride % 4 == 0);
     if (vec) {
-        const int threads = d >= 4096 ? 512 : (d >= 1024 ? 256 : 128);
+        const int threads = d >= 4096 ? 1024 : (d >= 2048 ? 512 : (d >= 1024 ? 256 : 128));
         if (smem > 48 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO, true>,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

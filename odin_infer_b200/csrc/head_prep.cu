@@ -140,32 +140,55 @@ head_prep_fast_kernel(const TI* qkv, int n_split, size_t split_stride, bf16* q_o
                       bf16* __restrict__ v_cache, int page_size, int write_kv) {
     constexpr int HD = VEC * 32, HALF = HD / 2;
     pdl_trigger();
-    pdl_wait();
+    // What no earlier kernel of the step writes is fetched before the wait for that kernel: the
+    // step's tables, the page of the cache, the angles' cosines and sines, the norms' weights.
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y * HP_WARPS + warp;
-    if (head >= Hq + 2 * Hkv) return;
-    const int seq = tok_seq[t];
-    if (seq < 0) return;
+    const bool in_range = head < Hq + 2 * Hkv;
+    const int seq = in_range ? tok_seq[t] : -1;
     const int pos = tok_pos[t];
     const bool is_q = head < Hq;
     const bool is_k = !is_q && head < Hq + Hkv;
-    if (!is_q && !write_kv) return;
+    bool active = in_range && seq >= 0 && (is_q || write_kv);
     const int kvh = is_q ? 0 : (is_k ? head - Hq : head - Hq - Hkv);
-    const TI* src = qkv + (size_t)t * row_stride + (size_t)head * HD + lane * VEC;
     bf16* dst = q_out + (size_t)t * q_out_stride + (size_t)head * HD + lane * VEC;
-    if (!is_q) {
+    if (active && !is_q) {
         const int page = block_table[(size_t)seq * bt_stride + pos / page_size];
-        if (page < 0) return;
-        dst = (is_k ? k_cache : v_cache) + (((size_t)page * Hkv + kvh) * page_size + (pos % page_size)) * HD + lane * VEC;
+        if (page < 0) active = false;
+        else dst = (is_k ? k_cache : v_cache) + (((size_t)page * Hkv + kvh) * page_size + (pos % page_size)) * HD + lane * VEC;
     }
+    const bool rotates = active && (is_q || is_k);
+    const bool in_table = (pos >= 0 && pos < table_len);
+    float c[VEC], sn[VEC], wn[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) { c[e] = 1.f; sn[e] = 0.f; wn[e] = 1.f; }
+    if (rotates && in_table) {
+        load_vec<VEC>(cos_t + (size_t)pos * HALF + (lane & 15) * VEC, c);
+        load_vec<VEC>(sin_t + (size_t)pos * HALF + (lane & 15) * VEC, sn);
+    }
+    if (rotates && has_norm) {
+        const VecRef& w = is_q ? qw : kw;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) wn[e] = w.at(lane * VEC + e);
+    }
+    pdl_wait();
+    if (!active) return;
+    const TI* src = qkv + (size_t)t * row_stride + (size_t)head * HD + lane * VEC;
     float v[VEC];
     load_vec<VEC>(src, v);
-    for (int sp = 1; sp < n_split; ++sp) {
-        float w2[VEC];
-        load_vec<VEC>(src + (size_t)sp * split_stride, w2);
+    // the parts of a split product, four loads in flight at a time, added in their order
+    for (int s0 = 1; s0 < n_split; s0 += 4) {
+        float w2[4][VEC];
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) v[e] += w2[e];
+        for (int u = 0; u < 4; ++u)
+            if (s0 + u < n_split) load_vec<VEC>(src + (size_t)(s0 + u) * split_stride, w2[u]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (s0 + u < n_split) {
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) v[e] += w2[u][e];
+            }
     }
     if (!is_q && !is_k) {  // value head: stored as it is
         store_vec_bf16<VEC>(dst, v);
@@ -179,23 +202,16 @@ head_prep_fast_kernel(const TI* qkv, int n_split, size_t split_stride, bf16* q_o
         ss /= (float)HD;
         ss += eps;
         const float r = 1.0f / sqrtf(ss);
-        const VecRef& w = is_q ? qw : kw;
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) v[e] = w.at(lane * VEC + e) * (r * v[e]);
+        for (int e = 0; e < VEC; ++e) v[e] = wn[e] * (r * v[e]);
     }
     float o[VEC];
-    const bool in_table = (pos >= 0 && pos < table_len);
 #pragma unroll
     for (int e = 0; e < VEC; ++e) {
         const float other = __shfl_xor_sync(0xffffffffu, v[e], 16);
-        if (in_table) {
-            const int i = (lane & 15) * VEC + e;
-            const float c = cos_t[(size_t)pos * HALF + i], sn = sin_t[(size_t)pos * HALF + i];
-            // first half: x c - y s with (x, y) = (mine, other); second half: x s + y c with (x, y) = (other, mine)
-            o[e] = (lane < 16) ? (v[e] * c - other * sn) : (other * sn + v[e] * c);
-        } else {
-            o[e] = v[e];
-        }
+        // first half: x c - y s with (x, y) = (mine, other); second half: x s + y c with (x, y) = (other, mine)
+        if (in_table) o[e] = (lane < 16) ? (v[e] * c[e] - other * sn[e]) : (other * sn[e] + v[e] * c[e]);
+        else o[e] = v[e];
     }
     store_vec_bf16<VEC>(dst, o);
 }
@@ -218,7 +234,8 @@ extern "C" int odin_head_prep(const void* qkv, int in_dtype, int n_split, long l
     VecRef qw{q_norm_w, w_dtype == ODIN_BF16}, kw{k_norm_w, w_dtype == ODIN_BF16};
     const bool fast_in = (in_dtype == ODIN_BF16 && n_split == 1) || in_dtype == ODIN_F32;
     if (fast_in && dtype == ODIN_BF16 && rot == hd && (hd == 64 || hd == 128) && (row_stride % 4) == 0 &&
-        (split_stride % 4) == 0 && (q_out_stride % 4) == 0 && ((((uintptr_t)qkv) | ((uintptr_t)q_out)) & 15) == 0) {
+        (split_stride % 4) == 0 && (q_out_stride % 4) == 0 &&
+        ((((uintptr_t)qkv) | ((uintptr_t)q_out) | ((uintptr_t)cos_t) | ((uintptr_t)sin_t)) & 15) == 0) {
 #define FAST(VEC, TI)                                                                                              \
     odin_launch(head_prep_fast_kernel<VEC, TI>, grid, dim3(HP_WARPS * 32), 0, s, (const TI*)qkv, n_split,           \
                 (size_t)split_stride, (bf16*)q_out, (size_t)q_out_stride, Hq, Hkv, (size_t)row_stride, qw, kw,     \
