@@ -247,7 +247,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                       const DecodeTcParams p) {
     using namespace attn;
     constexpr int TILE = PAGE_T * HD * 2;
-    constexpr int STAGES = 3;
+    constexpr int STAGES = 3, BT_KEEP = 128;
     constexpr int KB = HD / 16, NB_O = HD / 8;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -257,6 +257,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     uint64_t* full = reinterpret_cast<uint64_t*>(sQ + 16 * HD * 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(full + STAGES);
     float* s_ml = reinterpret_cast<float*>(full + STAGES + 1);  // [4 warps][16 rows][2]
+    int* s_pages = reinterpret_cast<int*>(s_ml + 4 * 16 * 2);  // [BT_KEEP]
 
     const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -288,8 +289,10 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     }
     const int* bt = p.block_table + (size_t)seq * p.bt_stride;
 
+    // this CTA's page numbers, so that no trip to the block table sits between two pages
+    for (int i = threadIdx.x; i < min(pb - pa, BT_KEEP); i += 128) s_pages[i] = bt[pa + i];
     auto issue = [&](int page_idx, int stage) {
-        const int page = bt[page_idx];
+        const int page = (page_idx - pa < BT_KEEP) ? s_pages[page_idx - pa] : bt[page_idx];
         const int row = (page * p.Hkv + kvh) * PAGE_T;
         tc::mbar_expect_tx(&full[stage], 2 * TILE);
 #pragma unroll
@@ -302,9 +305,11 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         for (int s = 0; s < STAGES; ++s) tc::mbar_init(&full[s], 1);
         *abort_flag = 0;
         tc::fence_barrier_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0)
         for (int s = 0; s < STAGES && pa + s < pb; ++s)
             if (pa + s != p_last) issue(pa + s, s);
-    }
     pdl_wait();
     for (int idx = threadIdx.x; idx < 16 * (HD / 8); idx += 128) {
         const int r = idx / (HD / 8), c = idx % (HD / 8);
@@ -519,7 +524,7 @@ int launch_decode_tc(const bf16* q, size_t q_stride, bf16* out, size_t out_strid
                      const bf16* k_cache, const bf16* v_cache, int n_pages, const int* tok_pos, const int* tok_seq,
                      const int* block_table, int bt_stride, int window, float* part_acc, float* part_ml, int n_split,
                      cudaStream_t s) {
-    constexpr int SMEM = 6 * attn::PAGE_T * HD * 2 + 16 * HD * 2 + 64 + 4 * 16 * 2 * 4 + 1024;
+    constexpr int SMEM = 6 * attn::PAGE_T * HD * 2 + 16 * HD * 2 + 64 + 4 * 16 * 2 * 4 + 128 * 4 + 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);

@@ -44,6 +44,12 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr",
 ]
 
+# ODIN_KERNEL_TRACE=1: libraries of their own (libodin_<group>_trace.so) whose kernels record a
+# timeline (see common.cuh); for tuning, never for serving
+TRACE = os.environ.get("ODIN_KERNEL_TRACE", "0") not in ("", "0")
+if TRACE:
+    NVCC_FLAGS.append("-DODIN_TRACE")
+
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
 
@@ -82,7 +88,7 @@ def _out_dir() -> str:
 
 
 def lib_path(group: str) -> str:
-    return os.path.join(_out_dir(), f"libodin_{group}.so")
+    return os.path.join(_out_dir(), f"libodin_{group}{'_trace' if TRACE else ''}.so")
 
 
 def _is_fresh(group: str) -> bool:

@@ -75,8 +75,53 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 //   * every kernel launched this way calls pdl_wait(), so completion stays in stream
 //     order.  Set ODIN_PDL=0 in the environment to launch in plain stream order.
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#ifdef ODIN_TRACE
+// Kernel timeline for tuning (libraries built with ODIN_KERNEL_TRACE=1 only): thread 0 of every
+// CTA records the time at which it starts and at which its wait for the previous kernel ends,
+// as [time in ns, point << 56 | block size << 44 | grid size << 22 | block number] after a counter in word 0.
+static __device__ unsigned long long* odin_trace_buf = nullptr;
+static __device__ unsigned int odin_trace_cap = 0;
+__device__ __forceinline__ void odin_trace_emit(unsigned long long point, unsigned long long t) {
+    if (odin_trace_buf == nullptr) return;
+    const unsigned long long idx = atomicAdd(odin_trace_buf, 1ULL);
+    if (idx >= odin_trace_cap) return;
+    const unsigned long long grid = (unsigned long long)gridDim.x * gridDim.y * gridDim.z;
+    const unsigned long long block = ((unsigned long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    odin_trace_buf[1 + 2 * idx] = t;
+    odin_trace_buf[2 + 2 * idx] = (point << 56) | ((unsigned long long)blockDim.x << 44) | ((grid & 0x3fffff) << 22) | (block & 0x3fffff);
+}
+__device__ __forceinline__ unsigned long long odin_trace_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void odin_trace_mark(unsigned long long point, bool any_thread = false) {
+    if ((!any_thread && (threadIdx.x | threadIdx.y | threadIdx.z) != 0) || odin_trace_buf == nullptr) return;
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    const unsigned long long idx = atomicAdd(odin_trace_buf, 1ULL);
+    if (idx >= odin_trace_cap) return;
+    const unsigned long long grid = (unsigned long long)gridDim.x * gridDim.y * gridDim.z;
+    const unsigned long long block = ((unsigned long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    odin_trace_buf[1 + 2 * idx] = t;
+    odin_trace_buf[2 + 2 * idx] = (point << 56) | ((unsigned long long)blockDim.x << 44) | ((grid & 0x3fffff) << 22) | (block & 0x3fffff);
+}
+extern "C" __attribute__((weak)) int odin_trace_attach(void* buf, unsigned int cap) {
+    if (cudaMemcpyToSymbol(odin_trace_buf, &buf, sizeof(buf)) != cudaSuccess) return 1;
+    return cudaMemcpyToSymbol(odin_trace_cap, &cap, sizeof(cap)) != cudaSuccess;
+}
+#else
+__device__ __forceinline__ void odin_trace_mark(unsigned long long, bool = false) {}
+#endif
+
+__device__ __forceinline__ void pdl_trigger() {
+    odin_trace_mark(0);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    odin_trace_mark(1);
+}
 
 #include <cstdlib>
 #include <cstring>
