@@ -212,11 +212,15 @@ attn_decode_kernel(const bf16* __restrict__ q, size_t q_stride, int Hq, int Hkv,
 //
 // A CTA of 4 warps takes (sequence, kv head, key split).  The query heads of the kv
 // head are the rows of a 16-row MMA tile.  The split's pages stream through a ring of
-// 3 shared-memory stages by TMA (one page of one kv head is a contiguous [64, hd] tile;
-// 128-byte swizzle); of every page warp w takes keys 16w .. 16w+15: S = Q K^T and
-// O += P V with mma.sync m16n8k16, online softmax in registers.  The four warps' partial
-// results are merged through shared memory, then either written as this split's
-// partial or, with one split, normalised and stored as the result.
+// SLOTS shared-memory slots by TMA (one page of one kv head is a contiguous [64, hd]
+// tile; 128-byte swizzle).  Page i of the split belongs to warp i mod 4, which computes
+// S = Q K^T and O += P V for its 64 keys with mma.sync m16n8k16 and keeps its own
+// running maximum and sum; when it is done with a page it asks for the page that uses
+// the slot next.  No warp waits for another inside the loop: with a few pages per CTA
+// the kernel is a chain of latencies, and four pages are in flight per CTA instead of
+// a quarter of one per warp.  The four warps' results are merged through shared
+// memory at the end, then either written as this split's partial or, with one split,
+// normalised and stored as the result.
 // ---------------------------------------------------------------------------
 struct DecodeTcParams {
     const bf16* q;
@@ -234,30 +238,92 @@ struct DecodeTcParams {
     float* part_ml;
     int n_split;
     int* error;
+    int* counters;  // one per (token, kv head), zero between launches: how many splits have written their partial
 };
+
+// The splits of one (token, kv head) meet here once their partials are written: the one that
+// arrives last adds them up, writes the result and leaves the counter at zero for the next
+// launch.  out[h][:] = sum_s w_s acc_s / sum_s w_s l_s with w_s = 2^(m_s - max m).
+template <int HD>
+__device__ __forceinline__ void split_arrive_and_combine(const DecodeTcParams& p, int t, int kvh, int g, int h0,
+                                                         int* s_last) {
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) *s_last = (atomicAdd(&p.counters[t * p.Hkv + kvh], 1) == p.n_split - 1);
+    __syncthreads();
+    if (!*s_last) return;
+    __threadfence();
+    for (int idx = threadIdx.x * 4; idx < g * HD; idx += 128 * 4) {
+        const int r = idx / HD, d = idx % HD;
+        const float* ml = p.part_ml + ((size_t)t * p.Hq + h0 + r) * p.n_split * 2;
+        const float* ac = p.part_acc + ((size_t)t * p.Hq + h0 + r) * p.n_split * HD + d;
+        float mm = NEG_BIG;
+        for (int s0 = 0; s0 < p.n_split; ++s0) mm = fmaxf(mm, __ldcg(ml + 2 * s0));
+        float ll = 0.f;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < p.n_split; s0 += 4) {
+            float4 v[4];
+            float w[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (s0 + u < p.n_split) {
+                    v[u] = __ldcg(reinterpret_cast<const float4*>(ac + (size_t)(s0 + u) * HD));
+                    w[u] = exp2f(__ldcg(ml + 2 * (s0 + u)) - mm);
+                    ll += __ldcg(ml + 2 * (s0 + u) + 1) * w[u];
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (s0 + u < p.n_split) {
+                    a.x += v[u].x * w[u]; a.y += v[u].y * w[u]; a.z += v[u].z * w[u]; a.w += v[u].w * w[u];
+                }
+            }
+        }
+        const float inv = ll > 0.f ? 1.0f / ll : 0.f;
+        uint2 u2;
+        u2.x = attn::pack_bf16(a.x * inv, a.y * inv);
+        u2.y = attn::pack_bf16(a.z * inv, a.w * inv);
+        *reinterpret_cast<uint2*>(p.out + (size_t)t * p.out_stride + (size_t)(h0 + r) * HD + d) = u2;
+    }
+    if (threadIdx.x == 0) p.counters[t * p.Hkv + kvh] = 0;
+}
 
 __device__ __forceinline__ uint32_t q_off(int row, int col) {  // a [16 x HD] tile in 64-column sub-tiles of 2 KB
     const int sub = col >> 6, chunk = (col & 63) >> 3;
     return (uint32_t)(sub * 2048 + row * 128 + ((chunk ^ (row & 7)) << 4));
 }
 
-template <int HD>
+template <int HD, int SLOTS>
+struct DecodeTcSmem {
+    static constexpr int TILE = attn::PAGE_T * HD * 2;  // K or V of one page
+    static constexpr int SLOT = 2 * TILE;
+    static constexpr int BT_KEEP = 128;
+    static constexpr int OS = HD + 8;                   // row of the merge buffer (floats), padded against bank conflicts
+    static constexpr int TAIL = 16 * HD * 2 /*Q*/ + 64 /*barriers, flag*/ + 4 * 16 * 2 * 4 /*m, l*/ + 4 * 16 * 4 /*scales*/ +
+                                BT_KEEP * 4 + 32 /*requests per slot*/;
+    static constexpr int BYTES = SLOTS * SLOT + TAIL + 1024 /*alignment*/;
+    static_assert(4 * 16 * OS * 4 <= SLOTS * SLOT, "the merge buffer reuses the page slots");
+    static_assert(SLOTS <= 7, "barriers and the flag share 64 bytes");
+};
+
+template <int HD, int SLOTS>
 __global__ void __launch_bounds__(128)
 attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                       const DecodeTcParams p) {
     using namespace attn;
-    constexpr int TILE = PAGE_T * HD * 2;
-    constexpr int STAGES = 3, BT_KEEP = 128;
+    using L = DecodeTcSmem<HD, SLOTS>;
+    constexpr int TILE = L::TILE, SLOT = L::SLOT, BT_KEEP = L::BT_KEEP, OS = L::OS;
     constexpr int KB = HD / 16, NB_O = HD / 8;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t* sK = smem;                       // STAGES tiles; reused for the warps' merge at the end
-    uint8_t* sV = smem + STAGES * TILE;       // STAGES tiles
-    uint8_t* sQ = smem + 2 * STAGES * TILE;   // 16 x HD
+    uint8_t* sQ = smem + SLOTS * SLOT;  // 16 x HD
     uint64_t* full = reinterpret_cast<uint64_t*>(sQ + 16 * HD * 2);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(full + STAGES);
-    float* s_ml = reinterpret_cast<float*>(full + STAGES + 1);  // [4 warps][16 rows][2]
-    int* s_pages = reinterpret_cast<int*>(s_ml + 4 * 16 * 2);  // [BT_KEEP]
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(full + 7);
+    int* s_last = const_cast<int*>(abort_flag) + 1;
+    float* s_ml = reinterpret_cast<float*>(full + 8);  // [4 warps][16 rows][2]
+    float* s_scale = s_ml + 4 * 16 * 2;                // [4 warps][16 rows]
+    int* s_pages = reinterpret_cast<int*>(s_scale + 4 * 16);
+    volatile int* s_requested = s_pages + BT_KEEP;     // [SLOTS] how many pages have been requested into the slot
 
     const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -274,42 +340,47 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     const int p_first = first / PAGE_T, p_last = pos / PAGE_T;
     const int per = (p_last - p_first + 1 + p.n_split - 1) / p.n_split;
     const int pa = p_first + split * per, pb = min(p_last + 1, pa + per);  // pages [pa, pb)
+    const int n_here = pb - pa;
     const int t_lo = first, t_hi = pos + 1;                               // visible keys [t_lo, t_hi)
     float* my_acc = p.part_acc + (((size_t)t * p.Hq + h0) * p.n_split + split) * HD;
     float* my_ml = p.part_ml + (((size_t)t * p.Hq + h0) * p.n_split + split) * 2;
     const size_t head_step_acc = (size_t)p.n_split * HD, head_step_ml = (size_t)p.n_split * 2;
-    if (pa >= pb) {  // nothing for this split: an empty partial
+    if (n_here <= 0) {  // nothing for this split: an empty partial
         pdl_wait();
         for (int idx = threadIdx.x; idx < g * HD; idx += 128) {
             const int r = idx / HD, d = idx % HD;
             my_acc[(size_t)r * head_step_acc + d] = 0.f;
             if (d == 0) { my_ml[(size_t)r * head_step_ml] = NEG_BIG; my_ml[(size_t)r * head_step_ml + 1] = 0.f; }
         }
+        split_arrive_and_combine<HD>(p, t, kvh, g, h0, s_last);
         return;
     }
     const int* bt = p.block_table + (size_t)seq * p.bt_stride;
 
     // this CTA's page numbers, so that no trip to the block table sits between two pages
-    for (int i = threadIdx.x; i < min(pb - pa, BT_KEEP); i += 128) s_pages[i] = bt[pa + i];
-    auto issue = [&](int page_idx, int stage) {
-        const int page = (page_idx - pa < BT_KEEP) ? s_pages[page_idx - pa] : bt[page_idx];
+    for (int i = threadIdx.x; i < min(n_here, BT_KEEP); i += 128) s_pages[i] = bt[pa + i];
+    auto issue = [&](int i, int slot) {  // page pa + i of the sequence into a slot
+        const int page = (i < BT_KEEP) ? s_pages[i] : bt[pa + i];
         const int row = (page * p.Hkv + kvh) * PAGE_T;
-        tc::mbar_expect_tx(&full[stage], 2 * TILE);
+        uint8_t* dst = smem + slot * SLOT;
+        tc::mbar_expect_tx(&full[slot], SLOT);
 #pragma unroll
         for (int sub = 0; sub < HD / 64; ++sub) {
-            tc::tma_load_2d(sK + stage * TILE + sub * 8192, &map_k, sub * 64, row, &full[stage]);
-            tc::tma_load_2d(sV + stage * TILE + sub * 8192, &map_v, sub * 64, row, &full[stage]);
+            tc::tma_load_2d(dst + sub * 8192, &map_k, sub * 64, row, &full[slot]);
+            tc::tma_load_2d(dst + TILE + sub * 8192, &map_v, sub * 64, row, &full[slot]);
         }
+        __threadfence_block();
+        s_requested[slot] = i / SLOTS + 1;
     };
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) tc::mbar_init(&full[s], 1);
+        for (int s = 0; s < SLOTS; ++s) { tc::mbar_init(&full[s], 1); s_requested[s] = 0; }
         *abort_flag = 0;
         tc::fence_barrier_init();
     }
     __syncthreads();
     if (threadIdx.x == 0)
-        for (int s = 0; s < STAGES && pa + s < pb; ++s)
-            if (pa + s != p_last) issue(pa + s, s);
+        for (int i = 0; i < SLOTS && i < n_here; ++i)
+            if (pa + i != p_last) issue(i, i);
     pdl_wait();
     for (int idx = threadIdx.x; idx < 16 * (HD / 8); idx += 128) {
         const int r = idx / (HD / 8), c = idx % (HD / 8);
@@ -317,7 +388,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         if (r < g) v = *reinterpret_cast<const uint4*>(p.q + (size_t)t * p.q_stride + (size_t)(h0 + r) * HD + c * 8);
         *reinterpret_cast<uint4*>(sQ + q_off(r, c * 8)) = v;
     }
-    if (threadIdx.x == 0 && p_last >= pa && p_last < pb && p_last - pa < STAGES) issue(p_last, p_last - pa);
+    if (threadIdx.x == 0 && p_last >= pa && p_last < pb && p_last - pa < SLOTS) issue(p_last - pa, p_last - pa);
     __syncthreads();
 
     uint32_t qa[KB][4];
@@ -332,40 +403,60 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
     float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F}, l_run[2] = {0.f, 0.f};
 
-    bool ok = true;
-    for (int pg = pa; pg < pb; ++pg) {
-        const int it = pg - pa, stage = it % STAGES;
-        const uint32_t phase = (it / STAGES) & 1;
-        if (!tc::mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
-        const uint32_t sK_u = tc::smem_u32(sK + stage * TILE), sV_u = tc::smem_u32(sV + stage * TILE);
+    for (int i = warp; i < n_here; i += 4) {
+        const int slot = i % SLOTS, pg = pa + i;
+        const uint32_t phase = (i / SLOTS) & 1;
+        // A wait by parity cannot tell the slot's use before this one from the one that has not
+        // begun: the warp first waits until its page has been requested (by the warp that had the
+        // slot before, or at the start), only then for the page to land.
+        bool ok = true;
+        if (s_requested[slot] <= i / SLOTS) {
+            unsigned long long t0 = 0;
+            for (uint32_t n = 1; s_requested[slot] <= i / SLOTS; ++n) {
+                if (*abort_flag) { ok = false; break; }
+                if ((n & 255) == 0) {
+                    const unsigned long long now = tc::global_ns();
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > TC_WAIT_SECONDS * 1000000000ull) { *abort_flag = 1; ok = false; break; }
+                }
+            }
+        }
+        ok = ok && tc::mbar_wait(&full[slot], phase, abort_flag);
+        if (!__all_sync(0xffffffffu, ok)) break;
+        uint8_t* sK = smem + slot * SLOT;
+        uint8_t* sV = sK + TILE;
+        const uint32_t sK_u = tc::smem_u32(sK), sV_u = tc::smem_u32(sV);
         if (pg == p_last) {
             // slots past the sequence's end may hold a stale Inf or NaN; 0 x NaN is NaN: clear those value rows
             const int valid = t_hi - pg * PAGE_T;
             if (valid < PAGE_T) {
-                for (int idx = threadIdx.x; idx < (PAGE_T - valid) * (HD / 8); idx += 128) {
+                for (int idx = lane; idx < (PAGE_T - valid) * (HD / 8); idx += 32) {
                     const int r = valid + idx / (HD / 8), c = idx % (HD / 8);
-                    *reinterpret_cast<uint4*>(sV + stage * TILE + tile_off(r, c * 8)) = make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4*>(sV + tile_off(r, c * 8)) = make_uint4(0, 0, 0, 0);
                 }
-                __syncthreads();
+                __syncwarp();
             }
         }
-        // S = Q K^T for this warp's 16 keys of the page
-        float s[2][4];
+        // S = Q K^T for the page's 64 keys: eight blocks of eight keys
+        float s[8][4];
 #pragma unroll
-        for (int i = 0; i < 2; ++i)
+        for (int nb = 0; nb < 8; ++nb)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+            for (int j = 0; j < 4; ++j) s[nb][j] = 0.f;
 #pragma unroll
         for (int kb = 0; kb < KB; ++kb) {
-            uint32_t b[4];
-            ldmatrix_x4(b, sK_u + tile_off(warp * 16 + (lane & 7) + ((lane >> 4) << 3), kb * 16 + ((lane >> 3) & 1) * 8));
-            mma_bf16(s[0], qa[kb], b[0], b[1]);
-            mma_bf16(s[1], qa[kb], b[2], b[3]);
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                uint32_t b[4];
+                ldmatrix_x4(b, sK_u + tile_off(np * 16 + (lane & 7) + ((lane >> 4) << 3), kb * 16 + ((lane >> 3) & 1) * 8));
+                mma_bf16(s[2 * np], qa[kb], b[0], b[1]);
+                mma_bf16(s[2 * np + 1], qa[kb], b[2], b[3]);
+            }
         }
-        const int key0 = pg * PAGE_T + warp * 16 + (lane & 3) * 2;
+        const int key0 = pg * PAGE_T + (lane & 3) * 2;
         float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-        for (int nb = 0; nb < 2; ++nb) {
+        for (int nb = 0; nb < 8; ++nb) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int tk = key0 + nb * 8 + (j & 1);
@@ -387,7 +478,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
             l_run[r] *= corr[r];
         }
 #pragma unroll
-        for (int nb = 0; nb < 2; ++nb) {
+        for (int nb = 0; nb < 8; ++nb) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float pv = exp2f(s[nb][j] - m_use[j >> 1]);
@@ -396,41 +487,48 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
             }
         }
 #pragma unroll
-        for (int i = 0; i < NB_O; ++i) {
-            o[i][0] *= corr[0]; o[i][1] *= corr[0];
-            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        for (int n = 0; n < NB_O; ++n) {
+            o[n][0] *= corr[0]; o[n][1] *= corr[0];
+            o[n][2] *= corr[1]; o[n][3] *= corr[1];
         }
-        uint32_t pa_frag[4];
-        pa_frag[0] = pack_bf16(s[0][0], s[0][1]);
-        pa_frag[1] = pack_bf16(s[0][2], s[0][3]);
-        pa_frag[2] = pack_bf16(s[1][0], s[1][1]);
-        pa_frag[3] = pack_bf16(s[1][2], s[1][3]);
+        // O += P V, sixteen keys at a time
 #pragma unroll
-        for (int nb2 = 0; nb2 < NB_O / 2; ++nb2) {
-            uint32_t b[4];
-            ldmatrix_x4_trans(b, sV_u + tile_off(warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), nb2 * 16 + (lane >> 4) * 8));
-            mma_bf16(o[2 * nb2], pa_frag, b[0], b[1]);
-            mma_bf16(o[2 * nb2 + 1], pa_frag, b[2], b[3]);
+        for (int ks = 0; ks < 4; ++ks) {
+            uint32_t pf[4];
+            pf[0] = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
+            pf[1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
+            pf[2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
+            pf[3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+#pragma unroll
+            for (int nb2 = 0; nb2 < NB_O / 2; ++nb2) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, sV_u + tile_off(ks * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), nb2 * 16 + (lane >> 4) * 8));
+                mma_bf16(o[2 * nb2], pf, b[0], b[1]);
+                mma_bf16(o[2 * nb2 + 1], pf, b[2], b[3]);
+            }
         }
-        __syncthreads();  // everyone is done with this stage
-        if (threadIdx.x == 0 && pg + STAGES < pb) issue(pg + STAGES, stage);
+        __syncwarp();  // every lane is done with the slot
+        if (lane == 0 && i + SLOTS < n_here) issue(i + SLOTS, slot);
     }
-    if (threadIdx.x == 0 && (!ok || *abort_flag) && p.error != nullptr) atomicExch(p.error, 1);
-    if (!ok) return;
+    __syncthreads();  // no warp reads a slot any more and every requested page has been consumed
+    if (*abort_flag) {
+        if (threadIdx.x == 0 && p.error != nullptr) atomicExch(p.error, 1);
+        return;
+    }
 
-    // merge the four warps (each saw a quarter of the keys) through shared memory
+    // merge the four warps (each saw its own pages) through shared memory
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
     }
-    float* s_o = reinterpret_cast<float*>(sK);  // [4 warps][16 rows][HD]; no copy is in flight any more
+    float* s_o = reinterpret_cast<float*>(smem);  // [4 warps][16 rows][OS]
     const int row_a = lane >> 2, col = (lane & 3) * 2;
 #pragma unroll
-    for (int i = 0; i < NB_O; ++i) {
-        float* dst = s_o + ((size_t)warp * 16 + row_a) * HD + i * 8 + col;
-        dst[0] = o[i][0]; dst[1] = o[i][1];
-        dst[8 * HD] = o[i][2]; dst[8 * HD + 1] = o[i][3];
+    for (int n = 0; n < NB_O; ++n) {
+        float* dst = s_o + ((size_t)warp * 16 + row_a) * OS + n * 8 + col;
+        *reinterpret_cast<float2*>(dst) = make_float2(o[n][0], o[n][1]);
+        *reinterpret_cast<float2*>(dst + 8 * OS) = make_float2(o[n][2], o[n][3]);
     }
     if ((lane & 3) == 0) {
         s_ml[(warp * 16 + row_a) * 2] = fmaxf(m_run[0], NEG_BIG);
@@ -439,25 +537,38 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         s_ml[(warp * 16 + row_a + 8) * 2 + 1] = l_run[1];
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < g * HD; idx += 128) {
-        const int r = idx / HD, d = idx % HD;
+    if (threadIdx.x < 64) {  // each warp's weight in each row
+        const int r = threadIdx.x & 15, w = threadIdx.x >> 4;
         float mm = NEG_BIG;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, s_ml[(w * 16 + r) * 2]);
-        float a = 0.f, ll = 0.f;
+        for (int w2 = 0; w2 < 4; ++w2) mm = fmaxf(mm, s_ml[(w2 * 16 + r) * 2]);
+        s_scale[w * 16 + r] = exp2f(s_ml[(w * 16 + r) * 2] - mm);
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x * 4; idx < g * HD; idx += 128 * 4) {
+        const int r = idx / HD, d = idx % HD;  // four consecutive columns of one row
+        float mm = NEG_BIG, ll = 0.f;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            const float c = exp2f(s_ml[(w * 16 + r) * 2] - mm);
-            a += s_o[((size_t)w * 16 + r) * HD + d] * c;
+            const float c = s_scale[w * 16 + r];
+            const float4 v = *reinterpret_cast<const float4*>(s_o + ((size_t)w * 16 + r) * OS + d);
+            a.x += v.x * c; a.y += v.y * c; a.z += v.z * c; a.w += v.w * c;
             ll += s_ml[(w * 16 + r) * 2 + 1] * c;
+            mm = fmaxf(mm, s_ml[(w * 16 + r) * 2]);
         }
         if (p.n_split == 1) {
-            p.out[(size_t)t * p.out_stride + (size_t)(h0 + r) * HD + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
+            const float inv = ll > 0.f ? 1.0f / ll : 0.f;
+            uint2 u;
+            u.x = pack_bf16(a.x * inv, a.y * inv);
+            u.y = pack_bf16(a.z * inv, a.w * inv);
+            *reinterpret_cast<uint2*>(p.out + (size_t)t * p.out_stride + (size_t)(h0 + r) * HD + d) = u;
         } else {
-            my_acc[(size_t)r * head_step_acc + d] = a;
+            *reinterpret_cast<float4*>(my_acc + (size_t)r * head_step_acc + d) = a;
             if (d == 0) { my_ml[(size_t)r * head_step_ml] = mm; my_ml[(size_t)r * head_step_ml + 1] = ll; }
         }
     }
+    if (p.n_split > 1) split_arrive_and_combine<HD>(p, t, kvh, g, h0, s_last);
 }
 
 // out[t][h][:] = sum_s w_s acc_s / sum_s w_s l_s, w_s = 2^(m_s - max m)
@@ -509,14 +620,44 @@ int launch_decode(const bf16* q, size_t q_stride, bf16* out, size_t out_stride, 
 }
 
 
-int* decode_error_flag() {
-    static int* flag = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        if (cudaMalloc(&flag, sizeof(int)) == cudaSuccess) cudaMemset(flag, 0, sizeof(int));
-        else flag = nullptr;
-    });
-    return flag;
+// The error flag and the split counters live in the library's device image, so that no entry
+// point of this file ever allocates device memory.  In host code these names are only handles
+// for cudaGetSymbolAddress.
+constexpr int SPLIT_COUNTERS = 1 << 16;
+static __device__ int g_decode_error;
+static __device__ int g_split_counters[SPLIT_COUNTERS];
+
+template <typename T>
+int* device_symbol(const T& symbol) {
+    constexpr int MAX_DEVICES = 64;
+    static int* addr[MAX_DEVICES] = {nullptr};
+    static std::mutex mu;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return nullptr;
+    std::lock_guard<std::mutex> g(mu);
+    if (addr[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, symbol) != cudaSuccess) return nullptr;
+        addr[dev] = static_cast<int*>(p);
+    }
+    return addr[dev];
+}
+
+int* decode_error_flag() { return device_symbol(g_decode_error); }
+int* split_counters() { return device_symbol(g_split_counters); }
+
+template <int HD, int SLOTS>
+int launch_decode_tc_slots(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeTcParams& p, dim3 grid, cudaStream_t s) {
+    constexpr int SMEM = DecodeTcSmem<HD, SLOTS>::BYTES;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_tc_kernel<HD, SLOTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    odin_launch(attn_decode_tc_kernel<HD, SLOTS>, grid, dim3(128), (size_t)SMEM, s, mk, mv, p);
+    ODIN_LAUNCH_CHECK();
+    return 0;
 }
 
 template <int HD>
@@ -524,13 +665,8 @@ int launch_decode_tc(const bf16* q, size_t q_stride, bf16* out, size_t out_strid
                      const bf16* k_cache, const bf16* v_cache, int n_pages, const int* tok_pos, const int* tok_seq,
                      const int* block_table, int bt_stride, int window, float* part_acc, float* part_ml, int n_split,
                      cudaStream_t s) {
-    constexpr int SMEM = 6 * attn::PAGE_T * HD * 2 + 16 * HD * 2 + 64 + 4 * 16 * 2 * 4 + 128 * 4 + 1024;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    // the result is written with 8-byte stores
+    if ((out_stride % 4) != 0 || (((uintptr_t)out) & 7) != 0) return ODIN_ERR_UNSUPPORTED;
     CUtensorMap mk, mv;
     int rc;
     const long long rows = (long long)n_pages * Hkv * attn::PAGE_T;
@@ -543,15 +679,20 @@ int launch_decode_tc(const bf16* q, size_t q_stride, bf16* out, size_t out_strid
     p.scale_log2 = 1.4426950408889634f / sqrtf((float)HD);
     p.part_acc = part_acc; p.part_ml = part_ml; p.n_split = n_split;
     p.error = decode_error_flag();
+    p.counters = split_counters();
+    if (n_split > 1 && (p.counters == nullptr || (long long)B * Hkv > SPLIT_COUNTERS)) return ODIN_ERR_UNSUPPORTED;
     dim3 grid(n_split, Hkv, B);
-    odin_launch(attn_decode_tc_kernel<HD>, grid, dim3(128), (size_t)SMEM, s, mk, mv, p);
-    ODIN_LAUNCH_CHECK();
-    if (n_split > 1) {
-        odin_launch(attn_combine_kernel, dim3(B * Hq), dim3(128), 0, s, (const float*)part_acc, (const float*)part_ml,
-                    n_split, (int)HD, out, out_stride, Hq, tok_seq);
-        ODIN_LAUNCH_CHECK();
+    // few CTAs: one per SM with a deep ring; many: two per SM with a ring half as deep
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
     }
-    return 0;
+    const long long ctas = (long long)n_split * Hkv * B;
+    if (ctas > sms) rc = launch_decode_tc_slots<HD, 3>(mk, mv, p, grid, s);
+    else rc = launch_decode_tc_slots<HD, 6>(mk, mv, p, grid, s);
+    return rc;
 }
 
 }  // namespace
@@ -566,7 +707,11 @@ extern "C" int odin_attention_decode_error() {
     if (f == nullptr) return 0;
     int v = 0;
     if (cudaMemcpy(&v, f, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-    if (v) cudaMemset(f, 0, sizeof(int));
+    if (v) {
+        cudaMemset(f, 0, sizeof(int));
+        // splits of the failed launch may never have met: their counters start from zero again
+        if (int* c = split_counters()) cudaMemset(c, 0, SPLIT_COUNTERS * sizeof(int));
+    }
     return v;
 }
 
@@ -591,7 +736,8 @@ extern "C" int odin_attention_decode(const void* q, long long q_row_stride, void
     float* part_ml = scratch + (size_t)B * Hq * n_split * hd;
     // head sizes 64 and 128 with at most 16 query heads per kv head: the tensor-core kernel
     if ((hd == 64 || hd == 128) && Hq / Hkv <= 16 && page_size == attn::PAGE_T && n_pages > 0 &&
-        (q_row_stride % 8) == 0 && (((uintptr_t)q) & 15) == 0) {
+        (q_row_stride % 8) == 0 && (((uintptr_t)q) & 15) == 0 && (out_row_stride % 4) == 0 &&
+        (((uintptr_t)out) & 7) == 0 && (((uintptr_t)scratch) & 15) == 0) {
         if (hd == 64)
             return launch_decode_tc<64>((const bf16*)q, (size_t)q_row_stride, (bf16*)out, (size_t)out_row_stride, B, Hq,
                                         Hkv, (const bf16*)k_cache, (const bf16*)v_cache, n_pages, tok_pos, tok_seq,

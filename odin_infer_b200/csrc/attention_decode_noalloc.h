@@ -18,6 +18,9 @@
  *   entry point with memory of your own.
  * - The first call on each device looks up the array's device address (with that
  *   device current).  Make that first call before any stream capture begins.
+ * - The counters on which the key splits of a launch meet, and the library's error flag,
+ *   are fixed arrays in the device image too (for every entry point of the library), so
+ *   that this one stays free of allocations on every path.
  * - All calls share the one array.  Nothing in it has to be cleared between calls:
  *   each call writes every element it later reads.  But two calls that overlap on
  *   the GPU (different streams, no ordering between them) race on it; keep calls on

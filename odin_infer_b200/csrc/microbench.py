@@ -92,8 +92,8 @@ def main(argv=None) -> int:
         o = torch.empty_like(q)
         pos = torch.full((B,), args.ctx - 1, dtype=torch.int32, device=DEV)
         seq = torch.arange(B, dtype=torch.int32, device=DEV)
-        ctas = B * hkv * ((hq // hkv + 3) // 4)
-        n_split = args.split or max(1, min(16, (2 * 148 + ctas - 1) // ctas))
+        from ..engine.runtime import decode_key_splits
+        n_split = args.split or decode_key_splits(B, hkv, args.ctx)
         scratch = torch.empty(ops.attention_decode_scratch(B, hq, hd, n_split), device=DEV)
         ms = timeit(lambda: ops.attention_decode(q, o, hq, hkv, hd, k, v, pos, seq, bt, 0, scratch, n_split), args.iters)
         out.update(batch=B, ctx=args.ctx, n_split=n_split, us=round(ms * 1e3, 2),

@@ -289,7 +289,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int, he
         _ptr(q), c_longlong(q.stride(0)), _ptr(out), c_longlong(out.stride(0)), c_int(B), c_int(n_q), c_int(n_kv),
         c_int(head_dim), _ptr(k_cache), _ptr(v_cache), c_int(PAGE), c_int(k_cache.shape[0]), _ptr(tok_pos),
         _ptr(tok_seq), _ptr(block_table), c_int(block_table.stride(0)), c_int(window), _ptr(scratch), c_int(n_split),
-        _stream()), "attention_decode", kernels=2 if n_split > 1 or head_dim not in (64, 128) else 1)
+        _stream()), "attention_decode", kernels=1 if head_dim in (64, 128) and n_q // n_kv <= 16 else 2)
 
 
 def attention_decode_check() -> None:

@@ -28,15 +28,21 @@ def choose_k_split(n_tiles: int, k_blocks: int, m: int, n_sms: int = 148, max_sp
     return best
 
 
-def decode_key_splits(n_seqs: int, n_kv_heads: int, longest: int, page: int = 64) -> int:
-    """Into how many parts decode attention cuts a sequence's keys.  One CTA walks its pages
-    through a TMA ring at well under a microsecond per page, so splitting pays only for long
-    contexts (more than 16 pages per CTA) or when there would be fewer than 32 CTAs; every
-    split costs a second (merge) kernel.  Depends on the batch bucket and on the longest
-    sequence's page count class, never on which sequences are in the batch."""
-    pages = max(1, (longest + page - 1) // page)
-    want = max((pages + 15) // 16, (32 + n_seqs * n_kv_heads - 1) // (n_seqs * n_kv_heads))
-    return max(1, min(want, 16))  # a split that finds no page of its own writes an empty partial
+def context_class_of(longest: int, page: int = 64) -> int:
+    """Contexts of one class launch the same kernels: the number of 8-page groups of the
+    longest sequence."""
+    return (max(1, (longest + page - 1) // page) + 7) // 8
+
+
+def decode_key_splits(n_seqs: int, n_kv_heads: int, longest: int, page: int = 64, n_sms: int = 148) -> int:
+    """Into how many parts decode attention cuts a sequence's keys.  A CTA's four warps take a
+    page each, so up to about four pages per CTA run side by side and more only lengthen the
+    chain; the split that finishes last adds the partials up inside the same kernel.  So: two
+    splits per 8 pages of context, as long as all CTAs together fit the GPU twice.  Depends on
+    the batch bucket and on the context class, never on which sequences are in the batch."""
+    want = 2 * context_class_of(longest, page)
+    room = max(1, (2 * n_sms) // max(1, n_seqs * n_kv_heads))
+    return max(1, min(want, room, 16))  # a split that finds no page of its own writes an empty partial
 
 
 class Runtime:
@@ -52,9 +58,8 @@ class Runtime:
         return {"gemm_tc", "attention_decode", "attention_prefill"} if self.dtype == torch.bfloat16 else set()
 
     def context_class(self, longest: int) -> int:
-        """Contexts of one class launch the same kernels (see decode_key_splits): the number
-        of 16-page groups of the longest sequence."""
-        return (max(1, (longest + 63) // 64) + 15) // 16
+        """Contexts of one class launch the same kernels (see decode_key_splits)."""
+        return context_class_of(longest)
 
     def run(self, model, batch):
         """Run one step of `model` eagerly; returns the logits at the wanted rows."""
@@ -111,7 +116,7 @@ class Runtime:
         kernels refuse go to the plain kernel."""
         if self.dtype == torch.bfloat16 and step.all_single and ops.attention_decode_supported(head_dim):
             B = q.shape[0]
-            n_split = decode_key_splits(B, n_kv, step.max_len_after)
+            n_split = decode_key_splits(B, n_kv, step.max_len_after, n_sms=self.n_sms)
             scratch = self.empty(ops.attention_decode_scratch(B, n_q, head_dim, n_split), dtype=torch.float32)
             ops.attention_decode(q, out, n_q, n_kv, head_dim, k_line, v_line, step.tok_pos, step.tok_seq, block_table,
                                  window, scratch, n_split)

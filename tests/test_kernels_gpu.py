@@ -325,6 +325,50 @@ def test_attention_decode_against_plain_kernel_and_reference(geom, n_split):
         close(out[r].float(), plain[r].float(), 1e-2)
 
 
+@pytest.mark.parametrize("geom", [(32, 8, 128), (8, 8, 64), (12, 3, 128)])
+@pytest.mark.parametrize("case", ["long", "many"])
+def test_attention_decode_slots_used_again(geom, case):
+    """More pages per CTA than the kernel has shared-memory slots, so that slots are used again:
+    few CTAs (the deep ring) with long sequences, and more CTAs than SMs (the shallow ring).
+    The far key that carries all the weight lies in a page that comes through a reused slot."""
+    from odin_infer_b200.csrc import ops
+    n_q, n_kv, hd = geom
+    torch.manual_seed(11 + hd)
+    lengths = [1500, 777, 1101] if case == "long" else [600 + 13 * i for i in range(40)]
+    B = len(lengths)
+    k_cache, v_cache, bt = paged_cache(B, lengths, n_kv, hd, torch.bfloat16)
+    q = 0.1 * torch.randn(B, n_q, hd, device=DEV)
+    far_vals = []
+    for s, n in enumerate(lengths):
+        keys = 0.1 * torch.randn(n, n_kv, hd, device=DEV)
+        vals = torch.randn(n, n_kv, hd, device=DEV)
+        far = n - 1 - 64 * (s % 3) - 7          # in one of the last pages: slots 0.. have been used again by then
+        keys[far] = 0.0
+        keys[far, :, 0] = 40.0
+        far_vals.append(vals[far, 0].bfloat16().float())
+        pages = bt[s, : (n + 63) // 64].long()
+        pad = pages.numel() * 64 - n
+        kp = torch.cat([keys, torch.full((pad, n_kv, hd), float('nan'), device=DEV)]).view(-1, 64, n_kv, hd).permute(0, 2, 1, 3)
+        vp = torch.cat([vals, torch.full((pad, n_kv, hd), float('nan'), device=DEV)]).view(-1, 64, n_kv, hd).permute(0, 2, 1, 3)
+        k_cache[pages] = kp.bfloat16()
+        v_cache[pages] = vp.bfloat16()
+    q[:, :, 0] = 40.0 / math.sqrt(hd) * 2
+    qf = q.reshape(B, n_q * hd).bfloat16()
+    tok_pos = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device=DEV)
+    tok_seq = torch.arange(B, dtype=torch.int32, device=DEV)
+    ref = torch.empty(B, n_q * hd, device=DEV, dtype=torch.bfloat16)
+    ops.attention_plain(qf, ref, n_q, n_kv, hd, k_cache, v_cache, tok_pos, tok_seq, bt, 0)
+    for n_split in (1, 2):
+        out = torch.zeros_like(ref)
+        scratch = torch.empty(ops.attention_decode_scratch(B, n_q, hd, n_split), device=DEV)
+        for _ in range(3):  # the race this guards against depended on timing
+            ops.attention_decode(qf, out, n_q, n_kv, hd, k_cache, v_cache, tok_pos, tok_seq, bt, 0, scratch, n_split)
+            close(out.float(), ref.float(), 1e-2)
+        for s in range(B):
+            close(out[s].float().view(n_q, hd)[0], far_vals[s], 2e-2)
+    ops.attention_decode_check()
+
+
 def test_attention_decode_window_and_far_key():
     from odin_infer_b200.csrc import ops
     n_q, n_kv, hd, n = 4, 2, 64, 300
