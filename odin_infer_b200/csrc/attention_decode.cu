@@ -17,7 +17,10 @@
 // Scratch: partial results [sequence][query head][split] of head_dim + 2 floats, in
 // memory the caller provides.
 #include "attn_common.cuh"
+#include "head_math.cuh"
 #include <math_constants.h>
+
+#include <type_traits>
 
 namespace {
 
@@ -239,6 +242,20 @@ struct DecodeTcParams {
     int n_split;
     int* error;
     int* counters;  // one per (token, kv head), zero between launches: how many splits have written their partial
+    // With head preparation inside the kernel (PREP): q, k and v come from the fused projection's
+    // output, [n_parts][tokens, (Hq + 2 Hkv) hd] partial sums; the new key and value go to the cache.
+    const void* qkv;
+    size_t qkv_row_stride, qkv_part_stride;
+    int qkv_parts;
+    VecRef q_norm, k_norm;
+    int has_norm;
+    float eps;
+    const float* cos_t;
+    const float* sin_t;
+    int table_len;
+    bf16* k_cache;
+    bf16* v_cache;
+    int write_kv;
 };
 
 // The splits of one (token, kv head) meet here once their partials are written: the one that
@@ -306,11 +323,18 @@ struct DecodeTcSmem {
     static_assert(SLOTS <= 7, "barriers and the flag share 64 bytes");
 };
 
-template <int HD, int SLOTS>
+// PREP 0: q is given and the cache is complete.  PREP 1 (32-bit parts) and 2 (bfloat16): the
+// kernel prepares its own heads (per-head RMSNorm and rotation, as head_prep.cu does): every
+// CTA its query heads, and the CTA whose pages include the newest one that token's key and
+// value, which it writes to the cache and into its own copy of the page.  The kernel before it
+// is then the projection itself, and every page can be requested before that one is done.
+template <int HD, int SLOTS, int PREP>
 __global__ void __launch_bounds__(128)
 attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                       const DecodeTcParams p) {
     using namespace attn;
+    using TI = typename std::conditional<PREP == 2, bf16, float>::type;
+    constexpr int VEC = HD / 32;
     using L = DecodeTcSmem<HD, SLOTS>;
     constexpr int TILE = L::TILE, SLOT = L::SLOT, BT_KEEP = L::BT_KEEP, OS = L::OS;
     constexpr int KB = HD / 16, NB_O = HD / 8;
@@ -380,15 +404,51 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     __syncthreads();
     if (threadIdx.x == 0)
         for (int i = 0; i < SLOTS && i < n_here; ++i)
-            if (pa + i != p_last) issue(i, i);
-    pdl_wait();
-    for (int idx = threadIdx.x; idx < 16 * (HD / 8); idx += 128) {
-        const int r = idx / (HD / 8), c = idx % (HD / 8);
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < g) v = *reinterpret_cast<const uint4*>(p.q + (size_t)t * p.q_stride + (size_t)(h0 + r) * HD + c * 8);
-        *reinterpret_cast<uint4*>(sQ + q_off(r, c * 8)) = v;
+            if (PREP != 0 || pa + i != p_last) issue(i, i);
+    float new_k[VEC], new_v[VEC];  // PREP: the newest key and value, in the warp that takes the last page
+    const bool has_last = (p_last >= pa && p_last < pb);
+    const int last_warp = (p_last - pa) & 3;
+    if (PREP == 0) {
+        pdl_wait();
+        for (int idx = threadIdx.x; idx < 16 * (HD / 8); idx += 128) {
+            const int r = idx / (HD / 8), c = idx % (HD / 8);
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < g) v = *reinterpret_cast<const uint4*>(p.q + (size_t)t * p.q_stride + (size_t)(h0 + r) * HD + c * 8);
+            *reinterpret_cast<uint4*>(sQ + q_off(r, c * 8)) = v;
+        }
+        if (threadIdx.x == 0 && has_last && p_last - pa < SLOTS) issue(p_last - pa, p_last - pa);
+    } else {
+        // before the wait: constants of this token's position and the norms' weights
+        const bool in_table = (pos >= 0 && pos < p.table_len);
+        float c[VEC], sn[VEC], wq[VEC], wk[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) { c[e] = 1.f; sn[e] = 0.f; wq[e] = 1.f; wk[e] = 1.f; }
+        if (in_table) {
+            headmath::load_vec<VEC>(p.cos_t + (size_t)pos * (HD / 2) + (lane & 15) * VEC, c);
+            headmath::load_vec<VEC>(p.sin_t + (size_t)pos * (HD / 2) + (lane & 15) * VEC, sn);
+        }
+        if (p.has_norm) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) { wq[e] = p.q_norm.at(lane * VEC + e); wk[e] = p.k_norm.at(lane * VEC + e); }
+        }
+        for (int idx = threadIdx.x; idx < 16 * (HD / 8); idx += 128)
+            *reinterpret_cast<uint4*>(sQ + idx * 16) = make_uint4(0, 0, 0, 0);
+        __syncthreads();
+        pdl_wait();
+        const TI* row = reinterpret_cast<const TI*>(p.qkv) + (size_t)t * p.qkv_row_stride + lane * VEC;
+        for (int r = warp; r < g; r += 4) {
+            float v[VEC], o[VEC];
+            headmath::load_parts<VEC, TI>(row + (size_t)(h0 + r) * HD, p.qkv_parts, p.qkv_part_stride, v);
+            headmath::norm_rotate<VEC>(v, p.has_norm != 0, wq, p.eps, in_table, c, sn, lane, o);
+            headmath::store_vec_bf16<VEC>(reinterpret_cast<bf16*>(sQ + q_off(r, lane * VEC)) + ((lane * VEC) & 7), o);
+        }
+        if (has_last && warp == last_warp) {
+            float v[VEC];
+            headmath::load_parts<VEC, TI>(row + (size_t)(p.Hq + kvh) * HD, p.qkv_parts, p.qkv_part_stride, v);
+            headmath::norm_rotate<VEC>(v, p.has_norm != 0, wk, p.eps, in_table, c, sn, lane, new_k);
+            headmath::load_parts<VEC, TI>(row + (size_t)(p.Hq + p.Hkv + kvh) * HD, p.qkv_parts, p.qkv_part_stride, new_v);
+        }
     }
-    if (threadIdx.x == 0 && p_last >= pa && p_last < pb && p_last - pa < SLOTS) issue(p_last - pa, p_last - pa);
     __syncthreads();
 
     uint32_t qa[KB][4];
@@ -426,6 +486,19 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         uint8_t* sK = smem + slot * SLOT;
         uint8_t* sV = sK + TILE;
         const uint32_t sK_u = tc::smem_u32(sK), sV_u = tc::smem_u32(sV);
+        if (PREP != 0 && pg == p_last) {
+            // the newest key and value: into this CTA's copy of the page, and into the cache
+            const int rrow = pos % PAGE_T;
+            headmath::store_vec_bf16<VEC>(reinterpret_cast<bf16*>(sK + tile_off(rrow, lane * VEC)), new_k);
+            headmath::store_vec_bf16<VEC>(reinterpret_cast<bf16*>(sV + tile_off(rrow, lane * VEC)), new_v);
+            if (p.write_kv) {
+                const int page = (i < BT_KEEP) ? s_pages[i] : bt[pa + i];
+                const size_t at = (((size_t)page * p.Hkv + kvh) * PAGE_T + rrow) * HD + lane * VEC;
+                headmath::store_vec_bf16<VEC>(p.k_cache + at, new_k);
+                headmath::store_vec_bf16<VEC>(p.v_cache + at, new_v);
+            }
+            __syncwarp();
+        }
         if (pg == p_last) {
             // slots past the sequence's end may hold a stale Inf or NaN; 0 x NaN is NaN: clear those value rows
             const int valid = t_hi - pg * PAGE_T;
@@ -646,25 +719,40 @@ int* device_symbol(const T& symbol) {
 int* decode_error_flag() { return device_symbol(g_decode_error); }
 int* split_counters() { return device_symbol(g_split_counters); }
 
-template <int HD, int SLOTS>
+template <int HD, int SLOTS, int PREP>
 int launch_decode_tc_slots(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeTcParams& p, dim3 grid, cudaStream_t s) {
     constexpr int SMEM = DecodeTcSmem<HD, SLOTS>::BYTES;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_tc_kernel<HD, SLOTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_tc_kernel<HD, SLOTS, PREP>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    odin_launch(attn_decode_tc_kernel<HD, SLOTS>, grid, dim3(128), (size_t)SMEM, s, mk, mv, p);
+    odin_launch(attn_decode_tc_kernel<HD, SLOTS, PREP>, grid, dim3(128), (size_t)SMEM, s, mk, mv, p);
     ODIN_LAUNCH_CHECK();
     return 0;
 }
+
+// What head preparation inside the kernel needs (see DecodeTcParams).
+struct PrepArgs {
+    const void* qkv;
+    int in_dtype, parts;
+    size_t row_stride, part_stride;
+    VecRef q_norm, k_norm;
+    int has_norm;
+    float eps;
+    const float* cos_t;
+    const float* sin_t;
+    int table_len;
+    int write_kv;
+};
 
 template <int HD>
 int launch_decode_tc(const bf16* q, size_t q_stride, bf16* out, size_t out_stride, int B, int Hq, int Hkv,
                      const bf16* k_cache, const bf16* v_cache, int n_pages, const int* tok_pos, const int* tok_seq,
                      const int* block_table, int bt_stride, int window, float* part_acc, float* part_ml, int n_split,
-                     cudaStream_t s) {
+                     cudaStream_t s, const PrepArgs* prep = nullptr) {
     // the result is written with 8-byte stores
     if ((out_stride % 4) != 0 || (((uintptr_t)out) & 7) != 0) return ODIN_ERR_UNSUPPORTED;
     CUtensorMap mk, mv;
@@ -673,6 +761,7 @@ int launch_decode_tc(const bf16* q, size_t q_stride, bf16* out, size_t out_strid
     if ((rc = attn::cache_map(&mk, k_cache, rows, HD))) return rc;
     if ((rc = attn::cache_map(&mv, v_cache, rows, HD))) return rc;
     DecodeTcParams p;
+    std::memset(&p, 0, sizeof(p));
     p.q = q; p.q_stride = q_stride; p.out = out; p.out_stride = out_stride;
     p.Hq = Hq; p.Hkv = Hkv; p.tok_pos = tok_pos; p.tok_seq = tok_seq;
     p.block_table = block_table; p.bt_stride = bt_stride; p.window = window;
@@ -681,6 +770,14 @@ int launch_decode_tc(const bf16* q, size_t q_stride, bf16* out, size_t out_strid
     p.error = decode_error_flag();
     p.counters = split_counters();
     if (n_split > 1 && (p.counters == nullptr || (long long)B * Hkv > SPLIT_COUNTERS)) return ODIN_ERR_UNSUPPORTED;
+    int mode = 0;
+    if (prep != nullptr) {
+        p.qkv = prep->qkv; p.qkv_row_stride = prep->row_stride; p.qkv_part_stride = prep->part_stride;
+        p.qkv_parts = prep->parts; p.q_norm = prep->q_norm; p.k_norm = prep->k_norm; p.has_norm = prep->has_norm;
+        p.eps = prep->eps; p.cos_t = prep->cos_t; p.sin_t = prep->sin_t; p.table_len = prep->table_len;
+        p.k_cache = const_cast<bf16*>(k_cache); p.v_cache = const_cast<bf16*>(v_cache); p.write_kv = prep->write_kv;
+        mode = prep->in_dtype == ODIN_F32 ? 1 : 2;
+    }
     dim3 grid(n_split, Hkv, B);
     // few CTAs: one per SM with a deep ring; many: two per SM with a ring half as deep
     static int sms = 0;
@@ -690,9 +787,14 @@ int launch_decode_tc(const bf16* q, size_t q_stride, bf16* out, size_t out_strid
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
     }
     const long long ctas = (long long)n_split * Hkv * B;
-    if (ctas > sms) rc = launch_decode_tc_slots<HD, 3>(mk, mv, p, grid, s);
-    else rc = launch_decode_tc_slots<HD, 6>(mk, mv, p, grid, s);
-    return rc;
+    const bool deep = ctas <= sms;
+#define GO(PREP)                                                                  \
+    (deep ? launch_decode_tc_slots<HD, 6, PREP>(mk, mv, p, grid, s)               \
+          : launch_decode_tc_slots<HD, 3, PREP>(mk, mv, p, grid, s))
+    if (mode == 0) return GO(0);
+    if (mode == 1) return GO(1);
+    return GO(2);
+#undef GO
 }
 
 }  // namespace
@@ -759,6 +861,49 @@ extern "C" int odin_attention_decode(const void* q, long long q_row_stride, void
         default: return ODIN_ERR_UNSUPPORTED;
     }
 #undef CALL
+}
+
+// Decode attention that prepares its own heads: qkv is the fused projection's output for the
+// step's B tokens, [parts][B, (Hq + 2 Hkv) hd] of in_dtype (32-bit partial sums, parts
+// part_stride elements apart, or one bfloat16 part); q and k get their per-head RMSNorm
+// (has_norm) and the rotation by the position's angles (cos_t, sin_t: [table_len, hd/2]);
+// the new key and value are written to the cache (write_kv) and attended to.  The same
+// arithmetic as odin_head_prep followed by odin_attention_decode, in one kernel.  Refuses
+// (ODIN_ERR_UNSUPPORTED) what the tensor-core kernel does not take; the caller then runs the two.
+extern "C" int odin_attention_decode_fused(const void* qkv, int in_dtype, int parts, long long part_stride,
+                                           long long row_stride, void* out, long long out_row_stride, int B, int Hq,
+                                           int Hkv, int hd, const void* q_norm_w, const void* k_norm_w, int w_dtype,
+                                           int has_norm, float eps, const float* cos_t, const float* sin_t, int rot,
+                                           int table_len, void* k_cache, void* v_cache, int page_size, int n_pages,
+                                           const int* tok_pos, const int* tok_seq, const int* block_table,
+                                           int bt_stride, int window, float* scratch, int n_split, int write_kv,
+                                           void* stream) {
+    if (B <= 0) return 0;
+    if (Hkv <= 0 || Hq % Hkv != 0 || n_split < 1 || scratch == nullptr || parts < 1) return ODIN_ERR_BAD_ARG;
+    if (B > 65535 || Hq > 65535 || n_split > 65535) return ODIN_ERR_UNSUPPORTED;
+    const bool in_ok = (in_dtype == ODIN_F32) || (in_dtype == ODIN_BF16 && parts == 1);
+    if (!((hd == 64 || hd == 128) && rot == hd && Hq / Hkv <= 16 && page_size == attn::PAGE_T && n_pages > 0 && in_ok &&
+          (row_stride % 4) == 0 && (part_stride % 4) == 0 && (out_row_stride % 4) == 0 &&
+          ((((uintptr_t)qkv) | ((uintptr_t)cos_t) | ((uintptr_t)sin_t) | ((uintptr_t)scratch)) & 15) == 0 &&
+          (((uintptr_t)out) & 7) == 0))
+        return ODIN_ERR_UNSUPPORTED;
+    PrepArgs prep;
+    prep.qkv = qkv; prep.in_dtype = in_dtype; prep.parts = parts;
+    prep.row_stride = (size_t)row_stride; prep.part_stride = (size_t)part_stride;
+    prep.q_norm = VecRef{q_norm_w, w_dtype == ODIN_BF16};
+    prep.k_norm = VecRef{k_norm_w, w_dtype == ODIN_BF16};
+    prep.has_norm = has_norm; prep.eps = eps; prep.cos_t = cos_t; prep.sin_t = sin_t; prep.table_len = table_len;
+    prep.write_kv = write_kv;
+    cudaStream_t s = (cudaStream_t)stream;
+    float* part_acc = scratch;
+    float* part_ml = scratch + (size_t)B * Hq * n_split * hd;
+    if (hd == 64)
+        return launch_decode_tc<64>(nullptr, 0, (bf16*)out, (size_t)out_row_stride, B, Hq, Hkv, (const bf16*)k_cache,
+                                    (const bf16*)v_cache, n_pages, tok_pos, tok_seq, block_table, bt_stride, window,
+                                    part_acc, part_ml, n_split, s, &prep);
+    return launch_decode_tc<128>(nullptr, 0, (bf16*)out, (size_t)out_row_stride, B, Hq, Hkv, (const bf16*)k_cache,
+                                 (const bf16*)v_cache, n_pages, tok_pos, tok_seq, block_table, bt_stride, window,
+                                 part_acc, part_ml, n_split, s, &prep);
 }
 
 // ---------------------------------------------------------------------------

@@ -43,6 +43,7 @@ struct GemmParams {
     int tiles_x, tiles_y;
     int n_split, kb_per_split, kb_total;
     int dual_offset;       // DUAL: first row of the second Y tile's matrix half
+    int stages;            // length of the ring of stages (0: as many as fit)
     int* error;            // set when a wait runs out
 };
 
@@ -114,7 +115,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     static_assert(!DUAL || MODE == 0, "the SwiGLU epilogue exists for mode 0 only");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE);
+    const uint32_t n_stages = (uint32_t)p.stages;  // at most C::STAGES: the ring may be shorter to leave shared memory to a neighbour
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + n_stages * C::STAGE);
     uint64_t* full = bars;                        // [STAGES] TMA landed
     uint64_t* empty = bars + C::STAGES;           // [STAGES] MMAs that read the stage are done
     uint64_t* acc_full = bars + 2 * C::STAGES;    // [ACC_BUFS] accumulator complete
@@ -126,7 +128,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     pdl_trigger();  // the next kernel may take its place; it waits for this one before it touches memory
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C::STAGES; ++s) {
+        for (int s = 0; s < C::STAGES; ++s) {  // all of them: the places are there whatever the ring's length
             tc::mbar_init(&full[s], 1);
             tc::mbar_init(&empty[s], 1);
         }
@@ -160,7 +162,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 const int s = (int)(w % p.n_split);
                 const int tx = (int)((w / p.n_split) % p.tiles_x), ty = (int)((w / p.n_split) / p.tiles_x);
                 const int kb0 = s * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
-                pre = min(C::STAGES, kb1 - kb0);
+                pre = min((int)n_stages, kb1 - kb0);
                 for (int i = 0; i < pre; ++i) {
                     tc::mbar_expect_tx(&full[i], C::STAGE);
                     tc::tma_load_2d(smem + i * C::STAGE, &map_x, (kb0 + i) * BK, tx * BM, &full[i]);
@@ -179,7 +181,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (pre > 0) {  // already requested above
                         --pre;
-                        if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                        if (++stage == n_stages) { stage = 0; phase ^= 1; }
                         continue;
                     }
                     if (!tc::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { report(p.error, 1, (int)w, kb, stage, MODE, BN); ok = false; break; }
@@ -189,12 +191,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     tc::tma_load_2d(sx, &map_x, kb * BK, tx * BM, &full[stage]);
                     tc::tma_load_2d(sy, &map_y, kb * BK, ty * BN, &full[stage]);
                     if (DUAL) tc::tma_load_2d(sy + C::STAGE_Y1, &map_y, kb * BK, p.dual_offset + ty * BN, &full[stage]);
-                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                    if (++stage == n_stages) { stage = 0; phase ^= 1; }
                 }
             }
             if (!ok) {
                 // aborted: let the copies already in flight land before the CTA's memory is released
-                for (int s2 = 0; s2 < C::STAGES; ++s2)
+                for (uint32_t s2 = 0; s2 < n_stages; ++s2)
                     for (uint32_t i = 0; i < 4096; ++i)
                         if (tc::mbar_try_wait(&full[s2], 0) || tc::mbar_try_wait(&full[s2], 1)) break;
             }
@@ -226,7 +228,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 if (!ok) { if (lane == 0) report(p.error, 3, (int)w, kb, stage, MODE, BN); break; }
                 tc::fence_after_sync();
                 const uint32_t cur = stage;
-                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                if (++stage == n_stages) { stage = 0; phase ^= 1; }
                 ready = __all_sync(0xffffffffu, tc::mbar_test_wait(&full[stage], phase));
                 if (tc::elect_one()) {
                     const uint32_t ax = tc::smem_u32(smem + cur * C::STAGE);
@@ -420,7 +422,10 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, cu
     }
     const long long items = (long long)p.tiles_x * p.tiles_y * p.n_split;
     const int grid = (int)(items < sm_count() ? items : sm_count());
-    odin_launch(kern, dim3(grid), dim3(192), (size_t)C::SMEM, s, mx, my, p);
+    GemmParams q = p;
+    q.stages = (p.stages >= 2 && p.stages < C::STAGES) ? p.stages : C::STAGES;
+    const size_t smem = (size_t)C::SMEM - (size_t)(C::STAGES - q.stages) * C::STAGE;
+    odin_launch(kern, dim3(grid), dim3(192), smem, s, mx, my, q);
     ODIN_LAUNCH_CHECK();
     return 0;
 }
@@ -444,9 +449,11 @@ int dispatch_bn(int bn, const CUtensorMap& mx, const CUtensorMap& my, const Gemm
 // split_stride elements apart.  mode 0: tokens on the 128-row side; mode 1: weights on
 // it (for M <= bn).  bn: the tile's N side: 16..256.  Strides and K must be multiples
 // of 8 elements and the pointers 16-byte aligned (TMA), else ODIN_ERR_UNSUPPORTED.
+// stages: the length of the ring of shared-memory stages; 0: as many as fit (the product then has the SM to
+// itself), fewer to let a CTA of the kernel before or after it share the SM.
 extern "C" int odin_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, long long lda,
                             long long ldw, long long ldc, int mode, int bn, int n_split, long long split_stride,
-                            void* stream) {
+                            int stages, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || n_split < 1) return ODIN_ERR_BAD_ARG;
     if ((lda % 8) || (ldw % 8) || (K % 8) || (((uintptr_t)A) & 15) || (((uintptr_t)W) & 15)) return ODIN_ERR_UNSUPPORTED;
@@ -463,6 +470,7 @@ extern "C" int odin_gemm_tc(const void* A, const void* W, void* C, int c_dtype, 
     if ((p.kb_total + p.kb_per_split - 1) / p.kb_per_split != n_split) return ODIN_ERR_BAD_ARG;  // an empty part
     p.n_split = n_split;
     p.dual_offset = 0;
+    p.stages = stages;
     p.error = error_flag();
     CUtensorMap mx, my;
     int rc;
@@ -503,6 +511,7 @@ extern "C" int odin_gemm_tc_swiglu(const void* A, const void* W, void* C, int c_
     p.kb_total = (K + BK - 1) / BK;
     p.kb_per_split = p.kb_total;
     p.n_split = 1;
+    p.stages = 0;
     p.dual_offset = I;
     p.error = error_flag();
     p.rows_x = M;

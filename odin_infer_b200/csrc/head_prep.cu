@@ -11,6 +11,7 @@
 // Cache layout of one layer: [page][kv head][slot in page][hd]; a sequence's
 // pages are named by its row of the block table.
 #include "common.cuh"
+#include "head_math.cuh"
 
 #define HP_WARPS 4
 #define HP_MAX_HD 512
@@ -93,42 +94,8 @@ head_prep_kernel(const TI* qkv, int n_split, size_t split_stride, T* q_out,  // 
 // VEC = hd/32 consecutive elements in registers, the rotation partner (i +- hd/2) lives in
 // lane ^ 16, and rows move with vector loads and stores.  The input is bfloat16, or 32-bit
 // partial sums of a split product that are added first, in order.  Same arithmetic as above.
-template <int VEC>
-__device__ __forceinline__ void load_vec(const bf16* p, float (&v)[VEC]) {
-    if (VEC == 4) {
-        const uint2 raw = *reinterpret_cast<const uint2*>(p);
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-        v[0] = a.x; v[1] = a.y; v[2 % VEC] = b.x; v[3 % VEC] = b.y;
-    } else {
-        const uint32_t raw = *reinterpret_cast<const uint32_t*>(p);
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw));
-        v[0] = a.x; v[1] = a.y;
-    }
-}
-template <int VEC>
-__device__ __forceinline__ void load_vec(const float* p, float (&v)[VEC]) {
-    if (VEC == 4) {
-        const float4 a = *reinterpret_cast<const float4*>(p);
-        v[0] = a.x; v[1] = a.y; v[2 % VEC] = a.z; v[3 % VEC] = a.w;
-    } else {
-        const float2 a = *reinterpret_cast<const float2*>(p);
-        v[0] = a.x; v[1] = a.y;
-    }
-}
-template <int VEC>
-__device__ __forceinline__ void store_vec_bf16(bf16* p, const float (&o)[VEC]) {
-    if (VEC == 4) {
-        __nv_bfloat162 a = __floats2bfloat162_rn(o[0], o[1]), b = __floats2bfloat162_rn(o[2 % VEC], o[3 % VEC]);
-        uint2 u;
-        u.x = *reinterpret_cast<uint32_t*>(&a);
-        u.y = *reinterpret_cast<uint32_t*>(&b);
-        *reinterpret_cast<uint2*>(p) = u;
-    } else {
-        __nv_bfloat162 a = __floats2bfloat162_rn(o[0], o[1]);
-        *reinterpret_cast<uint32_t*>(p) = *reinterpret_cast<uint32_t*>(&a);
-    }
-}
+using headmath::load_vec;
+using headmath::store_vec_bf16;
 
 template <int VEC, typename TI>
 __global__ void __launch_bounds__(HP_WARPS * 32)
@@ -176,43 +143,13 @@ head_prep_fast_kernel(const TI* qkv, int n_split, size_t split_stride, bf16* q_o
     if (!active) return;
     const TI* src = qkv + (size_t)t * row_stride + (size_t)head * HD + lane * VEC;
     float v[VEC];
-    load_vec<VEC>(src, v);
-    // the parts of a split product, four loads in flight at a time, added in their order
-    for (int s0 = 1; s0 < n_split; s0 += 4) {
-        float w2[4][VEC];
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-            if (s0 + u < n_split) load_vec<VEC>(src + (size_t)(s0 + u) * split_stride, w2[u]);
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-            if (s0 + u < n_split) {
-#pragma unroll
-                for (int e = 0; e < VEC; ++e) v[e] += w2[u][e];
-            }
-    }
+    headmath::load_parts<VEC, TI>(src, n_split, split_stride, v);
     if (!is_q && !is_k) {  // value head: stored as it is
         store_vec_bf16<VEC>(dst, v);
         return;
     }
-    if (has_norm) {
-        float ss = 0.f;
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) ss += v[e] * v[e];
-        ss = warp_sum(ss);
-        ss /= (float)HD;
-        ss += eps;
-        const float r = 1.0f / sqrtf(ss);
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) v[e] = wn[e] * (r * v[e]);
-    }
     float o[VEC];
-#pragma unroll
-    for (int e = 0; e < VEC; ++e) {
-        const float other = __shfl_xor_sync(0xffffffffu, v[e], 16);
-        // first half: x c - y s with (x, y) = (mine, other); second half: x s + y c with (x, y) = (other, mine)
-        if (in_table) o[e] = (lane < 16) ? (v[e] * c[e] - other * sn[e]) : (other * sn[e] + v[e] * c[e]);
-        else o[e] = v[e];
-    }
+    headmath::norm_rotate<VEC>(v, has_norm != 0, wn, eps, in_table, c, sn, lane, o);
     store_vec_bf16<VEC>(dst, o);
 }
 

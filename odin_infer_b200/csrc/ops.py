@@ -156,12 +156,15 @@ def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, bn: int, n_split: int = 1) -> None:
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, bn: int, n_split: int = 1,
+            stages: int = 0) -> None:
     """out = a[M, K] @ w[N, K]^T on the tcgen05 tensor cores (bfloat16 in, 32-bit accumulation).
 
     mode 0: tokens on the 128-row side of the MMA, tiles of bn weight rows.
     mode 1: weight rows on the 128-row side, tiles of bn tokens (M <= bn is usual).
     n_split > 1: out is float32 [n_split, M, N]; slice s holds the partial sum of K part s.
+    stages: length of the kernel's ring of shared-memory stages; 0: as many as fit, fewer to
+    leave room on the SM for a CTA of the neighbouring kernel.
     """
     M, K = a.shape
     N = w.shape[0]
@@ -178,7 +181,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, bn: 
     _check(_fn("gemm_tc", "odin_gemm_tc")(
         _ptr(a), _ptr(w), _ptr(out), c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K),
         c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(ldc), c_int(mode), c_int(bn), c_int(n_split),
-        c_longlong(stride), _stream()), "gemm_tc")
+        c_longlong(stride), c_int(stages), _stream()), "gemm_tc")
 
 
 def gemm_tc_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
@@ -290,6 +293,47 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int, he
         c_int(head_dim), _ptr(k_cache), _ptr(v_cache), c_int(PAGE), c_int(k_cache.shape[0]), _ptr(tok_pos),
         _ptr(tok_seq), _ptr(block_table), c_int(block_table.stride(0)), c_int(window), _ptr(scratch), c_int(n_split),
         _stream()), "attention_decode", kernels=1 if head_dim in (64, 128) and n_q // n_kv <= 16 else 2)
+
+
+def attention_decode_fused(qkv: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
+                           q_norm: torch.Tensor | None, k_norm: torch.Tensor | None, eps: float, cos: torch.Tensor,
+                           sin: torch.Tensor, rotary_dim: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                           tok_pos: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor, window: int,
+                           scratch: torch.Tensor, n_split: int, write_kv: bool = True) -> bool:
+    """`head_prep` and `attention_decode` in one kernel, for one token per sequence: qkv is the
+    fused projection's output ([B, width] bfloat16, or float32 partial sums [parts, B, width]).
+    Returns False, and launches nothing, where the tensor-core kernel does not apply; the
+    caller then runs the two kernels."""
+    width = (n_q + 2 * n_kv) * head_dim
+    if qkv.dim() == 3:
+        parts, B = qkv.shape[0], qkv.shape[1]
+        if not (qkv.is_contiguous() and qkv.shape[2] == width and qkv.dtype == torch.float32):
+            return False
+        part_stride, row_stride = B * width, width
+    else:
+        parts, B, part_stride, row_stride = 1, qkv.shape[0], 0, qkv.stride(0)
+        if not (qkv.stride(1) == 1 and qkv.shape[1] == width and qkv.dtype in (torch.bfloat16, torch.float32)):
+            return False
+    if not (out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16 and out.stride(1) == 1
+            and tuple(out.shape) == (B, n_q * head_dim) and k_cache.is_contiguous() and v_cache.is_contiguous()
+            and tuple(k_cache.shape[1:]) == (n_kv, PAGE, head_dim) and cos.dtype == sin.dtype == torch.float32):
+        return False
+    has_norm = q_norm is not None
+    if has_norm and not (k_norm is not None and q_norm.dtype == k_norm.dtype and q_norm.numel() == head_dim
+                         and k_norm.numel() == head_dim):
+        return False
+    assert scratch.dtype == torch.float32 and scratch.numel() >= attention_decode_scratch(B, n_q, head_dim, n_split)
+    code = _fn("attention_decode", "odin_attention_decode_fused")(
+        _ptr(qkv), c_int(dtype_code(qkv.dtype)), c_int(parts), c_longlong(part_stride), c_longlong(row_stride),
+        _ptr(out), c_longlong(out.stride(0)), c_int(B), c_int(n_q), c_int(n_kv), c_int(head_dim), _ptr(q_norm),
+        _ptr(k_norm), c_int(dtype_code(q_norm.dtype) if has_norm else 0), c_int(1 if has_norm else 0), c_float(eps),
+        _ptr(cos), _ptr(sin), c_int(rotary_dim), c_int(cos.shape[0]), _ptr(k_cache), _ptr(v_cache), c_int(PAGE),
+        c_int(k_cache.shape[0]), _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table), c_int(block_table.stride(0)),
+        c_int(window), _ptr(scratch), c_int(n_split), c_int(1 if write_kv else 0), _stream())
+    if code == -1:  # unsupported: nothing was launched
+        return False
+    _check(code, "attention_decode_fused")
+    return True
 
 
 def attention_decode_check() -> None:

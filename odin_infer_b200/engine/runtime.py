@@ -3,6 +3,8 @@ tensors, and the choice between kernel variants for matrix products and
 attention.  Parts never choose a kernel themselves."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..csrc import ops
@@ -26,6 +28,10 @@ def choose_k_split(n_tiles: int, k_blocks: int, m: int, n_sms: int = 148, max_sp
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = parts, cost
     return best
+
+
+# ring length of a product that shares the SM with a decode attention CTA (see Runtime.linear)
+LIGHT_STAGES = int(os.environ.get("ODIN_GEMM_LIGHT_STAGES", "6"))
 
 
 def context_class_of(longest: int, page: int = 64) -> int:
@@ -70,12 +76,17 @@ class Runtime:
 
     # ---- matrix product: out[M, N] = a[M, K] @ w[N, K]^T -----------------
     def linear(self, a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
-               may_split: bool = False) -> torch.Tensor:
+               may_split: bool = False, beside_attention: bool = False) -> torch.Tensor:
         """bfloat16 operands that TMA can read go to the tcgen05 kernel, everything else
         (the 32-bit path, odd widths, tensors stored in 32-bit) to the CUDA-core kernel.
 
         may_split: the caller's consumer adds partial sums, so a product of few tokens
-        may come back as float32 [parts, M, N] (split along K to occupy every SM)."""
+        may come back as float32 [parts, M, N] (split along K to occupy every SM).
+
+        beside_attention: the product comes right before or after attention; for few tokens
+        it then keeps a shorter ring of stages, so that a CTA of the decode attention kernel
+        fits on the SM beside it and can fetch its pages (or this product its weights) while
+        the other still runs."""
         M, N, K = a.shape[0], w.shape[0], a.shape[1]
         out_dtype = out_dtype or self.dtype
         if M > 0 and ops.gemm_tc_supported(a, w):
@@ -83,12 +94,13 @@ class Runtime:
                 bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
                 n_split = choose_k_split((N + 127) // 128, (K + 63) // 64, M, self.n_sms) if may_split else 1
                 n_split = ops.gemm_tc_splits(K, n_split)
+                stages = LIGHT_STAGES if beside_attention else 0
                 if n_split > 1:
                     out = self.empty(n_split, M, N, dtype=torch.float32)
-                    ops.gemm_tc(a, w, out, 1, bn, n_split)
+                    ops.gemm_tc(a, w, out, 1, bn, n_split, stages)
                     return out
                 out = self.empty(M, N, dtype=out_dtype)
-                ops.gemm_tc(a, w, out, 1, bn)
+                ops.gemm_tc(a, w, out, 1, bn, 1, stages)
                 return out
             out = self.empty(M, N, dtype=out_dtype)
             ops.gemm_tc(a, w, out, 0, 256 if N > 128 else 128 if N > 64 else 64)
@@ -110,6 +122,23 @@ class Runtime:
         return act
 
     # ---- attention over the cache ---------------------------------------
+    def attention_with_head_prep(self, step, qkv, out, n_q, n_kv, head_dim, q_norm, k_norm, eps, cos, sin,
+                                 rotary_dim, k_line, v_line, block_table, window, write_kv) -> bool:
+        """One token per sequence in bfloat16: head preparation (per-head norm, rotation, the
+        cache write) inside the attention kernel.  False where that kernel does not apply;
+        the caller then prepares the heads and calls `attention`."""
+        if os.environ.get("ODIN_FUSED_ATTENTION", "1") == "0":  # for comparisons
+            return False
+        if not (self.dtype == torch.bfloat16 and step.all_single and head_dim in (64, 128)
+                and rotary_dim == head_dim and n_kv > 0 and n_q // n_kv <= 16 and write_kv):
+            return False
+        B = out.shape[0]
+        n_split = decode_key_splits(B, n_kv, step.max_len_after, n_sms=self.n_sms)
+        scratch = self.empty(ops.attention_decode_scratch(B, n_q, head_dim, n_split), dtype=torch.float32)
+        return ops.attention_decode_fused(qkv, out, n_q, n_kv, head_dim, q_norm, k_norm, eps, cos, sin, rotary_dim,
+                                          k_line, v_line, step.tok_pos, step.tok_seq, block_table, window, scratch,
+                                          n_split, write_kv)
+
     def attention(self, step, q, out, n_q, n_kv, head_dim, k_line, v_line, block_table, window) -> None:
         """bfloat16: one token per sequence goes to the split-key kernel, prompts (and pieces
         of prompts) to the flash kernel.  The 32-bit path and head sizes that the fast

@@ -69,17 +69,23 @@ class GQAttention(Mixer):
 
     def forward(self, rt, step, h, entry):
         T = h.shape[0]
-        qkv = rt.linear(h, self.w_qkv, may_split=True)
+        qkv = rt.linear(h, self.w_qkv, may_split=True, beside_attention=True)
         k_line, v_line, block_table = step.kv(entry)
         rot = self.pe.rotation() if self.pe is not None else None
         cos, sin, rot_dim = rot if rot is not None else (self._dummy, self._dummy, 0)
         writes = step.writes_cache(entry) and not self.kv_shared
+        o = rt.empty(T, self.n_q * self.hd)
+        # decoding: the attention kernel may prepare its heads itself
+        if not self.kv_shared and rt.attention_with_head_prep(
+                step, qkv, o, self.n_q, self.n_kv, self.hd, self.q_norm if self.qk_norm else None,
+                self.k_norm if self.qk_norm else None, self.eps, cos, sin, rot_dim, k_line, v_line, block_table,
+                self.window, writes):
+            return rt.linear(o, self.w_o, out_dtype=torch.float32, may_split=True, beside_attention=True)
         # a product of few tokens may come back as partial sums: they are added here
         q_out = rt.empty(T, self.n_q * self.hd) if qkv.dim() == 3 else None
         q = ops.head_prep(qkv, self.n_q, 0 if self.kv_shared else self.n_kv, self.hd,
                           self.q_norm if self.qk_norm else None, self.k_norm if self.qk_norm else None, self.eps,
                           cos, sin, rot_dim, step.tok_pos, step.tok_seq, block_table, k_line, v_line,
                           write_kv=writes, q_out=q_out)
-        o = rt.empty(T, self.n_q * self.hd)
         rt.attention(step, q, o, self.n_q, self.n_kv, self.hd, k_line, v_line, block_table, self.window)
-        return rt.linear(o, self.w_o, out_dtype=torch.float32, may_split=True)
+        return rt.linear(o, self.w_o, out_dtype=torch.float32, may_split=True, beside_attention=True)

@@ -124,3 +124,21 @@ def test_fused_swiglu_product(shape):
     ops.gemm_tc_swiglu(a2.bfloat16(), w2.bfloat16(), out)
     ref = (2.0 * torch.sigmoid(torch.tensor(2.0))).item() * (a2[:, 1:2].double() * w2[I:, 1].double()[None, :])
     close(out, ref, 5e-3, "fused swiglu structured")
+
+
+@pytest.mark.parametrize("stages", [2, 3, 6])
+@pytest.mark.parametrize("case", [(8, 6144, 4096, 1, 16, 3), (64, 1000, 1032, 1, 64, 1), (300, 512, 1024, 0, 256, 1)])
+def test_short_ring_gives_the_same_result(case, stages):
+    """A ring of fewer stages (room for a neighbour on the SM) changes no bit of the result."""
+    from odin_infer_b200.csrc import ops
+    M, N, K, mode, bn, n_split = case
+    torch.manual_seed(stages)
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    w = torch.randn(N, K, device=DEV).bfloat16()
+    shape = (ops.gemm_tc_splits(K, n_split), M, N) if n_split > 1 else (M, N)
+    full = torch.empty(shape, device=DEV, dtype=torch.float32)
+    short = torch.full(shape, float("nan"), device=DEV, dtype=torch.float32)
+    ops.gemm_tc(a, w, full, mode, bn, n_split)
+    ops.gemm_tc(a, w, short, mode, bn, n_split, stages)
+    ops.gemm_tc_check()
+    assert torch.equal(full, short)

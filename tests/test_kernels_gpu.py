@@ -369,6 +369,56 @@ def test_attention_decode_slots_used_again(geom, case):
     ops.attention_decode_check()
 
 
+@pytest.mark.parametrize("geom", [(32, 8, 128), (8, 2, 64), (16, 1, 128), (6, 3, 64)])
+@pytest.mark.parametrize("parts", [0, 1, 3])
+def test_attention_decode_with_head_prep_equals_the_two_kernels(geom, parts):
+    """Decode attention that prepares its own heads against head preparation followed by decode
+    attention: the same results bit for bit, in the output and in the cache; sequences whose
+    newest token opens a page, fills one, or lies in a page that comes through a reused slot;
+    a padding row; one and several key splits.  parts 0: a bfloat16 projection output."""
+    from odin_infer_b200.csrc import ops
+    n_q, n_kv, hd = geom
+    lengths = [1, 64, 65, 128, 200, 641, 1000]
+    B = len(lengths)
+    torch.manual_seed(3 + hd + parts)
+    k_cache, v_cache, bt = paged_cache(B, lengths, n_kv, hd, torch.bfloat16)
+    for s, n in enumerate(lengths):  # everything but the newest token is in the cache already
+        pages = bt[s, : (n + 63) // 64].long()
+        k_cache[pages] = torch.randn(pages.numel(), n_kv, 64, hd, device=DEV).bfloat16()
+        v_cache[pages] = torch.randn(pages.numel(), n_kv, 64, hd, device=DEV).bfloat16()
+        last = int(pages[-1])
+        k_cache[last, :, (n - 1) % 64:] = float("nan")   # the newest token's place and what lies behind it
+        v_cache[last, :, (n - 1) % 64:] = float("nan")
+    order = [3, 0, -1, 6, 1, 5, 2, 4]
+    tok_seq = torch.tensor(order, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([lengths[s] - 1 if s >= 0 else 0 for s in order], dtype=torch.int32, device=DEV)
+    T, width = len(order), (n_q + 2 * n_kv) * hd
+    if parts == 0:
+        qkv = torch.randn(T, width, device=DEV).bfloat16()
+    else:
+        qkv = torch.randn(parts, T, width, device=DEV) / math.sqrt(parts)
+    q_norm = (1 + 0.1 * torch.randn(hd, device=DEV)).bfloat16()
+    k_norm = (1 + 0.1 * torch.randn(hd, device=DEV)).bfloat16()
+    ang = torch.arange(1100, device=DEV, dtype=torch.float32)[:, None] * (1.0 / 10000 ** (torch.arange(hd // 2, device=DEV) / (hd // 2)))[None, :]
+    cos, sin = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
+    for n_split in (1, 3):
+        ka, va, kb, vb = k_cache.clone(), v_cache.clone(), k_cache.clone(), v_cache.clone()
+        scratch = torch.empty(ops.attention_decode_scratch(T, n_q, hd, n_split), device=DEV)
+        q = ops.head_prep(qkv.clone(), n_q, n_kv, hd, q_norm, k_norm, 1e-6, cos, sin, hd, tok_pos, tok_seq, bt, ka, va,
+                          q_out=torch.empty(T, n_q * hd, device=DEV, dtype=torch.bfloat16))
+        ref = torch.full((T, n_q * hd), 7.0, device=DEV, dtype=torch.bfloat16)
+        ops.attention_decode(q, ref, n_q, n_kv, hd, ka, va, tok_pos, tok_seq, bt, 0, scratch, n_split)
+        out = torch.full_like(ref, 7.0)
+        assert ops.attention_decode_fused(qkv, out, n_q, n_kv, hd, q_norm, k_norm, 1e-6, cos, sin, hd, kb, vb,
+                                          tok_pos, tok_seq, bt, 0, scratch, n_split)
+        assert torch.equal(out, ref)
+        for s, n in enumerate(lengths):  # the newest token's key and value, bit for bit
+            page, row = int(bt[s, (n - 1) // 64]), (n - 1) % 64
+            assert torch.equal(ka[page, :, row], kb[page, :, row]) and torch.equal(va[page, :, row], vb[page, :, row])
+            assert not torch.isnan(kb[page, :, row].float()).any()
+    ops.attention_decode_check()
+
+
 def test_attention_decode_window_and_far_key():
     from odin_infer_b200.csrc import ops
     n_q, n_kv, hd, n = 4, 2, 64, 300
