@@ -71,8 +71,8 @@ __device__ __forceinline__ float4 load4w(const VecRef& w, int j) {
 // The loads of a group are issued together (eight parts at a time), so that a row costs
 // one trip to memory and not one per part; the weights of the first group and the row
 // number, which no earlier kernel writes, are fetched before the wait for that kernel.
-template <typename TD, typename TO, bool VEC>
-__global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_split,
+template <typename TD, typename TO, bool VEC, int MAX_THREADS = 512>
+__global__ void __launch_bounds__(MAX_THREADS, MAX_THREADS > 512 ? 1 : 3) add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_split,
                                    size_t split_stride, VecRef w, float eps, TO* __restrict__ out,
                                    const int* __restrict__ rows, int d) {
     __shared__ float red[32];
@@ -96,13 +96,14 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(float* __restrict__ x
             float4 v = load4<float>(xr + j);
             if (delta != nullptr) {
                 const TD* dp = delta + (size_t)src * d + j;
-                for (int s0 = 0; s0 < n_split; s0 += 8) {
-                    float4 dv[8];
+                constexpr int BATCH = MAX_THREADS > 512 ? 8 : 2;  // loads in flight per thread (registers)
+                for (int s0 = 0; s0 < n_split; s0 += BATCH) {
+                    float4 dv[BATCH];
 #pragma unroll
-                    for (int u = 0; u < 8; ++u)
+                    for (int u = 0; u < BATCH; ++u)
                         if (s0 + u < n_split) dv[u] = load4<TD>(dp + (size_t)(s0 + u) * split_stride);
 #pragma unroll
-                    for (int u = 0; u < 8; ++u)
+                    for (int u = 0; u < BATCH; ++u)
                         if (s0 + u < n_split) { v.x += dv[u].x; v.y += dv[u].y; v.z += dv[u].z; v.w += dv[u].w; }
                 }
             }
@@ -149,14 +150,17 @@ static int launch_add_rmsnorm(float* x, const void* delta, int n_split, size_t s
     const bool vec = (d % 4 == 0) && ((((uintptr_t)x) | ((uintptr_t)delta) | ((uintptr_t)out) | ((uintptr_t)w.p)) % 16 == 0) &&
                      (split_stride % 4 == 0);
     if (vec) {
-        const int threads = d >= 4096 ? 1024 : (d >= 2048 ? 512 : (d >= 1024 ? 256 : 128));
+        // few rows (decoding): the whole row in one pass of a large block, a chain of latencies;
+        // many rows (prompts): smaller blocks, more of them per SM, two passes each
+        const bool big = d >= 4096 && n_rows <= 256;
+        const int threads = big ? 1024 : (d >= 2048 ? 512 : (d >= 1024 ? 256 : 128));
+        auto kern = big ? add_rmsnorm_kernel<TD, TO, true, 1024> : add_rmsnorm_kernel<TD, TO, true, 512>;
         if (smem > 48 * 1024) {
-            cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO, true>,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;
         }
-        odin_launch(add_rmsnorm_kernel<TD, TO, true>, dim3(n_rows), dim3(threads), smem, s, x, (const TD*)delta, n_split,
-                    split_stride, w, eps, (TO*)out, rows, d);
+        odin_launch(kern, dim3(n_rows), dim3(threads), smem, s, x, (const TD*)delta, n_split, split_stride, w, eps,
+                    (TO*)out, rows, d);
     } else {
         const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
         if (smem > 48 * 1024) {

@@ -203,54 +203,95 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
     } else if (warp == 1) {
         // --------------------------------------------------------- MMA issuer
-        // The whole warp walks the loop and one elected lane issues: in code that a single lane
-        // runs alone the per-stage cost (wait, descriptors, four MMAs, commit) was 520 cycles
-        // against 350 this way, which matters when an MMA is as short as with 16 tokens.  The
-        // next stage's barrier is tested before this stage's MMAs go out, so that its latency
-        // hides behind them.
-        constexpr uint32_t idesc = tc::make_idesc_bf16(BM, BN);
-        uint32_t stage = 0, phase = 0;
-        uint32_t local = 0;
-        bool ok = true;
-        pdl_wait();  // nothing can be multiplied before the previous kernel's output exists: sleep, do not spin
-        bool ready = false;
-        for (long long w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++local) {
-            const int s = (int)(w % p.n_split);
-            const int kb0 = s * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
-            const uint32_t acc = local % ACC_BUFS, acc_phase = (local / ACC_BUFS) & 1;
-            ok = __all_sync(0xffffffffu, tc::mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag));
-            if (!ok) { if (lane == 0) report(p.error, 2, (int)w, -1, (int)acc, MODE, BN); break; }
-            tc::fence_after_sync();
-            const uint32_t tmem_d = tmem_base + acc * C::ACC_W;
-            for (int kb = kb0; kb < kb1; ++kb) {
-                if (!ready) ready = tc::mbar_wait(&full[stage], phase, abort_flag);
-                ok = __all_sync(0xffffffffu, ready);
-                if (!ok) { if (lane == 0) report(p.error, 3, (int)w, kb, stage, MODE, BN); break; }
+        if (MODE == 1) {
+            // The whole warp walks the loop and one elected lane issues: in code that a single lane
+            // runs alone the per-stage cost (wait, descriptors, four MMAs, commit) was 520 cycles
+            // against 350 this way, which matters when an MMA is as short as with 16 tokens.  The
+            // next stage's barrier is tested before this stage's MMAs go out, so that its latency
+            // hides behind them.
+            constexpr uint32_t idesc = tc::make_idesc_bf16(BM, BN);
+            uint32_t stage = 0, phase = 0;
+            uint32_t local = 0;
+            bool ok = true;
+            pdl_wait();  // nothing can be multiplied before the previous kernel's output exists: sleep, do not spin
+            bool ready = false;
+            for (long long w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++local) {
+                const int s = (int)(w % p.n_split);
+                const int kb0 = s * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                const uint32_t acc = local % ACC_BUFS, acc_phase = (local / ACC_BUFS) & 1;
+                ok = __all_sync(0xffffffffu, tc::mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag));
+                if (!ok) { if (lane == 0) report(p.error, 2, (int)w, -1, (int)acc, MODE, BN); break; }
                 tc::fence_after_sync();
-                const uint32_t cur = stage;
-                if (++stage == n_stages) { stage = 0; phase ^= 1; }
-                ready = __all_sync(0xffffffffu, tc::mbar_test_wait(&full[stage], phase));
-                if (tc::elect_one()) {
-                    const uint32_t ax = tc::smem_u32(smem + cur * C::STAGE);
-                    const uint64_t dx = tc::make_smem_desc_sw128(ax);
-                    const uint64_t dy = tc::make_smem_desc_sw128(ax + C::STAGE_X);
+                const uint32_t tmem_d = tmem_base + acc * C::ACC_W;
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!ready) ready = tc::mbar_wait(&full[stage], phase, abort_flag);
+                    ok = __all_sync(0xffffffffu, ready);
+                    if (!ok) { if (lane == 0) report(p.error, 3, (int)w, kb, stage, MODE, BN); break; }
+                    tc::fence_after_sync();
+                    const uint32_t cur = stage;
+                    if (++stage == n_stages) { stage = 0; phase ^= 1; }
+                    ready = __all_sync(0xffffffffu, tc::mbar_test_wait(&full[stage], phase));
+                    if (tc::elect_one()) {
+                        const uint32_t ax = tc::smem_u32(smem + cur * C::STAGE);
+                        const uint64_t dx = tc::make_smem_desc_sw128(ax);
+                        const uint64_t dy = tc::make_smem_desc_sw128(ax + C::STAGE_X);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        // +32 bytes per K step inside the 128-byte swizzle row: +2 in 16-byte units
-                        tc::umma_bf16(tmem_d, dx + 2 * k, dy + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-                    }
-                    if (DUAL) {
-                        const uint64_t dy2 = tc::make_smem_desc_sw128(ax + C::STAGE_X + C::STAGE_Y1);
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            // +32 bytes per K step inside the 128-byte swizzle row: +2 in 16-byte units
+                            tc::umma_bf16(tmem_d, dx + 2 * k, dy + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                        }
+                        if (DUAL) {
+                            const uint64_t dy2 = tc::make_smem_desc_sw128(ax + C::STAGE_X + C::STAGE_Y1);
 #pragma unroll
-                        for (int k = 0; k < BK / UMMA_K; ++k)
-                            tc::umma_bf16(tmem_d + BN, dx + 2 * k, dy2 + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                            for (int k = 0; k < BK / UMMA_K; ++k)
+                                tc::umma_bf16(tmem_d + BN, dx + 2 * k, dy2 + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                        }
+                        tc::umma_commit(&empty[cur]);
                     }
-                    tc::umma_commit(&empty[cur]);
+                    __syncwarp();
                 }
+                if (ok && tc::elect_one()) tc::umma_commit(&acc_full[acc]);
                 __syncwarp();
             }
-            if (ok && tc::elect_one()) tc::umma_commit(&acc_full[acc]);
-            __syncwarp();
+        } else {
+            // many tokens: an MMA of 256 columns takes 128 cycles, the issuing lane is never the limit,
+            // and a single lane that walks the loop alone measured 2 % faster than the converged warp
+            if (lane == 0) {
+                constexpr uint32_t idesc = tc::make_idesc_bf16(BM, BN);
+                uint32_t stage = 0, phase = 0;
+                uint32_t local = 0;
+                bool ok = true;
+                pdl_wait();  // nothing can be multiplied before the previous kernel's output exists: sleep, do not spin
+                for (long long w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++local) {
+                    const int s = (int)(w % p.n_split);
+                    const int kb0 = s * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                    const uint32_t acc = local % ACC_BUFS, acc_phase = (local / ACC_BUFS) & 1;
+                    if (!tc::mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { report(p.error, 2, (int)w, -1, (int)acc, MODE, BN); ok = false; break; }
+                    tc::fence_after_sync();
+                    const uint32_t tmem_d = tmem_base + acc * C::ACC_W;
+                    for (int kb = kb0; kb < kb1; ++kb) {
+                        if (!tc::mbar_wait(&full[stage], phase, abort_flag)) { report(p.error, 3, (int)w, kb, stage, MODE, BN); ok = false; break; }
+                        tc::fence_after_sync();
+                        const uint32_t ax = tc::smem_u32(smem + stage * C::STAGE);
+                        const uint64_t dx = tc::make_smem_desc_sw128(ax);
+                        const uint64_t dy = tc::make_smem_desc_sw128(ax + C::STAGE_X);
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            // +32 bytes per K step inside the 128-byte swizzle row: +2 in 16-byte units
+                            tc::umma_bf16(tmem_d, dx + 2 * k, dy + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                        }
+                        if (DUAL) {
+                            const uint64_t dy2 = tc::make_smem_desc_sw128(ax + C::STAGE_X + C::STAGE_Y1);
+#pragma unroll
+                            for (int k = 0; k < BK / UMMA_K; ++k)
+                                tc::umma_bf16(tmem_d + BN, dx + 2 * k, dy2 + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                        }
+                        tc::umma_commit(&empty[stage]);
+                        if (++stage == n_stages) { stage = 0; phase ^= 1; }
+                    }
+                    if (ok) tc::umma_commit(&acc_full[acc]);
+                }
+            }
         }
     } else {
         // ------------------------------------------------------------ epilogue
