@@ -31,7 +31,7 @@ GROUPS = {
     "head_prep": ["head_prep.cu"],
     "attention_plain": ["attention_plain.cu"],
     "sampling": ["sampling.cu"],
-    "gemm_tc": ["gemm_tc.cu"],
+    "gemm_tc": ["gemm_tc.cu", "gemm_tc2.cu"],
     "attention_decode": ["attention_decode.cu"],
     "attention_prefill": ["attention_prefill.cu", "attention_prefill_tc.cu"],
 }

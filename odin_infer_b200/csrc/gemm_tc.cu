@@ -257,7 +257,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             // many tokens: an MMA of 256 columns takes 128 cycles, the issuing lane is never the limit,
             // and a single lane that walks the loop alone measured 2 % faster than the converged warp
             if (lane == 0) {
-                constexpr uint32_t idesc = tc::make_idesc_bf16(BM, BN);
+                // DUAL: the gate tile and the up tile lie one after the other in shared memory: one MMA over
+                // both, gate in the accumulator's columns [0, BN), up in [BN, 2 BN)
+                constexpr uint32_t idesc = tc::make_idesc_bf16(BM, DUAL ? 2 * BN : BN);
                 uint32_t stage = 0, phase = 0;
                 uint32_t local = 0;
                 bool ok = true;
@@ -279,12 +281,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         for (int k = 0; k < BK / UMMA_K; ++k) {
                             // +32 bytes per K step inside the 128-byte swizzle row: +2 in 16-byte units
                             tc::umma_bf16(tmem_d, dx + 2 * k, dy + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-                        }
-                        if (DUAL) {
-                            const uint64_t dy2 = tc::make_smem_desc_sw128(ax + C::STAGE_X + C::STAGE_Y1);
-#pragma unroll
-                            for (int k = 0; k < BK / UMMA_K; ++k)
-                                tc::umma_bf16(tmem_d + BN, dx + 2 * k, dy2 + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                         }
                         tc::umma_commit(&empty[stage]);
                         if (++stage == n_stages) { stage = 0; phase ^= 1; }
@@ -322,7 +318,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll
                     for (int q = 0; q < 32; ++q) {
                         float g = __uint_as_float(r[q]);
-                        g *= 1.0f / (1.0f + __expf(-g));
+                        g = __fdividef(g, 1.0f + __expf(-g));  // one ex2 and one rcp: the epilogue's arithmetic is not free beside the MMAs
                         r[q] = __float_as_uint(g * __uint_as_float(u[q]));
                     }
                 } else if (CH == 32) {

@@ -197,6 +197,35 @@ def gemm_tc_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) 
         "gemm_tc_swiglu")
 
 
+def gemm_tc2(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out = a[M, K] @ w[N, K]^T on pairs of SMs (tcgen05 cta_group::2, tiles of 256 x 256): for many tokens."""
+    M, K = a.shape
+    N = w.shape[0]
+    if not gemm_tc_supported(a, w):
+        raise KernelError("gemm_tc2: operands must be bfloat16 with 16-byte aligned rows (K and strides multiples of 8)")
+    assert w.shape[1] == K and tuple(out.shape) == (M, N) and out.stride(1) == 1
+    _check(_fn("gemm_tc", "odin_gemm_tc2")(
+        _ptr(a), _ptr(w), _ptr(out), c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K),
+        c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)), _stream()), "gemm_tc2")
+
+
+def gemm_tc2_swiglu_supported(inner: int) -> bool:
+    return inner % 64 == 0
+
+
+def gemm_tc2_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, I] = silu(a Wg^T) * (a Wu^T) for w_gate_up = [Wg; Wu] ([2 I, K]) on pairs of SMs; I a multiple of 64."""
+    M, K = a.shape
+    I = out.shape[1]
+    if not gemm_tc_supported(a, w_gate_up):
+        raise KernelError("gemm_tc2_swiglu: operands must be bfloat16 with 16-byte aligned rows")
+    assert w_gate_up.shape == (2 * I, K) and out.shape[0] == M and out.stride(1) == 1
+    _check(_fn("gemm_tc", "odin_gemm_tc2_swiglu")(
+        _ptr(a), _ptr(w_gate_up), _ptr(out), c_int(dtype_code(out.dtype)), c_int(M), c_int(I), c_int(K),
+        c_longlong(a.stride(0)), c_longlong(w_gate_up.stride(0)), c_longlong(out.stride(0)), _stream()),
+        "gemm_tc2_swiglu")
+
+
 def gemm_tc_check() -> None:
     """Raise if a tensor-core kernel gave up a bounded wait since the last check (synchronises)."""
     lib = build.load("gemm_tc")
@@ -208,6 +237,10 @@ def gemm_tc_check() -> None:
     if f() != 0:
         raise KernelError("gemm_tc: a device-side wait ran out (pipeline stalled); results are invalid "
                           f"[wait, block, item, k block, slot, mode, tile, grid] = {list(detail)}")
+    lib.odin_gemm_tc2_error.restype = c_int
+    if lib.odin_gemm_tc2_error(detail) != 0:
+        raise KernelError("gemm_tc2: a device-side wait ran out (pipeline stalled); results are invalid "
+                          f"[wait, block, tile, k block, slot, 2, tile, grid] = {list(detail)}")
 
 
 def head_prep(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, q_norm: torch.Tensor | None,

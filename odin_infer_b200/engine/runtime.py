@@ -30,6 +30,9 @@ def choose_k_split(n_tiles: int, k_blocks: int, m: int, n_sms: int = 148, max_sp
     return best
 
 
+# from this many tokens on a product runs on pairs of SMs (tiles of 256 token rows)
+PAIR_MIN_TOKENS = 256
+
 # ring length of a product that shares the SM with a decode attention CTA (see Runtime.linear)
 LIGHT_STAGES = int(os.environ.get("ODIN_GEMM_LIGHT_STAGES", "6"))
 
@@ -103,7 +106,10 @@ class Runtime:
                 ops.gemm_tc(a, w, out, 1, bn, 1, stages)
                 return out
             out = self.empty(M, N, dtype=out_dtype)
-            ops.gemm_tc(a, w, out, 0, 256 if N > 128 else 128 if N > 64 else 64)
+            if M >= PAIR_MIN_TOKENS and N > 128:
+                ops.gemm_tc2(a, w, out)  # tiles of 256 x 256 on pairs of SMs
+            else:
+                ops.gemm_tc(a, w, out, 0, 256 if N > 128 else 128 if N > 64 else 64)
             return out
         out = self.empty(M, N, dtype=out_dtype)
         ops.gemm_plain(a, w, out)
@@ -116,7 +122,10 @@ class Runtime:
         M = a.shape[0]
         act = self.empty(M, inner)
         if M > 128 and ops.gemm_tc_supported(a, w_gate_up):
-            ops.gemm_tc_swiglu(a, w_gate_up, act)
+            if M >= PAIR_MIN_TOKENS and ops.gemm_tc2_swiglu_supported(inner):
+                ops.gemm_tc2_swiglu(a, w_gate_up, act)
+            else:
+                ops.gemm_tc_swiglu(a, w_gate_up, act)
             return act
         ops.swiglu(self.linear(a, w_gate_up, may_split=True), act)
         return act

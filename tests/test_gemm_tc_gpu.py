@@ -142,3 +142,58 @@ def test_short_ring_gives_the_same_result(case, stages):
     ops.gemm_tc(a, w, short, mode, bn, n_split, stages)
     ops.gemm_tc_check()
     assert torch.equal(full, short)
+
+
+PAIR_CASES = [(256, 256, 64), (256, 512, 128), (300, 1000, 1032), (129, 200, 72), (2048, 768, 4096), (1000, 6144, 512),
+              (513, 264, 96)]
+
+
+@pytest.mark.parametrize("case", PAIR_CASES)
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_pair_kernel_ladder(case, out_dtype):
+    """The two-CTA kernel (tiles of 256 x 256 on pairs of SMs): structured inputs, then random ones; ragged
+    edges in M, N and K; more tiles than clusters; each result also against the one-CTA kernel."""
+    from odin_infer_b200.csrc import ops
+    M, N, K = case
+    exact = 1e-6 if out_dtype == torch.float32 else 4e-3
+
+    def run2(a, w):
+        out = torch.full((M, N), float("nan"), device=DEV, dtype=out_dtype)
+        ops.gemm_tc2(a, w, out)
+        ops.gemm_tc_check()
+        assert not torch.isnan(out.float()).any()
+        return out
+
+    ones_a = torch.ones(M, K, device=DEV, dtype=torch.bfloat16)
+    ones_w = torch.ones(N, K, device=DEV, dtype=torch.bfloat16)
+    close(run2(ones_a, ones_w), torch.full((M, N), float(K)), exact, "ones")
+    rows = (torch.arange(M, device=DEV)[:, None].expand(M, K) % 7).bfloat16().contiguous()
+    cols = ((torch.arange(N, device=DEV)[:, None].expand(N, K) % 5) * 0.25).bfloat16().contiguous()
+    close(run2(rows, cols), rows.double() @ cols.double().t(), exact, "rows x columns")
+    eye = torch.eye(N, K, device=DEV, dtype=torch.bfloat16)
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    close(run2(a, eye), a.double() @ eye.double().t(), exact, "identity")
+    torch.manual_seed(M + N + K)
+    w = torch.randn(N, K, device=DEV).bfloat16()
+    got = run2(a, w)
+    tol = 1e-7 * math.sqrt(K) * 8 if out_dtype == torch.float32 else 4e-3
+    close(got, a.double() @ w.double().t(), tol, "random")
+    one = torch.empty(M, N, device=DEV, dtype=out_dtype)
+    ops.gemm_tc(a, w, one, 0, 256)
+    close(got, one, 1e-6 if out_dtype == torch.float32 else 8e-3, "against the one-CTA kernel")
+
+
+@pytest.mark.parametrize("case", [(256, 128, 64), (300, 192, 1032), (2048, 1536, 512), (130, 64, 128)])
+def test_pair_kernel_swiglu(case):
+    """The two-CTA kernel with the SwiGLU in its epilogue against the formula in float64."""
+    from odin_infer_b200.csrc import ops
+    M, I, K = case
+    torch.manual_seed(I + K)
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    w = (torch.randn(2 * I, K, device=DEV) / math.sqrt(K)).bfloat16()
+    out = torch.full((M, I), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops.gemm_tc2_swiglu(a, w, out)
+    ops.gemm_tc_check()
+    g = a.double() @ w[:I].double().t()
+    u = a.double() @ w[I:].double().t()
+    close(out, g * torch.sigmoid(g) * u, 8e-3, "swiglu")
