@@ -123,6 +123,15 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
         c_int(dtype_code(out.dtype)), c_int(T), c_int(I), _stream()), "swiglu")
 
 
+def scale_rows(rows: torch.Tensor, ssq: torch.Tensor, width: int, eps: float, out: torch.Tensor) -> None:
+    """out[j] = rows[j] / sqrt(sum(ssq[j]) / width + eps) for bfloat16 rows [n, d] (see gemm_tc's sink)."""
+    assert rows.dtype == out.dtype == torch.bfloat16 and rows.is_contiguous() and out.is_contiguous()
+    assert ssq.dtype == torch.float32 and ssq.is_contiguous() and ssq.shape[0] == rows.shape[0]
+    _check(_fn("elementwise", "odin_scale_rows")(
+        _ptr(rows), _ptr(ssq), c_int(ssq.shape[1]), c_int(width), c_float(eps), _ptr(out), c_int(rows.shape[0]),
+        c_int(rows.shape[1]), _stream()), "scale_rows")
+
+
 def cast(src: torch.Tensor, dst: torch.Tensor) -> None:
     assert src.is_contiguous() and dst.is_contiguous() and src.numel() == dst.numel()
     _check(_fn("elementwise", "odin_cast")(
@@ -156,8 +165,15 @@ def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+class _GemmExtras(ctypes.Structure):
+    _fields_ = [("in_ssq", c_void_p), ("in_ssq_parts", c_int), ("in_width", c_int), ("in_eps", c_float),
+                ("res", c_void_p), ("res_ld", c_longlong), ("norm_w", c_void_p), ("norm_w_dtype", c_int),
+                ("normed", c_void_p), ("normed_ld", c_longlong), ("out_ssq", c_void_p)]
+
+
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, bn: int, n_split: int = 1,
-            stages: int = 0) -> None:
+            stages: int = 0, row_ssq: torch.Tensor | None = None, row_width: int = 0, row_eps: float = 0.0,
+            sink: tuple | None = None) -> None:
     """out = a[M, K] @ w[N, K]^T on the tcgen05 tensor cores (bfloat16 in, 32-bit accumulation).
 
     mode 0: tokens on the 128-row side of the MMA, tiles of bn weight rows.
@@ -165,6 +181,13 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, bn: 
     n_split > 1: out is float32 [n_split, M, N]; slice s holds the partial sum of K part s.
     stages: length of the kernel's ring of shared-memory stages; 0: as many as fit, fewer to
     leave room on the SM for a CTA of the neighbouring kernel.
+    row_ssq (mode 1): [M, parts] float32; row j of a still lacks its norm's factor
+    1 / sqrt(sum(row_ssq[j]) / row_width + row_eps), which is applied to the sums.
+    sink (mode 1, float32 out): (res, norm_w, normed, out_ssq): the product is added to the
+    32-bit residual stream res [M, N] by the CTA that writes a tile's last partial sum;
+    normed [M, N] bfloat16 = res * norm_w (without the norm's factor) and out_ssq
+    [M, ceil(N/128)] the tiles' shares of each row's sum of squares: what the next product
+    takes as (a, row_ssq).  out then holds scratch only.
     """
     M, K = a.shape
     N = w.shape[0]
@@ -178,10 +201,26 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, bn: 
     else:
         assert tuple(out.shape) == (M, N)
         ldc, stride = out.stride(0), 0
-    _check(_fn("gemm_tc", "odin_gemm_tc")(
+    extras = None
+    if row_ssq is not None or sink is not None:
+        extras = _GemmExtras()
+        if row_ssq is not None:
+            assert row_ssq.dtype == torch.float32 and row_ssq.is_contiguous() and row_ssq.shape[0] == M and row_width > 0
+            extras.in_ssq, extras.in_ssq_parts = row_ssq.data_ptr(), row_ssq.shape[1]
+            extras.in_width, extras.in_eps = row_width, row_eps
+        if sink is not None:
+            res, norm_w, normed, out_ssq = sink
+            assert res.dtype == torch.float32 and tuple(res.shape) == (M, N) and res.stride(1) == 1
+            assert normed.dtype == torch.bfloat16 and tuple(normed.shape) == (M, N) and normed.stride(1) == 1
+            assert out_ssq.dtype == torch.float32 and out_ssq.is_contiguous() and tuple(out_ssq.shape) == (M, (N + 127) // 128)
+            assert norm_w.numel() == N and norm_w.is_contiguous() and out.dtype == torch.float32
+            extras.res, extras.res_ld = res.data_ptr(), res.stride(0)
+            extras.norm_w, extras.norm_w_dtype = norm_w.data_ptr(), dtype_code(norm_w.dtype)
+            extras.normed, extras.normed_ld, extras.out_ssq = normed.data_ptr(), normed.stride(0), out_ssq.data_ptr()
+    _check(_fn("gemm_tc", "odin_gemm_tc_ex")(
         _ptr(a), _ptr(w), _ptr(out), c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K),
         c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(ldc), c_int(mode), c_int(bn), c_int(n_split),
-        c_longlong(stride), c_int(stages), _stream()), "gemm_tc")
+        c_longlong(stride), c_int(stages), ctypes.byref(extras) if extras is not None else None, _stream()), "gemm_tc")
 
 
 def gemm_tc_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:

@@ -62,8 +62,15 @@ class DecoderModel:
         for pe in self.position_encodings.values():
             pe.on_embedding(rt, step, x)
         pending = None
-        for idx, e in enumerate(self.spec.schedule):
-            x, pending = self.layers[e.layer].forward(rt, step, x, pending, idx)
+        sched = self.spec.schedule
+        for idx, e in enumerate(sched):
+            block = self.layers[e.layer]
+            if block.takes_next_norm:
+                # the norm that will take this block's update: the next block's first one
+                nxt = self.layers[sched[idx + 1].layer].first_norm if idx + 1 < len(sched) else None
+                x, pending = block.forward(rt, step, x, pending, idx, next_norm=nxt)
+            else:
+                x, pending = block.forward(rt, step, x, pending, idx)
         if step.n_logit_rows == 0:
             return None
         h = self.final_norm.forward(rt, x, pending, rows=step.logit_rows)

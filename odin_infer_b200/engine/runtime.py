@@ -8,6 +8,7 @@ import os
 import torch
 
 from ..csrc import ops
+from ..parts.base import NormedRows
 
 
 def choose_k_split(n_tiles: int, k_blocks: int, m: int, n_sms: int = 148, max_split: int = 16) -> int:
@@ -28,6 +29,16 @@ def choose_k_split(n_tiles: int, k_blocks: int, m: int, n_sms: int = 148, max_sp
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = parts, cost
     return best
+
+
+# Products of few tokens can carry out the residual add and the next norm's weighting themselves
+# (`ResidualSink`): two launches fewer per layer, and yet 10 % slower on the 8B shape, because the
+# add+RMSNorm kernel between two products is where the second one fetches its first weights.  Off
+# unless ODIN_FUSE_SINKS=1; the tests run it both ways.
+FUSE_SINKS = os.environ.get("ODIN_FUSE_SINKS", "0") == "1"
+
+def fuse_sinks() -> bool:
+    return FUSE_SINKS
 
 
 # from this many tokens on a product runs on pairs of SMs (tiles of 256 token rows)
@@ -78,8 +89,16 @@ class Runtime:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
 
     # ---- matrix product: out[M, N] = a[M, K] @ w[N, K]^T -----------------
-    def linear(self, a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
-               may_split: bool = False, beside_attention: bool = False) -> torch.Tensor:
+    def materialize(self, h):
+        """`NormedRows` as ordinary rows (their norm's factor applied); anything else unchanged."""
+        if not isinstance(h, NormedRows):
+            return h
+        out = self.empty(*h.rows.shape)
+        ops.scale_rows(h.rows, h.ssq, h.width, h.eps, out)
+        return out
+
+    def linear(self, a, w: torch.Tensor, out_dtype: torch.dtype | None = None,
+               may_split: bool = False, beside_attention: bool = False, sink=None):
         """bfloat16 operands that TMA can read go to the tcgen05 kernel, everything else
         (the 32-bit path, odd widths, tensors stored in 32-bit) to the CUDA-core kernel.
 
@@ -89,22 +108,41 @@ class Runtime:
         beside_attention: the product comes right before or after attention; for few tokens
         it then keeps a shorter ring of stages, so that a CTA of the decode attention kernel
         fits on the SM beside it and can fetch its pages (or this product its weights) while
-        the other still runs."""
-        M, N, K = a.shape[0], w.shape[0], a.shape[1]
+        the other still runs.
+
+        a may be `NormedRows` (rows that still lack their norm's factor): a product of few
+        tokens applies the factor to its sums, any other path scales the rows first.
+        sink: a `ResidualSink`; a product of few tokens may then add its result to the
+        residual stream itself and weight it for the sink's norm, and returns `NormedRows`
+        (the norm's output, to be handed to that norm) instead of the update."""
+        rows = a.rows if isinstance(a, NormedRows) else a
+        M, N, K = rows.shape[0], w.shape[0], rows.shape[1]
         out_dtype = out_dtype or self.dtype
-        if M > 0 and ops.gemm_tc_supported(a, w):
+        if M > 0 and ops.gemm_tc_supported(rows, w):
             if M <= 128:
                 bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
                 n_split = choose_k_split((N + 127) // 128, (K + 63) // 64, M, self.n_sms) if may_split else 1
                 n_split = ops.gemm_tc_splits(K, n_split)
                 stages = LIGHT_STAGES if beside_attention else 0
+                scale = dict(row_ssq=a.ssq, row_width=a.width, row_eps=a.eps) if isinstance(a, NormedRows) else {}
+                if (sink is not None and fuse_sinks() and out_dtype == torch.float32 and may_split
+                        and getattr(sink.norm, "weight", None) is not None and sink.norm.weight.numel() == N
+                        and tuple(sink.x.shape) == (M, N) and sink.x.dtype == torch.float32):
+                    scratch = self.empty(n_split, M, N, dtype=torch.float32) if n_split > 1 else self.empty(M, N, dtype=torch.float32)
+                    normed = self.empty(M, N)
+                    ssq = self.empty(M, (N + 127) // 128, dtype=torch.float32)
+                    ops.gemm_tc(rows, w, scratch, 1, bn, n_split, stages,
+                                sink=(sink.x, sink.norm.weight, normed, ssq), **scale)
+                    return NormedRows(normed, ssq, N, sink.norm.eps, sink.norm)
                 if n_split > 1:
                     out = self.empty(n_split, M, N, dtype=torch.float32)
-                    ops.gemm_tc(a, w, out, 1, bn, n_split, stages)
+                    ops.gemm_tc(rows, w, out, 1, bn, n_split, stages, **scale)
                     return out
                 out = self.empty(M, N, dtype=out_dtype)
-                ops.gemm_tc(a, w, out, 1, bn, 1, stages)
+                ops.gemm_tc(rows, w, out, 1, bn, 1, stages, **scale)
                 return out
+        a = self.materialize(a)
+        if M > 0 and ops.gemm_tc_supported(a, w):
             out = self.empty(M, N, dtype=out_dtype)
             if M >= PAIR_MIN_TOKENS and N > 128:
                 ops.gemm_tc2(a, w, out)  # tiles of 256 x 256 on pairs of SMs
@@ -121,6 +159,8 @@ class Runtime:
         (which also adds the partial sums of a split product)."""
         M = a.shape[0]
         act = self.empty(M, inner)
+        if M > 128:
+            a = self.materialize(a)
         if M > 128 and ops.gemm_tc_supported(a, w_gate_up):
             if M >= PAIR_MIN_TOKENS and ops.gemm_tc2_swiglu_supported(inner):
                 ops.gemm_tc2_swiglu(a, w_gate_up, act)

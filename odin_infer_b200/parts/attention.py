@@ -67,7 +67,9 @@ class GQAttention(Mixer):
     def kernel_groups(self):
         return {"head_prep", "attention_plain", "gemm_plain"}
 
-    def forward(self, rt, step, h, entry):
+    takes_sinks = True
+
+    def forward(self, rt, step, h, entry, sink=None):
         T = h.shape[0]
         qkv = rt.linear(h, self.w_qkv, may_split=True, beside_attention=True)
         k_line, v_line, block_table = step.kv(entry)
@@ -80,7 +82,7 @@ class GQAttention(Mixer):
                 step, qkv, o, self.n_q, self.n_kv, self.hd, self.q_norm if self.qk_norm else None,
                 self.k_norm if self.qk_norm else None, self.eps, cos, sin, rot_dim, k_line, v_line, block_table,
                 self.window, writes):
-            return rt.linear(o, self.w_o, out_dtype=torch.float32, may_split=True, beside_attention=True)
+            return rt.linear(o, self.w_o, out_dtype=torch.float32, may_split=True, beside_attention=True, sink=sink)
         # a product of few tokens may come back as partial sums: they are added here
         q_out = rt.empty(T, self.n_q * self.hd) if qkv.dim() == 3 else None
         q = ops.head_prep(qkv, self.n_q, 0 if self.kv_shared else self.n_kv, self.hd,
@@ -88,4 +90,4 @@ class GQAttention(Mixer):
                           cos, sin, rot_dim, step.tok_pos, step.tok_seq, block_table, k_line, v_line,
                           write_kv=writes, q_out=q_out)
         rt.attention(step, q, o, self.n_q, self.n_kv, self.hd, k_line, v_line, block_table, self.window)
-        return rt.linear(o, self.w_o, out_dtype=torch.float32, may_split=True, beside_attention=True)
+        return rt.linear(o, self.w_o, out_dtype=torch.float32, may_split=True, beside_attention=True, sink=sink)

@@ -60,11 +60,45 @@ class Part:
         return set()
 
 
+@dataclasses.dataclass
+class NormedRows:
+    """Rows that a norm has weighted but not yet scaled: row j stands for
+    rows[j] / sqrt(sum(ssq[j]) / width + eps).  What a product with a `ResidualSink` hands to
+    the norm it was made for; a product that takes it as input applies the factor to its sums
+    (`Runtime.linear`), anything else asks the runtime to `materialize` it."""
+    rows: torch.Tensor   # [n, width] in the runtime's element type
+    ssq: torch.Tensor    # [n, parts] 32-bit shares of the rows' sums of squares
+    width: int
+    eps: float
+    norm: Any            # the norm part these rows are the output of
+
+    @property
+    def shape(self):
+        return self.rows.shape
+
+
+@dataclasses.dataclass
+class ResidualSink:
+    """Where a part's last product may put its result itself: added to the residual stream x,
+    and on through `norm` (see `Runtime.linear`).  A part that is handed a sink and cannot use
+    it ignores it and returns its update as usual."""
+    x: torch.Tensor
+    norm: Any
+
+
 class Norm(Part):
-    def forward(self, rt, x: torch.Tensor, delta: torch.Tensor | None, rows: torch.Tensor | None = None) -> torch.Tensor:
+    def sink(self, x: torch.Tensor) -> ResidualSink | None:
+        """A sink through which the product before this norm may carry out the norm's add and
+        weighting itself, or None if this norm cannot finish such rows."""
+        return None
+
+
+    def forward(self, rt, x: torch.Tensor, delta, rows: torch.Tensor | None = None, unscaled_ok: bool = False):
         """x: the 32-bit residual stream [n, width], updated in place by `delta`
         (None, [n, width] or [splits, n, width]); returns the normalised rows in
-        the runtime's element type.  rows: gather these rows only (x untouched)."""
+        the runtime's element type.  rows: gather these rows only (x untouched).
+        delta may be the `NormedRows` that a product made through this norm's sink (x is then
+        up to date already); they are returned as they are if `unscaled_ok`, else scaled."""
         raise NotImplementedError
 
 
@@ -90,6 +124,10 @@ class Mixer(Part):
         """Bytes of fixed-size state this mixer keeps per sequence."""
         return 0
 
+    # A mixer or feed-forward that sets this takes `NormedRows` as h (it passes them to
+    # `Runtime.linear` / `gated_linear` only) and a keyword `sink=` for its last product.
+    takes_sinks = False
+
     def forward(self, rt, step, h: torch.Tensor, entry: int) -> torch.Tensor:
         """h: [T, width] normalised input.  entry: index of the schedule entry being run
         (names the cache line and the state through `step`).  Returns the update of the
@@ -98,15 +136,26 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    takes_sinks = False  # as for Mixer
+
     def forward(self, rt, step, h: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
 
 class Block(Part):
-    def forward(self, rt, step, x: torch.Tensor, pending: torch.Tensor | None, entry: int):
-        """x: residual stream (in place); pending: an update not yet added to it.
-        Returns (x, pending)."""
+    # a block that sets this takes `next_norm=` (the norm that will consume its pending update,
+    # or None) and may hand that norm's sink to its last part
+    takes_next_norm = False
+
+    def forward(self, rt, step, x: torch.Tensor, pending, entry: int):
+        """x: residual stream (in place); pending: an update not yet added to it (or the
+        `NormedRows` of this block's first norm).  Returns (x, pending)."""
         raise NotImplementedError
+
+    @property
+    def first_norm(self):
+        """The norm that takes this block's input, if the block before may feed it through a sink."""
+        return None
 
     @property
     def mixer(self) -> Mixer:

@@ -32,6 +32,8 @@ class SwiGLU(FeedForward):
     def kernel_groups(self):
         return {"elementwise", "gemm_plain"}
 
-    def forward(self, rt, step, h):
+    takes_sinks = True
+
+    def forward(self, rt, step, h, sink=None):
         act = rt.gated_linear(h, self.w_gate_up, self.inner)
-        return rt.linear(act, self.w_down, out_dtype=torch.float32, may_split=True)
+        return rt.linear(act, self.w_down, out_dtype=torch.float32, may_split=True, sink=sink)

@@ -76,6 +76,16 @@ def test_last_32_one_by_one(folders, requests_and_refs, name, dtype):
     check(run(folders[name], dtype, traces.tail_one_by_one(reqs, 32)), refs, dtype, "last32")
 
 
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+def test_last_32_one_by_one_with_sinks(folders, requests_and_refs, name, monkeypatch):
+    """The same with the products of few tokens adding to the residual stream and weighting for the
+    next norm themselves (off by default): the decoded tokens go through that path."""
+    from odin_infer_b200.engine import runtime
+    monkeypatch.setattr(runtime, "FUSE_SINKS", True)
+    reqs, refs = requests_and_refs[name]
+    check(run(folders[name], "bfloat16", traces.tail_one_by_one(reqs, 32)), refs, "bfloat16", "sinks")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_unequal_batches_slots_reused(folders, requests_and_refs, name, dtype):
