@@ -21,6 +21,7 @@
 // Every wait is bounded (tc::mbar_wait); a CTA that gives up sets the error flag, and both
 // CTAs of a pair always reach the final cluster barrier, since no wait of either is endless.
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 #include "tc_common.cuh"
@@ -46,6 +47,7 @@ struct Params2 {
     int tiles_m, tiles_n; // pair tiles: 256 rows x 256 columns (DUAL: 256 x 128)
     int kb_total;
     int dual_offset;      // DUAL: first weight row of the up half
+    int accumulate;       // float32 out: C += the product (the residual stream takes its update in place)
     int* error;
 };
 
@@ -287,7 +289,23 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int j0 = tn * ACC_N + c0;
                 if (i < p.M && j0 < p.N) {
                     const int n = min(32, p.N - j0);
-                    store32<TO>(out + (size_t)i * p.ldc + j0, r, n);
+                    TO* dst = out + (size_t)i * p.ldc + j0;
+                    if (std::is_same<TO, float>::value && p.accumulate) {
+                        const float* old = reinterpret_cast<const float*>(dst);
+                        if (n == 32 && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                const float4 o4 = reinterpret_cast<const float4*>(old)[q];
+                                r[4 * q] = __float_as_uint(o4.x + __uint_as_float(r[4 * q]));
+                                r[4 * q + 1] = __float_as_uint(o4.y + __uint_as_float(r[4 * q + 1]));
+                                r[4 * q + 2] = __float_as_uint(o4.z + __uint_as_float(r[4 * q + 2]));
+                                r[4 * q + 3] = __float_as_uint(o4.w + __uint_as_float(r[4 * q + 3]));
+                            }
+                        } else {
+                            for (int q = 0; q < n; ++q) r[q] = __float_as_uint(old[q] + __uint_as_float(r[q]));
+                        }
+                    }
+                    store32<TO>(dst, r, n);
                 }
             }
             tc::fence_before_sync();
@@ -396,8 +414,9 @@ int launch2(const CUtensorMap& ma, const CUtensorMap& mw, const Params2& p, cuda
 // C[M, N] = A[M, K] W[N, K]^T on pairs of SMs (tiles of 256 x 256); for many tokens.  A: bfloat16, row
 // stride lda; W: bfloat16, row stride ldw; C of c_dtype (bfloat16 or float32), row stride ldc.
 // Strides and K multiples of 8 elements, pointers 16-byte aligned, else ODIN_ERR_UNSUPPORTED.
+// accumulate (float32 C only): C += A W^T, each element read once and written once by the thread that holds its sum.
 extern "C" int odin_gemm_tc2(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, long long lda,
-                             long long ldw, long long ldc, void* stream) {
+                             long long ldw, long long ldc, int accumulate, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0) return ODIN_ERR_BAD_ARG;
     if ((lda % 8) || (ldw % 8) || (K % 8) || (((uintptr_t)A) & 15) || (((uintptr_t)W) & 15)) return ODIN_ERR_UNSUPPORTED;
@@ -407,6 +426,8 @@ extern "C" int odin_gemm_tc2(const void* A, const void* W, void* C, int c_dtype,
     p.tiles_n = (N + BN - 1) / BN;
     p.kb_total = (K + BK - 1) / BK;
     p.dual_offset = 0;
+    if (accumulate && c_dtype != ODIN_F32) return ODIN_ERR_BAD_ARG;
+    p.accumulate = accumulate ? 1 : 0;
     p.error = error_flag2();
     CUtensorMap ma, mw;
     int rc;
@@ -433,6 +454,7 @@ extern "C" int odin_gemm_tc2_swiglu(const void* A, const void* W, void* C, int c
     p.tiles_n = (I + BN / 2 - 1) / (BN / 2);
     p.kb_total = (K + BK - 1) / BK;
     p.dual_offset = I;
+    p.accumulate = 0;
     p.error = error_flag2();
     CUtensorMap ma, mw;
     int rc;

@@ -236,8 +236,9 @@ def gemm_tc_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) 
         "gemm_tc_swiglu")
 
 
-def gemm_tc2(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """out = a[M, K] @ w[N, K]^T on pairs of SMs (tcgen05 cta_group::2, tiles of 256 x 256): for many tokens."""
+def gemm_tc2(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    """out = a[M, K] @ w[N, K]^T on pairs of SMs (tcgen05 cta_group::2, tiles of 256 x 256): for many tokens.
+    accumulate: out (float32) += the product."""
     M, K = a.shape
     N = w.shape[0]
     if not gemm_tc_supported(a, w):
@@ -245,7 +246,8 @@ def gemm_tc2(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     assert w.shape[1] == K and tuple(out.shape) == (M, N) and out.stride(1) == 1
     _check(_fn("gemm_tc", "odin_gemm_tc2")(
         _ptr(a), _ptr(w), _ptr(out), c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K),
-        c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)), _stream()), "gemm_tc2")
+        c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)), c_int(1 if accumulate else 0),
+        _stream()), "gemm_tc2")
 
 
 def gemm_tc2_swiglu_supported(inner: int) -> bool:

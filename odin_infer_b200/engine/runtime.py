@@ -8,7 +8,7 @@ import os
 import torch
 
 from ..csrc import ops
-from ..parts.base import NormedRows
+from ..parts.base import NormedRows, ResidualAdded
 
 
 def choose_k_split(n_tiles: int, k_blocks: int, m: int, n_sms: int = 148, max_split: int = 16) -> int:
@@ -143,6 +143,11 @@ class Runtime:
                 return out
         a = self.materialize(a)
         if M > 0 and ops.gemm_tc_supported(a, w):
+            if (M >= PAIR_MIN_TOKENS and N > 128 and sink is not None and out_dtype == torch.float32
+                    and tuple(sink.x.shape) == (M, N) and sink.x.dtype == torch.float32 and sink.x.stride(1) == 1):
+                # many tokens: the product's epilogue adds to the residual stream in place
+                ops.gemm_tc2(a, w, sink.x, accumulate=True)
+                return ResidualAdded()
             out = self.empty(M, N, dtype=out_dtype)
             if M >= PAIR_MIN_TOKENS and N > 128:
                 ops.gemm_tc2(a, w, out)  # tiles of 256 x 256 on pairs of SMs

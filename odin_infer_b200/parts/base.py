@@ -86,6 +86,11 @@ class ResidualSink:
     norm: Any
 
 
+class ResidualAdded:
+    """What a product returns that has added its result to the sink's residual stream already:
+    nothing is left to add, the norm still has to be taken."""
+
+
 class Norm(Part):
     def sink(self, x: torch.Tensor) -> ResidualSink | None:
         """A sink through which the product before this norm may carry out the norm's add and

@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from .base import Norm, NormedRows, ParamSpec, ResidualSink, register_part
+from .base import Norm, NormedRows, ParamSpec, ResidualAdded, ResidualSink, register_part
 
 
 @register_part("norm", "rmsnorm")
@@ -32,6 +32,8 @@ class RMSNorm(Norm):
             if delta.norm is not self or rows is not None:
                 raise ValueError("rows made through another norm's sink cannot be finished by this one")
             return delta if unscaled_ok else rt.materialize(delta)
+        if isinstance(delta, ResidualAdded):
+            delta = None
         n = x.shape[0] if rows is None else rows.numel()
         out = rt.empty(n, self.width)
         ops.add_rmsnorm(x, delta, self.weight, self.eps, out, rows)

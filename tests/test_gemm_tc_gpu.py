@@ -246,3 +246,20 @@ def test_sink_and_row_factor_against_the_separate_kernels(case):
             ops.gemm_tc(normed, w2, got2, 1, bn, n2, row_ssq=ssq, row_width=N, row_eps=eps)
             ops.gemm_tc_check()
             close(got2.sum(0) if p2 > 1 else got2, ref2, 1.2e-2, "next product")
+
+
+@pytest.mark.parametrize("case", [(256, 256, 64), (300, 1000, 1032), (2048, 4096, 512)])
+def test_pair_kernel_adds_in_place(case):
+    """C += A W^T in the epilogue: exactly the separate product added to C."""
+    from odin_infer_b200.csrc import ops
+    M, N, K = case
+    torch.manual_seed(K)
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).bfloat16()
+    x0 = torch.randn(M, N, device=DEV)
+    prod = torch.empty(M, N, device=DEV)
+    ops.gemm_tc2(a, w, prod)
+    x = x0.clone()
+    ops.gemm_tc2(a, w, x, accumulate=True)
+    ops.gemm_tc_check()
+    assert torch.equal(x, x0 + prod)
