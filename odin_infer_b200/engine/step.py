@@ -18,6 +18,8 @@ import dataclasses
 import numpy as np
 import torch
 
+from ..cache.groups import PAGE
+
 
 @dataclasses.dataclass
 class StepEntry:
@@ -83,18 +85,24 @@ class StepBatch:
         self.seq_start, self.seq_slots, self.seq_len_after = view("seq_start"), view("seq_slots"), view("seq_len_after")
         self.block_tables = {key: view(("bt", key)) for key in cache.groups}
         self._copied = None
+        self._host_views: dict = {}
         self.h2d_bytes = self._host_t.numel() * 4
         self.fill(entries, start_positions)
 
     def _h(self, name):
-        o, shape = self._where[name]
-        n = int(np.prod(shape)) if shape else 1
-        return self._host[o:o + n].reshape(shape)
+        v = self._host_views.get(name)
+        if v is None:
+            o, shape = self._where[name]
+            n = int(np.prod(shape)) if shape else 1
+            v = self._host_views[name] = self._host[o:o + n].reshape(shape)
+        return v
 
     def fill(self, entries: list[StepEntry], start_positions: list[int]) -> None:
         """(Re)write the tables for these entries and copy them to the device."""
         if self._copied is not None:
             self._copied.synchronize()  # the last copy out of the pinned array must be over before it is rewritten
+        if self._advance(entries, start_positions):
+            return
         n_tok = sum(len(e.tokens) for e in entries)
         if len(entries) > self.n_seq_cap or n_tok > self.n_row_cap:
             raise StepError("step does not fit the buffers it was built for")
@@ -147,10 +155,40 @@ class StepBatch:
             bt[:] = -1
             if self.slots:
                 bt[:self.n_seqs] = g.block_table[self.slots]
+        self._last_starts = list(start_positions)
+        self._upload()
+
+    def _upload(self) -> None:
         self._dev.copy_(self._host_t, non_blocking=True)
         if self._dev.is_cuda:
-            self._copied = torch.cuda.Event()
+            if self._copied is None:
+                self._copied = torch.cuda.Event()
             self._copied.record()
+
+    def _advance(self, entries: list[StepEntry], start_positions: list[int]) -> bool:
+        """The usual decode step: the sequences of the last fill, in the same order, one token
+        further each.  Only the token ids, the positions, the lengths and (where a sequence
+        entered a new page or a window let pages go) the block tables change; the tables are
+        updated in place instead of being written anew.  False if this is not such a step."""
+        last = getattr(self, "_last_starts", None)
+        if (last is None or not self.all_single or len(entries) != self.n_seqs
+                or any(len(e.tokens) != 1 or e.slot != s for e, s in zip(entries, self.slots))
+                or any(p != q + 1 for p, q in zip(start_positions, last))
+                or (not self.all_rows_wanted and any(e.want != [0] for e in entries))):
+            return False
+        n = self.n_seqs
+        self._h("tok_ids")[:n] = [e.tokens[0] for e in entries]
+        self._h("tok_pos")[:n] += 1
+        self._h("seq_len_after")[:n] += 1
+        self.lengths_after = [p + 1 for p in start_positions]
+        self.max_len_after += 1
+        self.all_start = False
+        for key, g in self.cache.groups.items():
+            if g.request.window > 0 or any(p % PAGE == 0 for p in start_positions):
+                self._h(("bt", key))[:n] = g.block_table[self.slots]
+        self._last_starts = list(start_positions)
+        self._upload()
+        return True
 
     # ---- what a mixer asks for ------------------------------------------
     def kv(self, entry: int):
