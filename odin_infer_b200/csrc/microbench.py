@@ -1,6 +1,7 @@
 """Times one kernel of this package in isolation (CUDA events, L2 flushed between runs).
 
     python -m odin_infer_b200.csrc.microbench gemm --m 8 --n 24576 --k 4096 [--mode 1 --bn 16 --split 3]
+    python -m odin_infer_b200.csrc.microbench gemm --m 2048 --n 24576 --k 4096 --pair
     python -m odin_infer_b200.csrc.microbench decode-attention --batch 64 --ctx 640
     python -m odin_infer_b200.csrc.microbench prefill-attention --tokens 2048
     python -m odin_infer_b200.csrc.microbench add-rmsnorm --rows 8 --width 4096 --split 4
@@ -58,6 +59,7 @@ def main(argv=None) -> int:
     ap.add_argument("--bn", type=int, default=0)
     ap.add_argument("--split", type=int, default=0, help="0: as the runtime chooses")
     ap.add_argument("--stages", type=int, default=0, help="gemm: length of the ring of stages (0: as many as fit)")
+    ap.add_argument("--pair", action="store_true", help="gemm: the two-CTA kernel (tiles of 256 x 256 on pairs of SMs)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=640)
     ap.add_argument("--tokens", type=int, default=2048)
@@ -76,6 +78,13 @@ def main(argv=None) -> int:
         M, N, K = args.m, args.n, args.k
         a = torch.randn(M, K, device=DEV).bfloat16()
         w = torch.randn(N, K, device=DEV).bfloat16()
+        if args.pair:
+            c = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+            ms = timeit(lambda: ops.gemm_tc2(a, w, c), args.iters)
+            ops.gemm_tc_check()
+            out.update(m=M, n=N, k=K, pair=True, us=round(ms * 1e3, 2), tflops=round(2 * M * N * K / ms / 1e9, 1))
+            print(json.dumps(out))
+            return 0
         mode = args.mode if args.mode >= 0 else (1 if M <= 128 else 0)
         bn = args.bn or ((16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128) if mode == 1 else 256)
         split = args.split or (choose_k_split((N + 127) // 128, (K + 63) // 64, M) if mode == 1 else 1)
