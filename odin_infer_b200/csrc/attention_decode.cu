@@ -1,14 +1,17 @@
 // Attention of one new token per sequence over its paged bfloat16 cache, split
 // along the keys so that a small batch still occupies every SM.
 //
-// Grid: (key splits, kv heads x query-head groups, sequences).  A CTA takes one
+// Two kernels.  The general one (any head size that is a power of two from 16 to 256), on the
+// CUDA cores: grid (key splits, kv heads x query-head groups, sequences); a CTA takes one
 // sequence, one kv head, up to G of its query heads, and a contiguous range of the
 // sequence's pages; every key and value it loads serves all G query heads.  Inside
 // a warp a key's head_dim elements are spread over LPK lanes (16-byte loads, whole
 // rows coalesced), so one warp instruction covers 32/LPK keys.  Each lane group
 // keeps an "online softmax" of its own (running maximum, sum, weighted values);
-// groups, warps and finally splits are merged with the usual rescaling.  A second
-// kernel merges the splits and writes bfloat16.
+// groups, warps and finally splits are merged with the usual rescaling, the splits by a
+// second kernel.  The tensor-core one (head sizes 64 and 128; further down): pages by TMA,
+// both products on mma.sync, the splits merged inside the kernel, optionally with head
+// preparation inside.
 //
 // Arithmetic follows infer/forward.odin:88-115 (scores scaled by 1/sqrt(hd), softmax
 // with the maximum subtracted, weighted sum of values), all in 32-bit; the scale and

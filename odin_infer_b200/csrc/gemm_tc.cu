@@ -5,7 +5,9 @@
 // tile overlaps the products of the next.
 //
 // Roles (192 threads): warp 0 issues TMA loads, warp 1 allocates tensor memory and
-// issues the MMAs (one thread), warps 2..5 read the accumulator back and store.
+// issues the MMAs (one lane), warps 2..5 read the accumulator back and store.
+// This is the kernel of decode steps (mode 1) and of short prompts; from 256 tokens on
+// the products run on pairs of SMs (gemm_tc2.cu).
 //
 // The product is computed as D = X * Y^T with X on the 128-row side of the MMA and
 // Y on its N side.  Two modes map the matrices to X and Y:
@@ -18,6 +20,11 @@
 // partial sum to its own slice of the output ([n_split][M][N]); the consumer adds
 // them in a fixed order.  Which part a CTA takes never depends on M, so a token's
 // result does not depend on what else is in the batch.
+//
+// Mode 1 has two optional ends (GemmParams): its input rows may still lack their norm's
+// factor, which is then applied to the sums; and its output may go on into the residual
+// stream and through the next norm's weights, done by the CTA that writes a tile's last
+// partial sum.
 //
 // In the reference this is the weight-times-activation product of every layer
 // (infer/matmul.odin:77-109, one row-dot per thread on the CPU; gemv kernels in
