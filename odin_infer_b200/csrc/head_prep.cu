@@ -97,9 +97,11 @@ head_prep_kernel(const TI* qkv, int n_split, size_t split_stride, T* q_out,  // 
 using headmath::load_vec;
 using headmath::store_vec_bf16;
 
-template <int VEC, typename TI>
+// A warp per (token, head), TOK tokens per warp (one: for few tokens the kernel is a chain of
+// latencies, and everything that can be is fetched before the wait for the kernel before it).
+template <int VEC, typename TI, int TOK>
 __global__ void __launch_bounds__(HP_WARPS * 32)
-head_prep_fast_kernel(const TI* qkv, int n_split, size_t split_stride, bf16* q_out, size_t q_out_stride, int Hq,
+head_prep_fast_kernel(const TI* qkv, int n_split, size_t split_stride, bf16* q_out, size_t q_out_stride, int T, int Hq,
                       int Hkv, size_t row_stride, VecRef qw, VecRef kw, int has_norm, float eps,
                       const float* __restrict__ cos_t, const float* __restrict__ sin_t, int table_len,
                       const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
@@ -109,48 +111,127 @@ head_prep_fast_kernel(const TI* qkv, int n_split, size_t split_stride, bf16* q_o
     pdl_trigger();
     // What no earlier kernel of the step writes is fetched before the wait for that kernel: the
     // step's tables, the page of the cache, the angles' cosines and sines, the norms' weights.
-    const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y * HP_WARPS + warp;
     const bool in_range = head < Hq + 2 * Hkv;
-    const int seq = in_range ? tok_seq[t] : -1;
-    const int pos = tok_pos[t];
     const bool is_q = head < Hq;
     const bool is_k = !is_q && head < Hq + Hkv;
-    bool active = in_range && seq >= 0 && (is_q || write_kv);
     const int kvh = is_q ? 0 : (is_k ? head - Hq : head - Hq - Hkv);
-    bf16* dst = q_out + (size_t)t * q_out_stride + (size_t)head * HD + lane * VEC;
-    if (active && !is_q) {
-        const int page = block_table[(size_t)seq * bt_stride + pos / page_size];
-        if (page < 0) active = false;
-        else dst = (is_k ? k_cache : v_cache) + (((size_t)page * Hkv + kvh) * page_size + (pos % page_size)) * HD + lane * VEC;
-    }
-    const bool rotates = active && (is_q || is_k);
-    const bool in_table = (pos >= 0 && pos < table_len);
-    float c[VEC], sn[VEC], wn[VEC];
+    bool active[TOK], in_table[TOK];
+    bf16* dst[TOK];
+    float c[TOK][VEC], sn[TOK][VEC], wn[VEC];
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) { c[e] = 1.f; sn[e] = 0.f; wn[e] = 1.f; }
-    if (rotates && in_table) {
-        load_vec<VEC>(cos_t + (size_t)pos * HALF + (lane & 15) * VEC, c);
-        load_vec<VEC>(sin_t + (size_t)pos * HALF + (lane & 15) * VEC, sn);
-    }
-    if (rotates && has_norm) {
+    for (int e = 0; e < VEC; ++e) wn[e] = 1.f;
+    if (in_range && (is_q || is_k) && has_norm) {
         const VecRef& w = is_q ? qw : kw;
 #pragma unroll
         for (int e = 0; e < VEC; ++e) wn[e] = w.at(lane * VEC + e);
     }
-    pdl_wait();
-    if (!active) return;
-    const TI* src = qkv + (size_t)t * row_stride + (size_t)head * HD + lane * VEC;
-    float v[VEC];
-    headmath::load_parts<VEC, TI>(src, n_split, split_stride, v);
-    if (!is_q && !is_k) {  // value head: stored as it is
-        store_vec_bf16<VEC>(dst, v);
-        return;
+#pragma unroll
+    for (int u = 0; u < TOK; ++u) {
+        const int t = blockIdx.x * TOK + u;
+        const int seq = (in_range && t < T) ? tok_seq[t] : -1;
+        const int pos = (t < T) ? tok_pos[t] : 0;
+        active[u] = seq >= 0 && (is_q || write_kv);
+        dst[u] = q_out + (size_t)t * q_out_stride + (size_t)head * HD + lane * VEC;
+        if (active[u] && !is_q) {
+            const int page = block_table[(size_t)seq * bt_stride + pos / page_size];
+            if (page < 0) active[u] = false;
+            else dst[u] = (is_k ? k_cache : v_cache) + (((size_t)page * Hkv + kvh) * page_size + (pos % page_size)) * HD + lane * VEC;
+        }
+        in_table[u] = (pos >= 0 && pos < table_len);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) { c[u][e] = 1.f; sn[u][e] = 0.f; }
+        if (active[u] && (is_q || is_k) && in_table[u]) {
+            load_vec<VEC>(cos_t + (size_t)pos * HALF + (lane & 15) * VEC, c[u]);
+            load_vec<VEC>(sin_t + (size_t)pos * HALF + (lane & 15) * VEC, sn[u]);
+        }
     }
-    float o[VEC];
-    headmath::norm_rotate<VEC>(v, has_norm != 0, wn, eps, in_table, c, sn, lane, o);
-    store_vec_bf16<VEC>(dst, o);
+    pdl_wait();
+    float v[TOK][VEC];
+#pragma unroll
+    for (int u = 0; u < TOK; ++u) {
+        if (!active[u]) continue;
+        const int t = blockIdx.x * TOK + u;
+        headmath::load_parts<VEC, TI>(qkv + (size_t)t * row_stride + (size_t)head * HD + lane * VEC, n_split, split_stride, v[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < TOK; ++u) {
+        if (!active[u]) continue;
+        if (!is_q && !is_k) {  // value head: stored as it is
+            store_vec_bf16<VEC>(dst[u], v[u]);
+            continue;
+        }
+        float o[VEC];
+        headmath::norm_rotate<VEC>(v[u], has_norm != 0, wn, eps, in_table[u], c[u], sn[u], lane, o);
+        store_vec_bf16<VEC>(dst[u], o);
+    }
+}
+
+// For prompts: a CTA per token, its four warps share the token's heads (warp w takes heads w, w + 4,
+// ...), so the angles of the token's position are fetched once per warp and not once per head, and
+// four heads' loads are in flight per warp.  Same arithmetic (head_math.cuh).
+template <int VEC, typename TI>
+__global__ void __launch_bounds__(HP_WARPS * 32)
+head_prep_token_kernel(const TI* qkv, int n_split, size_t split_stride, bf16* q_out, size_t q_out_stride, int Hq,
+                       int Hkv, size_t row_stride, VecRef qw, VecRef kw, int has_norm, float eps,
+                       const float* __restrict__ cos_t, const float* __restrict__ sin_t, int table_len,
+                       const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                       const int* __restrict__ block_table, int bt_stride, bf16* __restrict__ k_cache,
+                       bf16* __restrict__ v_cache, int page_size, int write_kv) {
+    constexpr int HD = VEC * 32, HALF = HD / 2, UNROLL = 4;
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int seq = tok_seq[t];
+    const int pos = tok_pos[t];
+    const int page = (seq >= 0 && write_kv) ? block_table[(size_t)seq * bt_stride + pos / page_size] : -1;
+    const bool in_table = (pos >= 0 && pos < table_len);
+    float c[VEC], sn[VEC], wq[VEC], wk[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) { c[e] = 1.f; sn[e] = 0.f; wq[e] = 1.f; wk[e] = 1.f; }
+    if (seq >= 0 && in_table) {
+        load_vec<VEC>(cos_t + (size_t)pos * HALF + (lane & 15) * VEC, c);
+        load_vec<VEC>(sin_t + (size_t)pos * HALF + (lane & 15) * VEC, sn);
+    }
+    if (has_norm) {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) { wq[e] = qw.at(lane * VEC + e); wk[e] = kw.at(lane * VEC + e); }
+    }
+    pdl_wait();
+    if (seq < 0) return;
+    const int n_heads = Hq + 2 * Hkv;
+    const TI* row = qkv + (size_t)t * row_stride + lane * VEC;
+    for (int h0 = warp; h0 < n_heads; h0 += HP_WARPS * UNROLL) {
+        float v[UNROLL][VEC];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int head = h0 + u * HP_WARPS;
+            if (head < n_heads && (head < Hq || page >= 0))
+                headmath::load_parts<VEC, TI>(row + (size_t)head * HD, n_split, split_stride, v[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int head = h0 + u * HP_WARPS;
+            if (head >= n_heads) continue;
+            const bool is_q = head < Hq, is_k = !is_q && head < Hq + Hkv;
+            if (!is_q && page < 0) continue;
+            bf16* dst;
+            if (is_q) {
+                dst = q_out + (size_t)t * q_out_stride + (size_t)head * HD + lane * VEC;
+            } else {
+                const int kvh = is_k ? head - Hq : head - Hq - Hkv;
+                dst = (is_k ? k_cache : v_cache) + (((size_t)page * Hkv + kvh) * page_size + (pos % page_size)) * HD + lane * VEC;
+            }
+            if (!is_q && !is_k) {  // value head: stored as it is
+                store_vec_bf16<VEC>(dst, v[u]);
+                continue;
+            }
+            float o[VEC];
+            headmath::norm_rotate<VEC>(v[u], has_norm != 0, is_q ? wq : wk, eps, in_table, c, sn, lane, o);
+            store_vec_bf16<VEC>(dst, o);
+        }
+    }
 }
 
 // qkv: [n_split][T, (Hq + 2 Hkv) hd] of in_dtype (row stride row_stride, parts split_stride
@@ -173,15 +254,25 @@ extern "C" int odin_head_prep(const void* qkv, int in_dtype, int n_split, long l
     if (fast_in && dtype == ODIN_BF16 && rot == hd && (hd == 64 || hd == 128) && (row_stride % 4) == 0 &&
         (split_stride % 4) == 0 && (q_out_stride % 4) == 0 &&
         ((((uintptr_t)qkv) | ((uintptr_t)q_out) | ((uintptr_t)cos_t) | ((uintptr_t)sin_t)) & 15) == 0) {
-#define FAST(VEC, TI)                                                                                              \
-    odin_launch(head_prep_fast_kernel<VEC, TI>, grid, dim3(HP_WARPS * 32), 0, s, (const TI*)qkv, n_split,           \
-                (size_t)split_stride, (bf16*)q_out, (size_t)q_out_stride, Hq, Hkv, (size_t)row_stride, qw, kw,     \
-                has_norm, eps, cos_t, sin_t, table_len, tok_pos, tok_seq, block_table, bt_stride, (bf16*)k_cache,  \
-                (bf16*)v_cache, page_size, write_kv)
-        if (hd == 128 && in_dtype == ODIN_BF16) FAST(4, bf16);
-        else if (hd == 128) FAST(4, float);
-        else if (in_dtype == ODIN_BF16) FAST(2, bf16);
-        else FAST(2, float);
+#define FAST(VEC, TI, TOK)                                                                                         \
+    odin_launch(head_prep_fast_kernel<VEC, TI, TOK>, dim3((T + TOK - 1) / TOK, grid.y), dim3(HP_WARPS * 32), 0, s,     \
+                (const TI*)qkv, n_split, (size_t)split_stride, (bf16*)q_out, (size_t)q_out_stride, T, Hq, Hkv,         \
+                (size_t)row_stride, qw, kw, has_norm, eps, cos_t, sin_t, table_len, tok_pos, tok_seq, block_table,      \
+                bt_stride, (bf16*)k_cache, (bf16*)v_cache, page_size, write_kv)
+#define FAST_T(VEC, TI)                                                                                            \
+    do {                                                                                                           \
+        if (T >= 256)                                                                                              \
+            odin_launch(head_prep_token_kernel<VEC, TI>, dim3(T), dim3(HP_WARPS * 32), 0, s, (const TI*)qkv, n_split,  \
+                        (size_t)split_stride, (bf16*)q_out, (size_t)q_out_stride, Hq, Hkv, (size_t)row_stride, qw, kw, \
+                        has_norm, eps, cos_t, sin_t, table_len, tok_pos, tok_seq, block_table, bt_stride,              \
+                        (bf16*)k_cache, (bf16*)v_cache, page_size, write_kv);                                           \
+        else FAST(VEC, TI, 1);                                                                                     \
+    } while (0)
+        if (hd == 128 && in_dtype == ODIN_BF16) FAST_T(4, bf16);
+        else if (hd == 128) FAST_T(4, float);
+        else if (in_dtype == ODIN_BF16) FAST_T(2, bf16);
+        else FAST_T(2, float);
+#undef FAST_T
 #undef FAST
         ODIN_LAUNCH_CHECK();
         return 0;

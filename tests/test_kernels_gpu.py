@@ -194,6 +194,42 @@ def test_head_prep_and_attention_plain(geom, dtype):
         close(got, ref, 3e-6 if dtype == torch.float32 else 1e-2)
 
 
+@pytest.mark.parametrize("geom", [(8, 2, 128), (6, 3, 64)])
+@pytest.mark.parametrize("parts", [0, 2])
+def test_head_prep_many_tokens_equals_few_at_a_time(geom, parts):
+    """Prompts take a variant of the kernel that handles four tokens per warp: the same bits as the
+    one-token variant run on pieces of the rows; a row count that is no multiple of four, a
+    padding row, positions that differ per row."""
+    from odin_infer_b200.csrc import ops
+    n_q, n_kv, hd = geom
+    T, width = 517, (n_q + 2 * n_kv) * hd
+    torch.manual_seed(hd + parts)
+    lengths = [300, 217]
+    k_cache, v_cache, bt = paged_cache(2, lengths, n_kv, hd, torch.bfloat16)
+    tok_seq = torch.tensor([0] * 300 + [1] * 217, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor(list(range(300)) + list(range(217)), dtype=torch.int32, device=DEV)
+    tok_seq[77] = -1  # a padding row
+    qkv = torch.randn(T, width, device=DEV).bfloat16() if parts == 0 else torch.randn(parts, T, width, device=DEV)
+    qn = (1 + 0.1 * torch.randn(hd, device=DEV)).bfloat16()
+    kn = (1 + 0.1 * torch.randn(hd, device=DEV)).bfloat16()
+    ang = torch.arange(320, device=DEV, dtype=torch.float32)[:, None] * (1.0 / 10000 ** (torch.arange(hd // 2, device=DEV) / (hd // 2)))[None, :]
+    cos, sin = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
+    ka, va, kb, vb = k_cache.clone(), v_cache.clone(), k_cache.clone(), v_cache.clone()
+    q_all = torch.full((T, n_q * hd), 7.0, device=DEV, dtype=torch.bfloat16)
+    ops.head_prep(qkv, n_q, n_kv, hd, qn, kn, 1e-6, cos, sin, hd, tok_pos, tok_seq, bt, ka, va, q_out=q_all)
+    q_pieces = torch.full_like(q_all, 7.0)
+    for a in range(0, T, 100):
+        b = min(T, a + 100)
+        piece = qkv[a:b].contiguous() if parts == 0 else qkv[:, a:b].contiguous()
+        ops.head_prep(piece, n_q, n_kv, hd, qn, kn, 1e-6, cos, sin, hd, tok_pos[a:b].contiguous(),
+                      tok_seq[a:b].contiguous(), bt, kb, vb, q_out=q_pieces[a:b])
+    assert torch.equal(q_all, q_pieces)
+    assert torch.equal(q_all[77], torch.full_like(q_all[77], 7.0)), "a padding row must not be written"
+    # NaN marks the places that nobody wrote: they must agree too
+    assert torch.equal(torch.nan_to_num(ka.float(), nan=-1.0), torch.nan_to_num(kb.float(), nan=-1.0))
+    assert torch.equal(torch.nan_to_num(va.float(), nan=-1.0), torch.nan_to_num(vb.float(), nan=-1.0))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_attention_finds_a_far_key_and_respects_window(dtype):
     """One key far back among hundreds is made to stand out (its score dominates), so a
