@@ -1,7 +1,8 @@
 """Each part alone against the plain implementation's function for it, and a toy
-architecture defined HERE (a mixer with state of its own, a layer that runs twice, a
-layer that reads another layer's cache, a windowed layer with storage of its own),
-registered, built and stepped without touching the package's files."""
+architecture defined HERE (a mixer with state of its own, a feed-forward that routes each
+token to one of its experts, a second position encoding that acts on the embedded tokens,
+a layer that runs twice, a layer that reads another layer's cache, a windowed layer with
+storage of its own), registered, built and stepped without touching the package's files."""
 import dataclasses
 import math
 import os
@@ -156,6 +157,56 @@ def register_toy():
     from odin_infer_b200.config import ModelConfig, register_architecture
     from odin_infer_b200.config.base import KeyReader
     from odin_infer_b200.parts import Mixer, ModelSpec, ParamSpec, PartSpec, ScheduleEntry, register_part
+    from odin_infer_b200.parts.base import FeedForward, PositionEncoding
+
+    @register_part("feed_forward", "toy_top1_experts")
+    class Top1Experts(FeedForward):
+        """Each token goes to the expert whose router logit is largest (32-bit logits, the first
+        maximum wins) and gets that expert's SwiGLU."""
+
+        def __init__(self, width: int, inner: int, experts: int, prefix: str):
+            self.width, self.inner, self.experts, self.prefix = width, inner, experts, prefix
+            self.router, self.w = None, []
+
+        def params(self):
+            out = [ParamSpec(f"{self.prefix}.router", (self.experts, self.width))]
+            for e in range(self.experts):
+                out += [ParamSpec(f"{self.prefix}.e{e}.{k}", shape) for k, shape in
+                        (("gate", (self.inner, self.width)), ("up", (self.inner, self.width)), ("down", (self.width, self.inner)))]
+            return out
+
+        def bind(self, tensors, rt):
+            self.router = tensors[f"{self.prefix}.router"]
+            self.w = [tuple(tensors[f"{self.prefix}.e{e}.{k}"] for k in ("gate", "up", "down")) for e in range(self.experts)]
+
+        def forward(self, rt, step, h):
+            hf = h.float()
+            choice = torch.argmax(hf @ self.router.float().t(), dim=1)
+            out = torch.zeros(h.shape[0], self.width, dtype=torch.float32, device=h.device)
+            for e, (g, u, d) in enumerate(self.w):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    x = hf[rows]
+                    a = torch.nn.functional.silu(x @ g.float().t()) * (x @ u.float().t())
+                    out[rows] = a.to(h.dtype).float() @ d.float().t()
+            return out
+
+    @register_part("position_encoding", "toy_learned")
+    class LearnedPositions(PositionEncoding):
+        """A table of one vector per position, added to the embedded tokens."""
+
+        def __init__(self, width: int, max_positions: int, weight: str):
+            self.width, self.max_positions, self.weight_name, self.table = width, max_positions, weight, None
+
+        def params(self):
+            return [ParamSpec(self.weight_name, (self.max_positions, self.width))]
+
+        def bind(self, tensors, rt):
+            self.table = tensors[self.weight_name]
+
+        def on_embedding(self, rt, step, x):
+            n = step.n_tokens
+            x[:n] += self.table[step.tok_pos[:n].long()].float()
 
     @register_part("mixer", "toy_running_mean")
     class RunningMean(Mixer):
@@ -196,13 +247,16 @@ def register_toy():
         head_dim: int = 0
         inner: int = 0
         window: int = 0
+        experts: int = 0
+        max_positions: int = 0
         eps: float = 1e-6
         theta: float = 1e4
 
         @classmethod
         def from_dict(cls, raw, where="config.json"):
             r = KeyReader(raw, where)
-            vals = {k: r.get(k, int) for k in ("width", "vocab", "heads", "kv_heads", "head_dim", "inner", "window")}
+            vals = {k: r.get(k, int) for k in ("width", "vocab", "heads", "kv_heads", "head_dim", "inner", "window",
+                                               "experts", "max_positions")}
             r.finish()
             return cls(architecture=raw["architectures"][0], **vals)
 
@@ -218,19 +272,23 @@ def register_toy():
                                                   head_dim=cfg.head_dim, names=names, position_encoding="rope",
                                                   eps=cfg.eps, window=window, kv_shared=shared))
 
-        def block(l, mixer):
+        def block(l, mixer, routed=False):
             ffn = PartSpec("swiglu", dict(width=cfg.width, inner=cfg.inner,
                                           names={k: f"l{l}.ffn.{k}" for k in ("gate", "up", "down")}))
+            if routed:
+                ffn = PartSpec("toy_top1_experts", dict(width=cfg.width, inner=cfg.inner, experts=cfg.experts, prefix=f"l{l}.moe"))
             n1 = PartSpec("rmsnorm", dict(width=cfg.width, eps=cfg.eps, weight=f"l{l}.n1"))
             n2 = PartSpec("rmsnorm", dict(width=cfg.width, eps=cfg.eps, weight=f"l{l}.n2"))
             return PartSpec("prenorm", dict(mixer=mixer, feed_forward=ffn, norm_mixer=n1, norm_feed_forward=n2))
         layers = (block(0, attn("l0.att")), block(1, attn("l1.att", window=cfg.window)),
                   block(2, attn("l2.att", shared=True)),
-                  block(3, PartSpec("toy_running_mean", dict(width=cfg.width, weight="l3.mix"))))
+                  block(3, PartSpec("toy_running_mean", dict(width=cfg.width, weight="l3.mix")), routed=True))
         return ModelSpec(
             width=cfg.width, vocab_size=cfg.vocab,
             embedding=PartSpec("token_table", dict(vocab_size=cfg.vocab, width=cfg.width, weight="emb")),
-            position_encodings={"rope": PartSpec("rope", dict(rotary_dim=cfg.head_dim, theta=cfg.theta))},
+            position_encodings={"rope": PartSpec("rope", dict(rotary_dim=cfg.head_dim, theta=cfg.theta)),
+                                "learned": PartSpec("toy_learned", dict(width=cfg.width, max_positions=cfg.max_positions,
+                                                                        weight="pos"))},
             layers=layers,
             # layer 0 runs twice (each run keeps its own cache); layer 2 reads the cache of the first run
             schedule=(ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(2, reads_cache_of=0), ScheduleEntry(3)),
@@ -241,11 +299,14 @@ def register_toy():
     return ToyConfig
 
 
-TOY = dict(architectures=["ToyForCausalLM"], width=64, vocab=200, heads=4, kv_heads=2, head_dim=16, inner=96, window=40)
+TOY = dict(architectures=["ToyForCausalLM"], width=64, vocab=200, heads=4, kv_heads=2, head_dim=16, inner=96, window=40,
+           experts=3, max_positions=256)
 
 
 def toy_plain(w, cfg, tokens):
-    """The toy model, whole sequence, with the plain implementation's functions."""
+    """The toy model, whole sequence, with the plain implementation's functions.  Returns the logits and,
+    per position, by how much the chosen expert's router logit leads (a small lead may go the other
+    way under rounding)."""
     T = len(tokens)
     hq, hkv, hd, eps = cfg["heads"], cfg["kv_heads"], cfg["head_dim"], 1e-6
     cos, sin = P.rope_tables(T, hd, 1e4, torch.float64)
@@ -259,7 +320,7 @@ def toy_plain(w, cfg, tokens):
 
     def ffn(l, x):
         return P.swiglu_mlp(P.rmsnorm(x, w[f"l{l}.n2"], eps), w[f"l{l}.ffn.gate"], w[f"l{l}.ffn.up"], w[f"l{l}.ffn.down"])
-    x = P.embedding(w["emb"], tokens)
+    x = P.embedding(w["emb"], tokens) + w["pos"][:T]
     # entry 0: layer 0
     q, k0, v0 = qkv("l0.att", P.rmsnorm(x, w["l0.n1"], eps))
     x = x + P.linear(P.causal_attention(q, k0, v0), w["l0.att.o"])
@@ -280,8 +341,16 @@ def toy_plain(w, cfg, tokens):
     h = P.rmsnorm(x, w["l3.n1"], eps)
     mean = torch.cumsum(h, 0) / torch.arange(1, T + 1, dtype=h.dtype)[:, None]
     x = x + P.linear(mean, w["l3.mix"])
-    x = x + ffn(3, x)
-    return P.linear(P.rmsnorm(x, w["final"], eps), w["emb"])
+    h = P.rmsnorm(x, w["l3.n2"], eps)
+    router = P.linear(h, w["l3.moe.router"])
+    top2 = torch.topk(router, 2, dim=1).values
+    choice = torch.argmax(router, dim=1)
+    routed = torch.zeros_like(x)
+    for t in range(T):
+        e = int(choice[t])
+        routed[t] = P.swiglu_mlp(h[t:t + 1], w[f"l3.moe.e{e}.gate"], w[f"l3.moe.e{e}.up"], w[f"l3.moe.e{e}.down"])[0]
+    x = x + routed
+    return P.linear(P.rmsnorm(x, w["final"], eps), w["emb"]), (top2[:, 0] - top2[:, 1]) / router.abs().max()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -294,8 +363,13 @@ def test_toy_architecture_registers_builds_and_steps(tmp_path, dtype):
     folder = write_random_model(str(tmp_path / "toy"), config_from_dict(TOY), seed=21)
     _, w = P.read_model_folder(folder, torch.float64)
     assert "l2.att.k" not in w and "head" not in w and "l3.mix" in w      # shared kv: no k/v; tied head
+    assert "l3.moe.e2.down" in w and "l3.ffn.gate" not in w and tuple(w["pos"].shape) == (256, 64)
     reqs = {f"r{i}": tiny.random_tokens(n, TOY["vocab"], 50 + i) for i, n in enumerate([3, 70, 150, 41])}
-    refs = {rid: toy_plain(w, TOY, toks).numpy() for rid, toks in reqs.items()}
+    refs, leads = {}, {}
+    for rid, toks in reqs.items():
+        logits, lead = toy_plain(w, TOY, toks)
+        refs[rid], leads[rid] = logits.numpy(), lead.numpy()
+    assert sum(int((l > 0.05).sum()) for l in leads.values()) > 150, "most positions have a clear choice of expert"
     tol = tiny.TOL[dtype]
     for what, recs in (("whole", traces.whole(reqs)), ("tail", traces.tail_one_by_one(reqs, 32)),
                        ("batches", traces.batches(reqs, 2))):
@@ -309,6 +383,8 @@ def test_toy_architecture_registers_builds_and_steps(tmp_path, dtype):
         e.cache.check()
         for rid, ref in refs.items():
             for pos in range(ref.shape[0]):
+                if leads[rid][pos] <= 0.05:  # a near tie between experts: rounding may decide it the other way
+                    continue
                 err = tiny.rel_err(got[rid][pos], ref[pos])
                 assert err <= tol, f"toy {what} {dtype}: request {rid} first differs at position {pos}: {err:.3e}"
         e.destroy()
