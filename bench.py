@@ -180,6 +180,89 @@ def run_e2e(engine, batch, steps, vocab):
     return stats
 
 
+SHAPE_1P7B = dict(architectures=["Qwen3ForCausalLM"], hidden_size=2048, intermediate_size=6144, num_hidden_layers=28,
+                  num_attention_heads=16, num_key_value_heads=8, head_dim=128, vocab_size=151936, rope_theta=1e6,
+                  rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=40960)
+SHAPE_32B = dict(architectures=["Qwen3ForCausalLM"], hidden_size=5120, intermediate_size=25600, num_hidden_layers=64,
+                 num_attention_heads=64, num_key_value_heads=8, head_dim=128, vocab_size=151936, rope_theta=1e6,
+                 rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=40960)
+
+
+def other_workload(which: str) -> int:
+    """BASELINE.json configs[3] and configs[4]; one JSON line each, device-timed unless said otherwise."""
+    import time
+
+    import numpy as np
+    import torch
+    from odin_infer_b200 import Engine, Engine_Opts, StepEntry
+    from odin_infer_b200.config import config_from_dict
+    from odin_infer_b200.csrc import ops
+    from odin_infer_b200.engine.generate import GenerationStats
+    peaks, peak_source = load_peaks()
+    if which == "1.7b-mixed":
+        raw = dict(SHAPE_1P7B)
+        rng = np.random.default_rng(11)
+        lens = rng.integers(16, 2049, 64)
+        prompts = [rng.integers(0, raw["vocab_size"], int(n)).tolist() for n in lens]
+        need = sum((int(n) + 128 + 63) // 64 * 64 for n in lens)
+        e = Engine.random(config_from_dict(raw), 6, Engine_Opts(max_ctx=4096, max_tokens=need, max_batch=64,
+                                                                dtype="bfloat16", verbose=False))
+        e.generate(prompts[:4], max_new_tokens=4, stop_token_ids=[])  # warm-up: kernels, graphs of a small batch
+        st = GenerationStats()
+        t0 = time.perf_counter()
+        e.generate(prompts, max_new_tokens=128, stop_token_ids=[], stats=st)
+        total = time.perf_counter() - t0
+        out = {"metric": "Qwen3-1.7B shape, bf16: 64 prompts of 16..2048 tokens in one batch, 128 new tokens each, "
+                         "through Engine.generate (host clock)", "prompt_tokens": int(lens.sum()),
+               "ttft_ms": round(st.ttft_s * 1e3, 1), "prefill_tokens_per_s": round(float(lens.sum()) / st.ttft_s),
+               "decode_tokens_per_s": round(st.decode_tokens_per_s), "total_s": round(total, 3), "batches": st.n_batches}
+    else:
+        raw = dict(SHAPE_32B)
+        e = Engine.random(config_from_dict(raw), 7, Engine_Opts(max_ctx=8192, max_tokens=8 * 8192, max_batch=8,
+                                                                dtype="bfloat16", verbose=False))
+        rng = np.random.default_rng(12)
+        L = raw["num_hidden_layers"]
+        out = {"metric": "Qwen3-32B shape, bf16, 64 layers: a 2,048-token prompt; decoding at context 8192", "peak_source": peak_source}
+        for _ in range(3):
+            s = e.take_slot()
+            p = rng.integers(0, raw["vocab_size"], 2048).tolist()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            e.step([StepEntry(s, p, [2047])])
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b)
+            e.give_back_slot(s)
+        out["prefill"] = {"tokens": 2048, "ms": round(ms, 2), "value": round(2048 / ms * 1e3),
+                          "frac": round(prefill_flops(raw, L, 2048) / (ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}
+        for B in (1, 8):
+            slots = [e.take_slot() for _ in range(B)]
+            ctx0 = 8192 - 72
+            for a0 in range(0, ctx0, 2048):  # the context, in pieces of 2,048 tokens
+                n = min(2048, ctx0 - a0)
+                e.step([StepEntry(s, rng.integers(0, raw["vocab_size"], n).tolist(), []) for s in slots])
+            feed = rng.integers(0, raw["vocab_size"], (72, B))
+            for i in range(8):
+                e.step([StepEntry(s, [int(feed[i, b])], [0]) for b, s in enumerate(slots)])
+            torch.cuda.synchronize()
+            a, b2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for i in range(8, 72):
+                e.step([StepEntry(s, [int(feed[i, b])], [0]) for b, s in enumerate(slots)])
+            b2.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b2) / 64
+            out[f"decode_b{B}"] = {"ms_per_step": round(ms, 3), "value": round(B / ms * 1e3, 1), "context": 8192 - 32,
+                                   "hbm_frac": round(decode_bytes(raw, L, B, 8192 - 32) / (ms / 1e3) / 1e9 / peaks["hbm_gbs"], 4)}
+            for s in slots:
+                e.give_back_slot(s)
+    ops.gemm_tc_check()
+    ops.attention_prefill_check()
+    ops.attention_decode_check()
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -191,6 +274,10 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for profilers)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end run (for profilers)")
+    ap.add_argument("--workload", default="8b", choices=["8b", "1.7b-mixed", "32b-long"],
+                    help="8b: the contract's run (default).  The others are further workloads of the baseline's list and "
+                         "print a line of their own: 1.7b-mixed = Qwen3-1.7B shape, 64 prompts of 16..2048 tokens, 128 new "
+                         "tokens each; 32b-long = Qwen3-32B shape, a 2,048-token prompt, decoding 1 and 8 sequences at context 8192")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -202,6 +289,8 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     warmup = max(args.warmup, 3)
+    if args.workload != "8b":
+        return other_workload(args.workload)
 
     import torch
     from odin_infer_b200 import Engine, Engine_Opts
