@@ -78,6 +78,21 @@ def test_swiglu(dtype):
     close(out, g * torch.sigmoid(g) * u, 2e-6 if dtype == torch.float32 else 5e-3)
 
 
+@pytest.mark.parametrize("case", [(8, 12288, 3), (64, 1000, 2), (3, 204, 7), (5, 203, 2), (1, 64, 1)])
+def test_swiglu_of_partial_sums(case):
+    """The 32-bit partial sums of a split product in, bfloat16 out (the decode step's use): the vector
+    kernel where the width allows it, the scalar one else, both against the formula in float64."""
+    from odin_infer_b200.csrc import ops
+    T, I, parts = case
+    torch.manual_seed(I)
+    gu = torch.randn(parts, T, 2 * I, device=DEV) * (2.0 / math.sqrt(parts))
+    out = torch.full((T, I), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops.swiglu(gu, out)
+    sums = gu.double().sum(0)
+    g, u = sums[:, :I], sums[:, I:]
+    close(out, g * torch.sigmoid(g) * u, 5e-3)
+
+
 @pytest.mark.parametrize("shape", [(1, 5, 3), (7, 130, 72), (65, 64, 16), (130, 301, 200), (3, 1000, 1032)])
 @pytest.mark.parametrize("combo", [(torch.float32,) * 3, (torch.bfloat16,) * 3,
                                    (torch.bfloat16, torch.bfloat16, torch.float32),
