@@ -37,6 +37,7 @@ def choose_k_split(n_tiles: int, k_blocks: int, m: int, n_sms: int = 148, max_sp
 # unless ODIN_FUSE_SINKS=1; the tests run it both ways.
 FUSE_SINKS = os.environ.get("ODIN_FUSE_SINKS", "0") == "1"
 
+
 def fuse_sinks() -> bool:
     return FUSE_SINKS
 
