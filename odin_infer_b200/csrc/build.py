@@ -33,6 +33,7 @@ GROUPS = {
     "sampling": ["sampling.cu"],
     "gemm_tc": ["gemm_tc.cu", "gemm_tc2.cu"],
     "attention_decode": ["attention_decode.cu"],
+    "decode_program": ["decode_program.cu"],
     "attention_prefill": ["attention_prefill.cu", "attention_prefill_tc.cu"],
 }
 HEADERS = ["common.cuh"]

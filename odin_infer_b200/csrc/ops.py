@@ -67,9 +67,99 @@ def _check(code: int, what: str, kernels: int = 1) -> None:
 
 
 def _fn(group: str, name: str):
+    """A launcher of the kernel libraries.  While a program is being recorded, every kernel that
+    is not part of it runs after what has been recorded so far."""
+    if _program_bn and group != "decode_program":
+        program_flush()
     f = getattr(build.load(group), name)
     f.restype = c_int
     return f
+
+
+# ---------------------------------------------------------------------------- programs
+# A decode step of few tokens can run as a program: while one is being recorded, the wrappers
+# below hand the operations that a program can hold (products of few tokens with 32-bit partial
+# sums, residual add + RMSNorm, SwiGLU of partial sums, decode attention with head preparation)
+# to the persistent kernel of decode_program.cu instead of launching a kernel each.  Whatever
+# else is launched in between flushes the program first, so the order of the stream is kept.
+_program_bn = 0  # > 0: the token bucket of the program being recorded
+
+
+def recording() -> bool:
+    return _program_bn > 0
+
+
+def _prog(name: str):
+    f = getattr(build.load("decode_program"), name)
+    f.restype = c_int
+    return f
+
+
+def _program_count() -> None:
+    """Programs launched since the last call count as kernels."""
+    global _launches, _program_seen
+    f = build.load("decode_program").odin_prog_launches
+    f.restype = c_longlong
+    n = int(f())
+    _launches += n - _program_seen
+    _program_seen = n
+
+
+_program_seen = 0
+
+
+def program_flush() -> None:
+    code = _prog("odin_prog_flush")(_stream())
+    _program_count()
+    _check(code, "decode program", kernels=0)
+
+
+class program:
+    """`with ops.program(bn):` records the operations of a step of at most bn tokens (16, 32 or
+    64) and launches them as programs; only kernels of this package may run inside (a torch
+    operation between two of them would run ahead of the recorded ones)."""
+
+    def __init__(self, bn: int):
+        self.bn = bn
+
+    def __enter__(self):
+        global _program_bn
+        if _program_bn:
+            raise KernelError("a program is already being recorded")
+        _check(_prog("odin_prog_begin")(c_int(self.bn)), "decode program", kernels=0)
+        _program_bn = self.bn
+        return self
+
+    def __exit__(self, *exc):
+        global _program_bn
+        _program_bn = 0
+        code = _prog("odin_prog_end")(_stream())
+        _program_count()
+        if exc[0] is None:
+            _check(code, "decode program", kernels=0)
+        return False
+
+
+def program_bucket(n_tokens: int) -> int:
+    """The token bucket of a program for n_tokens, 0 if there is none."""
+    return 16 if n_tokens <= 16 else 32 if n_tokens <= 32 else 64 if n_tokens <= 64 else 0
+
+
+def program_check() -> None:
+    detail = (c_int * 8)()
+    v = _prog("odin_prog_error")(detail)
+    if v != 0:
+        raise KernelError(f"decode program: a device-side wait ran out; results are invalid (wait, block, operation, "
+                          f"item, K block, slot, grid: {list(detail)[:7]})")
+
+
+def _recorded(code: int, what: str) -> bool:
+    """The answer of an odin_prog_* call: recorded, or to be launched as a kernel of its own."""
+    if code == -1:
+        return False
+    _program_count()
+    _check(code, what, kernels=0)
+    return True
 
 
 # ----------------------------------------------------------------------------
@@ -106,6 +196,11 @@ def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tenso
     else:
         assert rows.dtype == torch.int32 and rows.numel() == n_rows
     assert weight.numel() == d
+    if (_program_bn and rows is None and out.dtype == torch.bfloat16 and (delta is None or delta.dtype == torch.float32)
+            and _recorded(_prog("odin_prog_add_rmsnorm")(
+                _ptr(x), _ptr(delta), c_int(n_split), c_longlong(stride), _ptr(weight), c_int(dtype_code(weight.dtype)),
+                c_float(eps), _ptr(out), c_int(n_rows), c_int(d), _stream()), "add_rmsnorm")):
+        return
     _check(_fn("elementwise", "odin_add_rmsnorm")(
         _ptr(x), _ptr(delta), c_int(dtype_code(delta.dtype) if delta is not None else 0), c_int(n_split),
         c_longlong(stride), _ptr(weight), c_int(dtype_code(weight.dtype)), c_float(eps), _ptr(out),
@@ -118,6 +213,10 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     T, I = out.shape
     assert gate_up.is_contiguous() and out.is_contiguous() and tuple(gate_up.shape[-2:]) == (T, 2 * I)
     n_split, stride = (gate_up.shape[0], T * 2 * I) if gate_up.dim() == 3 else (1, 0)
+    if (_program_bn and gate_up.dtype == torch.float32 and out.dtype == torch.bfloat16
+            and _recorded(_prog("odin_prog_swiglu")(_ptr(gate_up), c_int(n_split), c_longlong(stride), _ptr(out),
+                                                    c_int(T), c_int(I), _stream()), "swiglu")):
+        return
     _check(_fn("elementwise", "odin_swiglu")(
         _ptr(gate_up), c_int(dtype_code(gate_up.dtype)), c_int(n_split), c_longlong(stride), _ptr(out),
         c_int(dtype_code(out.dtype)), c_int(T), c_int(I), _stream()), "swiglu")
@@ -194,13 +293,19 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, bn: 
     if not gemm_tc_supported(a, w):
         raise KernelError("gemm_tc: operands must be bfloat16 with 16-byte aligned rows (K and strides multiples of 8)")
     assert w.shape[1] == K and out.stride(-1) == 1
-    if n_split > 1:
+    if n_split > 1 or out.dim() == 3:
         assert out.dtype == torch.float32 and out.dim() == 3 and tuple(out.shape[1:]) == (M, N)
         assert out.shape[0] == gemm_tc_splits(K, n_split), "allocate gemm_tc_splits(K, n_split) slices"
         ldc, stride = out.stride(1), out.stride(0)
     else:
         assert tuple(out.shape) == (M, N)
         ldc, stride = out.stride(0), 0
+    if (_program_bn and mode == 1 and out.dtype == torch.float32 and out.dim() == 3 and row_ssq is None and sink is None
+            and _recorded(_prog("odin_prog_gemm")(
+                _ptr(a), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K), c_longlong(a.stride(0)),
+                c_longlong(w.stride(0)), c_longlong(out.stride(1)), c_int(out.shape[0]), c_longlong(out.stride(0)),
+                _stream()), "gemm_tc")):
+        return
     extras = None
     if row_ssq is not None or sink is not None:
         extras = _GemmExtras()
@@ -397,6 +502,14 @@ def attention_decode_fused(qkv: torch.Tensor, out: torch.Tensor, n_q: int, n_kv:
                          and k_norm.numel() == head_dim):
         return False
     assert scratch.dtype == torch.float32 and scratch.numel() >= attention_decode_scratch(B, n_q, head_dim, n_split)
+    if (_program_bn and qkv.dtype == torch.float32 and _recorded(_prog("odin_prog_attention")(
+            _ptr(qkv), c_int(parts), c_longlong(part_stride), c_longlong(row_stride), _ptr(out),
+            c_longlong(out.stride(0)), c_int(B), c_int(n_q), c_int(n_kv), c_int(head_dim), _ptr(q_norm), _ptr(k_norm),
+            c_int(dtype_code(q_norm.dtype) if has_norm else 0), c_int(1 if has_norm else 0), c_float(eps), _ptr(cos),
+            _ptr(sin), c_int(rotary_dim), c_int(cos.shape[0]), _ptr(k_cache), _ptr(v_cache), c_int(PAGE),
+            c_int(k_cache.shape[0]), _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table), c_int(block_table.stride(0)),
+            c_int(window), _ptr(scratch), c_int(n_split), c_int(1 if write_kv else 0), _stream()), "attention")):
+        return True
     code = _fn("attention_decode", "odin_attention_decode_fused")(
         _ptr(qkv), c_int(dtype_code(qkv.dtype)), c_int(parts), c_longlong(part_stride), c_longlong(row_stride),
         _ptr(out), c_longlong(out.stride(0)), c_int(B), c_int(n_q), c_int(n_kv), c_int(head_dim), _ptr(q_norm),

@@ -45,12 +45,12 @@ class DecodeGraphs:
                               all_rows_wanted=True)
             # once eagerly: first-use set-up of the kernels (function attributes, tensor maps,
             # error flags, the allocator's pools) must not fall into the capture
-            self.model.forward(self.rt, batch)
+            self.rt.run(self.model, batch)
             torch.cuda.current_stream().synchronize()
             graph = torch.cuda.CUDAGraph()
             n0 = ops.launch_count()
             with torch.cuda.graph(graph):
-                logits = self.model.forward(self.rt, batch)
+                logits = self.rt.run(self.model, batch)
             self._graphs[bucket] = (graph, batch, logits, ops.launch_count() - n0)
             # the eager run and the capture have written this step's keys already; a replay writes them again
         else:

@@ -41,6 +41,11 @@ class DecoderModel:
     def kernel_groups(self) -> set[str]:
         return set().union(*(p.kernel_groups() for p in self._all_parts()))
 
+    @property
+    def kernels_only(self) -> bool:
+        """Do all parts launch kernels of this package only (see Part.kernels_only)?"""
+        return all(p.kernels_only for p in self._all_parts())
+
     def bind(self, tensors: dict[str, torch.Tensor], rt, n_positions: int) -> None:
         for part in self._all_parts():
             part.bind(tensors, rt)

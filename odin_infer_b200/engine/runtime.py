@@ -42,6 +42,14 @@ def fuse_sinks() -> bool:
     return FUSE_SINKS
 
 
+# Decode steps of few tokens can run as programs of one persistent kernel (csrc/decode_program.cu)
+# instead of a kernel per operation: a layer is then one launch with barriers across the grid
+# between its operations.  Its products stream their weights faster (the requests never stop at
+# an operation's end), but the operations between them no longer overlap the products' ends as
+# co-resident kernels do, and a layer takes 150 us against 95 on the 8B shape.  Off unless
+# ODIN_DECODE_PROGRAM=1; the tests run it both ways.
+DECODE_PROGRAM = os.environ.get("ODIN_DECODE_PROGRAM", "0") == "1"
+
 # from this many tokens on a product runs on pairs of SMs (tiles of 256 token rows)
 PAIR_MIN_TOKENS = 256
 
@@ -76,14 +84,21 @@ class Runtime:
 
     def kernel_groups(self) -> set[str]:
         """Kernel libraries the runtime itself may launch, beside those of the parts."""
-        return {"gemm_tc", "attention_decode", "attention_prefill"} if self.dtype == torch.bfloat16 else set()
+        return ({"gemm_tc", "attention_decode", "attention_prefill", "decode_program"}
+                if self.dtype == torch.bfloat16 else set())
 
     def context_class(self, longest: int) -> int:
         """Contexts of one class launch the same kernels (see decode_key_splits)."""
         return context_class_of(longest)
 
     def run(self, model, batch):
-        """Run one step of `model` eagerly; returns the logits at the wanted rows."""
+        """Run one step of `model` eagerly; returns the logits at the wanted rows.  One token per
+        sequence, bfloat16, a model whose parts launch kernels of this package only: the step's
+        operations are recorded and run as programs."""
+        bucket = ops.program_bucket(batch.n_rows) if batch.all_single else 0
+        if DECODE_PROGRAM and self.dtype == torch.bfloat16 and bucket and getattr(model, "kernels_only", False):
+            with ops.program(bucket):
+                return model.forward(self, batch)
         return model.forward(self, batch)
 
     def empty(self, *shape, dtype: torch.dtype | None = None) -> torch.Tensor:
@@ -135,7 +150,7 @@ class Runtime:
                     ops.gemm_tc(rows, w, scratch, 1, bn, n_split, stages,
                                 sink=(sink.x, sink.norm.weight, normed, ssq), **scale)
                     return NormedRows(normed, ssq, N, sink.norm.eps, sink.norm)
-                if n_split > 1:
+                if n_split > 1 or (may_split and ops.recording()):  # a program's products write 32-bit sums only
                     out = self.empty(n_split, M, N, dtype=torch.float32)
                     ops.gemm_tc(rows, w, out, 1, bn, n_split, stages, **scale)
                     return out

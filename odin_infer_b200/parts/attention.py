@@ -19,6 +19,8 @@ class GQAttention(Mixer):
     The three projection matrices are fused into one at load time.
     """
 
+    kernels_only = True
+
     def __init__(self, width: int, n_q_heads: int, n_kv_heads: int, head_dim: int, names: dict,
                  position_encoding: str | None = None, qk_norm: bool = True, eps: float = 1e-6,
                  window: int = 0, kv_shared: bool = False):

@@ -55,6 +55,12 @@ class Part:
     def bind(self, tensors: dict[str, torch.Tensor], rt) -> None:
         pass
 
+    # True for a part whose forward launches kernels of this package only (through `ops` and the
+    # runtime) and calls nothing that would put other work on the stream: only then may the
+    # runtime record a decode step's operations and run them as programs of one persistent
+    # kernel, where the order of launches is no longer the order of execution for anything else.
+    kernels_only = False
+
     def kernel_groups(self) -> set[str]:
         """Kernel libraries this part launches (compiled before the first step)."""
         return set()

@@ -37,6 +37,10 @@ class PreNormBlock(Block):
     takes_next_norm = True
 
     @property
+    def kernels_only(self):
+        return all(p.kernels_only for p in self._parts())
+
+    @property
     def first_norm(self):
         return self.norm_mixer
 

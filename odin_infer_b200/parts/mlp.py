@@ -12,6 +12,8 @@ class SwiGLU(FeedForward):
     """down( silu(gate(x)) * up(x) ), no bias (infer/forward.odin:125-135).  The gate
     and up matrices are fused into one at load time."""
 
+    kernels_only = True
+
     def __init__(self, width: int, inner: int, names: dict):
         self.width, self.inner, self.names = width, inner, dict(names)
         self.w_gate_up = self.w_down = None

@@ -11,6 +11,8 @@ from .base import Norm, NormedRows, ParamSpec, ResidualAdded, ResidualSink, regi
 class RMSNorm(Norm):
     """o = w * (x / sqrt(mean(x^2) + eps)), in 32-bit (infer/ops.odin:7-19)."""
 
+    kernels_only = True
+
     def __init__(self, width: int, eps: float, weight: str):
         self.width, self.eps, self.weight_name = width, float(eps), weight
         self.weight: torch.Tensor | None = None

@@ -14,6 +14,8 @@ class RotaryEncoding(PositionEncoding):
     32-bit as the reference does (infer/forward.odin:67-70); cos and sin of that
     angle are tabulated on the host, so every kernel reads the same values."""
 
+    kernels_only = True
+
     def __init__(self, rotary_dim: int, theta: float):
         if rotary_dim % 2:
             raise ValueError(f"rotary_dim must be even, got {rotary_dim}")
@@ -36,3 +38,5 @@ class RotaryEncoding(PositionEncoding):
 @register_part("position_encoding", "none")
 class NoEncoding(PositionEncoding):
     """No position information beyond the causal mask."""
+
+    kernels_only = True

@@ -86,6 +86,16 @@ def test_last_32_one_by_one_with_sinks(folders, requests_and_refs, name, monkeyp
     check(run(folders[name], "bfloat16", traces.tail_one_by_one(reqs, 32)), refs, "bfloat16", "sinks")
 
 
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+def test_last_32_one_by_one_as_programs(folders, requests_and_refs, name, monkeypatch):
+    """The same with each decode step run as programs of one persistent kernel (off by default)."""
+    from odin_infer_b200.engine import runtime
+    monkeypatch.setattr(runtime, "DECODE_PROGRAM", True)
+    reqs, refs = requests_and_refs[name]
+    check(run(folders[name], "bfloat16", traces.tail_one_by_one(reqs, 32)), refs, "bfloat16", "programs")
+    check(run(folders[name], "bfloat16", traces.batches(reqs, 3)), refs, "bfloat16", "programs, batches of 3")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_unequal_batches_slots_reused(folders, requests_and_refs, name, dtype):
