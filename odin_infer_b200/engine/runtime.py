@@ -84,8 +84,10 @@ class Runtime:
 
     def kernel_groups(self) -> set[str]:
         """Kernel libraries the runtime itself may launch, beside those of the parts."""
-        return ({"gemm_tc", "attention_decode", "attention_prefill", "decode_program"}
-                if self.dtype == torch.bfloat16 else set())
+        if self.dtype != torch.bfloat16:
+            return set()
+        groups = {"gemm_tc", "attention_decode", "attention_prefill"}
+        return groups | {"decode_program"} if DECODE_PROGRAM else groups  # else built when first asked for
 
     def context_class(self, longest: int) -> int:
         """Contexts of one class launch the same kernels (see decode_key_splits)."""
