@@ -16,7 +16,7 @@ import torch
 from ..cache import CacheManager, PAGE, pages_for
 from ..config import ModelConfig, load_config, lookup_architecture
 from ..csrc import build as kernel_build
-from ..sampling import SamplingParams, sample_batch
+from ..sampling import PendingTokens, SamplingParams, sample_batch, sample_batch_async
 from ..weights import load_weights, random_weights
 from .graphs import DecodeGraphs
 from .generate import GenerationResult, GenerationStats, generate
@@ -34,7 +34,8 @@ class Engine_Opts:
     that live sequences hold together, each rounded up to a page of 64; it sizes the
     cache (0: max_batch sequences of max_ctx).  dtype: "bfloat16" (the kernels and
     precisions of serving) or "float32" (everything in true 32-bit).  cuda_graphs: replay
-    captured graphs for one-token-per-sequence steps (bfloat16 only)."""
+    captured graphs for one-token-per-sequence steps (bfloat16 only).  run_ahead: generation
+    launches a decode step before the host has read the tokens it continues from."""
     max_ctx: int = DEFAULT_MAX_CONTEXT
     max_tokens: int = 0
     max_batch: int = 8
@@ -42,6 +43,7 @@ class Engine_Opts:
     device: str = "cuda:0"
     verbose: bool = True
     cuda_graphs: bool = True
+    run_ahead: bool = True
 
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
@@ -56,6 +58,7 @@ class Engine:
         self.config = config
         self.opts = opts
         self.rt = Runtime(opts.device, _DTYPES[opts.dtype])
+        self.run_ahead = opts.run_ahead
         torch.cuda.set_device(self.rt.device)
         spec = lookup_architecture(config.architecture).build_spec(config)
         self.spec = spec
@@ -135,10 +138,14 @@ class Engine:
         return tuple(self.spec.stop_token_ids)
 
     # ---- the step function ---------------------------------------------
-    def step(self, entries: list[StepEntry]) -> torch.Tensor | None:
+    def step(self, entries: list[StepEntry], device_tokens=None) -> torch.Tensor | None:
         """Run the given tokens of every entry as one batch from the cache; returns the
         32-bit logits at the wanted places, [wanted, vocab], on the device, in the order
-        of the entries and of their `want` lists (None when nothing is wanted)."""
+        of the entries and of their `want` lists (None when nothing is wanted).
+
+        device_tokens = (tokens, src): every entry brings one token whose value is still on the
+        device: entry b's is tokens[src[b]] (tokens[b] if src is None), tokens an int32 tensor as
+        `sample_async` leaves it; the entries' own token values are placeholders then."""
         if not entries:
             return None
         seen = set()
@@ -163,11 +170,15 @@ class Engine:
                 self._shrink(e.slot, s)
             raise
         logits = NotImplemented
+        if device_tokens is not None and any(len(e.tokens) != 1 for e in entries):
+            raise StepError("tokens from the device: one token per sequence")
         if self.graphs is not None and all(len(e.tokens) == 1 for e in entries):
-            logits = self.graphs.run(entries, starts)
+            logits = self.graphs.run(entries, starts, device_tokens)
             self.last_step_h2d_bytes = self.graphs.last_h2d_bytes
         if logits is NotImplemented:
             batch = StepBatch(self.cache, entries, starts, self.rt.device)
+            if device_tokens is not None:
+                batch.take_tokens(*device_tokens)
             logits = self.rt.run(self.model, batch)
             self.last_step_h2d_bytes = batch.h2d_bytes
         for e in entries:
@@ -185,6 +196,11 @@ class Engine:
     # ---- sampling and generation ----------------------------------------
     def sample(self, logits: torch.Tensor, samplers, params: SamplingParams) -> list[int]:
         return sample_batch(logits, samplers, params)
+
+    def sample_async(self, logits: torch.Tensor, samplers, params: SamplingParams) -> PendingTokens:
+        """Sampling that leaves the tokens on the device (for the next step's `device_tokens`) and
+        copies them to the host in the background; `.tokens()` waits for that copy."""
+        return sample_batch_async(logits, samplers, params)
 
     def generate(self, prompts, max_new_tokens: int = 256, temperature: float = 0.0, top_p: float = 1.0,
                  seed: int = 0, stop_token_ids=None, repetition_penalty: float = 1.0, include_stop_token: bool = False,

@@ -8,9 +8,17 @@ not fed back: serve_harness/serve.odin:514-515 checks EOS before emitting), afte
 finish reason "length"); it then leaves the batch, which goes on smaller.  When
 a batch is done its slots are given back and the next batch takes them.
 
+With an engine whose sampling can leave the tokens on the device (`sample_async`,
+and `step(..., device_tokens=...)`), the loop runs one step ahead of the host: it
+launches the next decode step on the tokens that are still on the device and reads
+the previous step's tokens while that step runs, so the host's share of a step
+hides behind the device's.  Who ends by length is known before the token is, and
+is left out of the step ahead; a sequence whose token turns out to be a stop token
+has run one step for nothing.  The tokens and reasons that come out are the same.
+
 The loop is written against a small interface (`take_slot`, `give_back_slot`,
-`step`, `sample`, `max_batch`, `max_ctx`, `fits`), so its decisions can be
-tested without a GPU.
+`step`, `sample`, `max_batch`, `max_ctx`, `fits`; optionally `sample_async`), so
+its decisions can be tested without a GPU.
 """
 from __future__ import annotations
 
@@ -92,6 +100,10 @@ def generate(engine, prompts: list[list[int]], max_new_tokens: int = 256, params
         return [GenerationResult([], "length", len(p)) for p in prompts]
     t_begin = time.perf_counter()
     first_token_seen = False
+    # an engine that can sample without handing the tokens to the host first runs one step ahead;
+    # the repetition penalty needs every token on the host before the next one is drawn
+    ahead = (hasattr(engine, "sample_async") and getattr(engine, "run_ahead", True)
+             and params.repetition_penalty == 1.0)
     for batch in plan_batches([len(p) for p in prompts], max_new_tokens, engine.max_batch,
                               lambda lens: engine.fits([min(n, engine.max_ctx) for n in lens])):
         stats.n_batches += 1
@@ -102,16 +114,20 @@ def generate(engine, prompts: list[list[int]], max_new_tokens: int = 256, params
             stats.n_steps += 1
             stats.prefill_tokens += sum(len(s.prompt) for s in live)
             t_decode0 = None
-            while True:
-                tokens = engine.sample(logits, [s.sampler for s in live], params)
+
+            def take(tokens_of: list[_Live], tokens: list[int]) -> None:
+                """The sampled tokens of these sequences: who goes on, who ends, and why."""
+                nonlocal first_token_seen, t_decode0
                 if not first_token_seen:
                     first_token_seen = True
                     stats.ttft_s = time.perf_counter() - t_begin
                 if t_decode0 is None:
                     t_decode0 = time.perf_counter()
                 else:
-                    stats.decode_tokens += len(live)
-                for s, tok in zip(live, tokens):
+                    stats.decode_tokens += sum(1 for s in tokens_of if s.finish is None)
+                for s, tok in zip(tokens_of, tokens):
+                    if s.finish is not None:  # ended a step ago; this token was computed for nothing
+                        continue
                     if tok in stops:
                         if include_stop_token:
                             s.out.append(tok)
@@ -120,16 +136,44 @@ def generate(engine, prompts: list[list[int]], max_new_tokens: int = 256, params
                     s.out.append(tok)
                     if len(s.out) >= max_new_tokens or s.length >= engine.max_ctx:
                         s.finish = "length"
-                for s in live:
-                    if s.finish is not None:
+                for s in tokens_of:
+                    if s.finish is not None and s.slot >= 0:
                         results[s.number] = GenerationResult(s.out, s.finish, len(s.prompt))
                         engine.give_back_slot(s.slot)
                         s.slot = -1
-                live = [s for s in live if s.finish is None]
-                if not live:
-                    break
-                logits = engine.step([StepEntry(s.slot, [s.out[-1]], [0]) for s in live])
-                stats.n_steps += 1
+
+            if ahead:
+                # One step ahead: the next step is launched with its input tokens still on the device,
+                # before the host has read them; the host reads a step's tokens while the device runs
+                # the next one.  A sequence whose token turns out to be a stop token has then run one
+                # step for nothing (its row is ignored; its slot goes back as usual: what is launched
+                # later runs later).  Sequences that end by length are known beforehand and left out.
+                order = list(live)  # the sequences whose tokens `pending` holds, row by row
+                pending = engine.sample_async(logits, [s.sampler for s in order], params)
+                while True:
+                    go_on = [s for s in order if s.finish is None and len(s.out) + 1 < max_new_tokens
+                             and s.length + 1 < engine.max_ctx]
+                    pending_next = None
+                    if go_on:
+                        src = None if len(go_on) == len(order) else [order.index(s) for s in go_on]
+                        logits = engine.step([StepEntry(s.slot, [0], [0]) for s in go_on],
+                                             device_tokens=(pending.device_tokens, src))
+                        stats.n_steps += 1
+                        pending_next = engine.sample_async(logits, [s.sampler for s in go_on], params)
+                    take(order, pending.tokens())
+                    live = [s for s in live if s.finish is None]
+                    if not live or pending_next is None:
+                        break
+                    order, pending = go_on, pending_next
+            else:
+                while True:
+                    tokens = engine.sample(logits, [s.sampler for s in live], params)
+                    take(live, tokens)
+                    live = [s for s in live if s.finish is None]
+                    if not live:
+                        break
+                    logits = engine.step([StepEntry(s.slot, [s.out[-1]], [0]) for s in live])
+                    stats.n_steps += 1
             stats.decode_s += time.perf_counter() - t_decode0
         finally:
             for s in live:

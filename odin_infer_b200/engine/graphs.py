@@ -29,7 +29,7 @@ class DecodeGraphs:
         self._graphs: dict[tuple, tuple] = {}
         self.last_h2d_bytes = 0
 
-    def run(self, entries: list[StepEntry], starts: list[int]) -> torch.Tensor | None:
+    def run(self, entries: list[StepEntry], starts: list[int], device_tokens=None) -> torch.Tensor | None:
         """Logits [wanted, vocab] of a one-token-per-sequence step, or NotImplemented if
         the batch is larger than the largest bucket."""
         bucket = bucket_for(len(entries))
@@ -57,6 +57,8 @@ class DecodeGraphs:
             batch = hit[1]
             batch.fill(entries, starts)
         graph, batch, logits, n_kernels = self._graphs[bucket]
+        if device_tokens is not None:  # the tokens come from the device: into the tables after their copy
+            batch.take_tokens(*device_tokens)
         graph.replay()
         ops.add_launches(n_kernels)
         self.last_h2d_bytes = batch.h2d_bytes

@@ -190,6 +190,17 @@ class StepBatch:
         self._upload()
         return True
 
+    def take_tokens(self, tokens: torch.Tensor, src: list[int] | None) -> None:
+        """The step's token ids from the device instead of from the host (one token per sequence):
+        sequence b takes tokens[src[b]] (tokens[b] if src is None).  Runs on the stream after the
+        copy of the tables, so it is what the step's kernels see."""
+        n = self.n_seqs
+        if src is None:
+            self.tok_ids[:n].copy_(tokens[:n])
+        else:
+            idx = torch.tensor(src, dtype=torch.int64).to(tokens.device, non_blocking=True)
+            self.tok_ids[:n].copy_(tokens.index_select(0, idx))
+
     # ---- what a mixer asks for ------------------------------------------
     def kv(self, entry: int):
         """(keys, values, block table) of the cache line that schedule entry `entry` uses:

@@ -1,4 +1,6 @@
 """Sampling: greedy, temperature, top-p, repetition penalty."""
-from .sampler import SamplingParams, SequenceSampler, XorShift64Star, sample_batch, splitmix64, stream_for
+from .sampler import (PendingTokens, SamplingParams, SequenceSampler, XorShift64Star, sample_batch,
+                      sample_batch_async, splitmix64, stream_for)
 
-__all__ = ["SamplingParams", "SequenceSampler", "XorShift64Star", "sample_batch", "splitmix64", "stream_for"]
+__all__ = ["PendingTokens", "SamplingParams", "SequenceSampler", "XorShift64Star", "sample_batch", "sample_batch_async",
+           "splitmix64", "stream_for"]

@@ -114,3 +114,43 @@ def sample_batch(logits, samplers: list[SequenceSampler], params: SamplingParams
     for s, t in zip(samplers, tokens):
         s.record(t)
     return tokens
+
+
+class PendingTokens:
+    """Sampled tokens that are on the device (`device_tokens`, int32 [B]) and on their way to the
+    host; `tokens()` waits for the copy."""
+
+    def __init__(self, device_tokens):
+        import torch
+        self.device_tokens = device_tokens
+        self._host = torch.empty(device_tokens.shape, dtype=device_tokens.dtype, pin_memory=device_tokens.is_cuda)
+        self._host.copy_(device_tokens, non_blocking=True)
+        self._event = None
+        if device_tokens.is_cuda:
+            self._event = torch.cuda.Event()
+            self._event.record()
+
+    def tokens(self) -> list[int]:
+        if self._event is not None:
+            self._event.synchronize()
+        return self._host.tolist()
+
+
+def sample_batch_async(logits, samplers: list[SequenceSampler], params: SamplingParams) -> PendingTokens:
+    """`sample_batch` without waiting for the tokens: the same kernels and coins; the host sees the
+    tokens when it asks for them.  Not with a repetition penalty, which needs each token on the host
+    before the next one is drawn."""
+    import torch
+    from ..csrc import ops
+
+    if params.repetition_penalty != 1.0:
+        raise ValueError("sampling ahead of the host cannot apply a repetition penalty")
+    B = logits.shape[0]
+    assert B == len(samplers)
+    out = torch.empty(B, dtype=torch.int32, device=logits.device)
+    if params.temperature == 0.0:
+        ops.argmax(logits, out)
+    else:
+        coins = torch.tensor([s.coin() for s in samplers], dtype=torch.float32).to(logits.device, non_blocking=True)
+        ops.sample(logits, params.temperature, params.top_p, coins, out)
+    return PendingTokens(out)

@@ -142,3 +142,72 @@ def test_rng_is_the_reference_generator():
     assert a.state != 0 and a.state != b.state
     assert stream_for(0, 0).random_f32() == a.random_f32()
     assert SamplingParams(repetition_penalty=0.5).repetition_penalty == 1.0
+
+
+class _Pending:
+    def __init__(self, toks):
+        self.device_tokens = list(toks)
+
+    def tokens(self):
+        return list(self.device_tokens)
+
+
+class FakeAheadEngine(FakeEngine):
+    """The same engine with sampling that leaves the tokens "on the device": the loop then runs one
+    step ahead and a step may take its tokens from the last sampling instead of from the host."""
+
+    def step(self, entries, device_tokens=None):
+        if device_tokens is not None:
+            toks, src = device_tokens
+            assert all(e.tokens == [0] for e in entries), "placeholders only"
+            entries = [type(e)(e.slot, [toks[src[b] if src is not None else b]], e.want) for b, e in enumerate(entries)]
+        return super().step(entries)
+
+    def sample_async(self, logits, samplers, params):
+        return _Pending(self.sample(logits, samplers, params))
+
+
+def test_one_step_ahead_gives_the_same_tokens():
+    prompts = [[1, 2, 3], [10], [20, 21, 22, 23, 24], [11], [40]]
+    for kwargs in (dict(max_new_tokens=5), dict(max_new_tokens=8, include_stop_token=True),
+                   dict(max_new_tokens=1), dict(max_new_tokens=2), dict(max_new_tokens=6, stop_token_ids=[])):
+        a, b = FakeEngine(max_batch=3), FakeAheadEngine(max_batch=3)
+        ra, rb = generate(a, prompts, **kwargs), generate(b, prompts, **kwargs)
+        assert [(r.tokens, r.finish_reason) for r in ra] == [(r.tokens, r.finish_reason) for r in rb], kwargs
+        assert not b.held and sorted(b.free) == sorted(a.free)
+    # a sequence that ends by length is left out of the step ahead; one that meets a stop token has run
+    # one step for nothing (the stop token was fed), and nobody else's tokens changed
+    e = FakeAheadEngine()
+    res = generate(e, [[10], [30]], max_new_tokens=4)
+    assert res[0].tokens == [11, 12] and res[0].finish_reason == "stop"
+    assert res[1].tokens == [31, 32, 33, 34] and res[1].finish_reason == "length"
+    fed = [[t[0] for _, t, _ in s] for s in e.steps[1:]]
+    assert fed == [[11, 31], [12, 32], [13, 33]], fed   # 13 fed once; the step after [34] was never launched
+    # the context limit, and the penalty that keeps the loop on the host's pace
+    e = FakeAheadEngine(max_ctx=8)
+    res = generate(e, [[20, 21, 22, 23, 24]], max_new_tokens=100, stop_token_ids=[])
+    assert res[0].tokens == [25, 26, 27] and res[0].finish_reason == "length"
+    e = FakeAheadEngine()
+    res = generate(e, [[10]], max_new_tokens=4, params=SamplingParams(repetition_penalty=1.3))
+    assert all(13 not in t for s in e.steps for _, t, _ in s)
+
+
+def test_one_step_ahead_stats_and_failures():
+    e = FakeAheadEngine(max_batch=2)
+    stats = GenerationStats()
+    res = generate(e, [[i] for i in (1, 20, 30, 40, 2)], max_new_tokens=3, stats=stats)
+    assert [r.tokens for r in res] == [[2, 3, 4], [21, 22, 23], [31, 32, 33], [41, 42, 43], [3, 4, 5]]
+    assert stats.n_batches == 3 and stats.decode_tokens == 5 * 2 and not e.held
+    e = FakeAheadEngine()
+    calls = {"n": 0}
+    real = e.step
+
+    def failing(entries, device_tokens=None):
+        calls["n"] += 1
+        if calls["n"] == 3:
+            raise RuntimeError("boom")
+        return real(entries, device_tokens)
+    e.step = failing
+    with pytest.raises(RuntimeError, match="boom"):
+        generate(e, [[1], [2]], max_new_tokens=10, stop_token_ids=[])
+    assert not e.held

@@ -150,3 +150,33 @@ def test_reference_style_api(folders):
     row0 = engine_forward(e, toks[0], 0).cpu().numpy()   # position 0 starts afresh
     assert tiny.rel_err(row0, ref[0]) < tiny.TOL["float32"]
     engine_destroy(e)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_one_step_ahead_equals_the_hosts_pace(folders, dtype):
+    """Generation that launches each decode step before the host has read the tokens it continues
+    from (the default) against generation that reads every token first: the same tokens and reasons,
+    greedy and sampled, with sequences that stop at different steps, end by length, and batches one
+    after another; and the cache's bookkeeping is whole afterwards."""
+    vocab = tiny.TINY_B["vocab_size"]
+    prompts = [tiny.random_tokens(n, vocab, 900 + n) for n in (9, 30, 4, 66, 17, 2, 41)]
+    ahead = engine_for(folders["B"], dtype, max_batch=3)
+    paced = engine_for(folders["B"], dtype, max_batch=3, run_ahead=False)
+    free = paced.generate(prompts, max_new_tokens=14, temperature=0.0, stop_token_ids=[])
+    stops = sorted({free[0].tokens[3], free[1].tokens[7], free[4].tokens[0], free[6].tokens[13]})
+    for kw in (dict(temperature=0.0, stop_token_ids=[]), dict(temperature=0.0, stop_token_ids=stops),
+               dict(temperature=0.0, stop_token_ids=stops, include_stop_token=True),
+               dict(temperature=0.9, top_p=0.8, seed=3, stop_token_ids=stops)):
+        a = ahead.generate(prompts, max_new_tokens=14, **kw)
+        b = paced.generate(prompts, max_new_tokens=14, **kw)
+        if dtype == "float32" or kw["temperature"] == 0.0:
+            # bfloat16: a sequence that has stopped stays one more step in its batch, which can move
+            # the step into another batch bucket; sums then round differently, and a draw near the
+            # edge of two tokens' shares may fall on the other side
+            assert [(o.tokens, o.finish_reason) for o in a] == [(o.tokens, o.finish_reason) for o in b], kw
+        if kw["temperature"] == 0.0:
+            assert any(o.finish_reason == "stop" for o in b) == bool(kw["stop_token_ids"])
+    for e in (ahead, paced):
+        e.cache.check()
+        assert all(g.pool.n_held == 0 for g in e.cache.groups.values())
+        e.destroy()
