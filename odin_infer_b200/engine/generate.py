@@ -150,9 +150,16 @@ def generate(engine, prompts: list[list[int]], max_new_tokens: int = 256, params
                 # later runs later).  Sequences that end by length are known beforehand and left out.
                 order = list(live)  # the sequences whose tokens `pending` holds, row by row
                 pending = engine.sample_async(logits, [s.sampler for s in order], params)
+                # the batch's first tokens go out before anything else is launched (whatever the first
+                # decode step has to set up must not stand between a request and its first token)
+                take(order, pending.tokens())
+                taken = True
                 while True:
-                    go_on = [s for s in order if s.finish is None and len(s.out) + 1 < max_new_tokens
-                             and s.length + 1 < engine.max_ctx]
+                    if taken:
+                        go_on = [s for s in order if s.finish is None]
+                    else:
+                        go_on = [s for s in order if s.finish is None and len(s.out) + 1 < max_new_tokens
+                                 and s.length + 1 < engine.max_ctx]
                     pending_next = None
                     if go_on:
                         src = None if len(go_on) == len(order) else [order.index(s) for s in go_on]
@@ -160,7 +167,9 @@ def generate(engine, prompts: list[list[int]], max_new_tokens: int = 256, params
                                              device_tokens=(pending.device_tokens, src))
                         stats.n_steps += 1
                         pending_next = engine.sample_async(logits, [s.sampler for s in go_on], params)
-                    take(order, pending.tokens())
+                    if not taken:
+                        take(order, pending.tokens())
+                    taken = False
                     live = [s for s in live if s.finish is None]
                     if not live or pending_next is None:
                         break
