@@ -185,12 +185,25 @@ head_prep_token_kernel(const TI* qkv, int n_split, size_t split_stride, bf16* q_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int seq = tok_seq[t];
     const int pos = tok_pos[t];
-    const int page = (seq >= 0 && write_kv) ? block_table[(size_t)seq * bt_stride + pos / page_size] : -1;
+    pdl_wait();
+    if (seq < 0) return;
+    // The first heads' loads go out before the loads that hang on the token's position (its page, its
+    // angles): a CTA lives for a chain of three trips to memory otherwise, with data in flight during one.
+    const int n_heads = Hq + 2 * Hkv;
+    const TI* row = qkv + (size_t)t * row_stride + lane * VEC;
+    float v[UNROLL][VEC];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+        const int head = warp + u * HP_WARPS;
+        if (head < n_heads && (head < Hq || write_kv))
+            headmath::load_parts<VEC, TI>(row + (size_t)head * HD, n_split, split_stride, v[u]);
+    }
+    const int page = write_kv ? block_table[(size_t)seq * bt_stride + pos / page_size] : -1;
     const bool in_table = (pos >= 0 && pos < table_len);
     float c[VEC], sn[VEC], wq[VEC], wk[VEC];
 #pragma unroll
     for (int e = 0; e < VEC; ++e) { c[e] = 1.f; sn[e] = 0.f; wq[e] = 1.f; wk[e] = 1.f; }
-    if (seq >= 0 && in_table) {
+    if (in_table) {
         load_vec<VEC>(cos_t + (size_t)pos * HALF + (lane & 15) * VEC, c);
         load_vec<VEC>(sin_t + (size_t)pos * HALF + (lane & 15) * VEC, sn);
     }
@@ -198,17 +211,14 @@ head_prep_token_kernel(const TI* qkv, int n_split, size_t split_stride, bf16* q_
 #pragma unroll
         for (int e = 0; e < VEC; ++e) { wq[e] = qw.at(lane * VEC + e); wk[e] = kw.at(lane * VEC + e); }
     }
-    pdl_wait();
-    if (seq < 0) return;
-    const int n_heads = Hq + 2 * Hkv;
-    const TI* row = qkv + (size_t)t * row_stride + lane * VEC;
     for (int h0 = warp; h0 < n_heads; h0 += HP_WARPS * UNROLL) {
-        float v[UNROLL][VEC];
+        if (h0 != warp) {
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int head = h0 + u * HP_WARPS;
-            if (head < n_heads && (head < Hq || page >= 0))
-                headmath::load_parts<VEC, TI>(row + (size_t)head * HD, n_split, split_stride, v[u]);
+            for (int u = 0; u < UNROLL; ++u) {
+                const int head = h0 + u * HP_WARPS;
+                if (head < n_heads && (head < Hq || page >= 0))
+                    headmath::load_parts<VEC, TI>(row + (size_t)head * HD, n_split, split_stride, v[u]);
+            }
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
