@@ -67,6 +67,27 @@ def test_add_rmsnorm(d, w_dtype, out_dtype):
     close(out3, ref3, 2e-6 if out_dtype == torch.float32 else 5e-3)
 
 
+@pytest.mark.parametrize("delta_dtype", [None, torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("d", [72, 1000, 2048, 4096, 5120, 8200])
+def test_add_rmsnorm_many_rows(d, delta_dtype):
+    """More than 256 rows, bfloat16 out: the prompt's variant (the row in registers; widths up to 8192,
+    beyond that the kernel of few rows), each row with a scale of its own so that a row read from the
+    wrong place shows."""
+    from odin_infer_b200.csrc import ops
+    n, eps = 301, 1e-6
+    torch.manual_seed(d)
+    x = torch.randn(n, d, device=DEV) * torch.linspace(0.1, 30.0, n, device=DEV)[:, None]
+    x0 = x.clone()
+    w = (1 + 0.1 * torch.randn(d, device=DEV)).bfloat16()
+    delta = None if delta_dtype is None else (torch.randn(2, n, d, device=DEV) * 3).to(delta_dtype)
+    out = torch.full((n, d), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops.add_rmsnorm(x, delta, w, eps, out)
+    xr = x0.double() if delta is None else x0.double() + delta.double().sum(0)
+    ref = w.double() * (xr / torch.sqrt((xr * xr).mean(-1, keepdim=True) + eps))
+    close(x, xr, 1e-6)
+    assert (out.double() - ref).abs().max().item() <= 2 ** -7 * ref.abs().max().item()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_swiglu(dtype):
     from odin_infer_b200.csrc import ops
