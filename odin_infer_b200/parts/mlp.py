@@ -3,7 +3,6 @@ from __future__ import annotations
 
 import torch
 
-from ..csrc import ops
 from .base import FeedForward, ParamSpec, register_part
 
 

@@ -5,7 +5,6 @@ and decoding, CUDA graphs) against the true 32-bit engine on the same weights.  
 path itself is checked against the plain implementation on the tiny configurations."""
 import numpy as np
 import pytest
-import torch
 
 from tests import tiny
 

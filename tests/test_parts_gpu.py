@@ -4,10 +4,7 @@ token to one of its experts, a second position encoding that acts on the embedde
 a layer that runs twice, a layer that reads another layer's cache, a windowed layer with
 storage of its own), registered, built and stepped without touching the package's files."""
 import dataclasses
-import math
-import os
 
-import numpy as np
 import pytest
 import torch
 
@@ -153,7 +150,6 @@ def test_embedding_head_and_block_parts():
 # A toy architecture, defined in this test only
 # ------------------------------------------------------------------------------------
 def register_toy():
-    from odin_infer_b200.cache import KVRequest  # noqa: F401
     from odin_infer_b200.config import ModelConfig, register_architecture
     from odin_infer_b200.config.base import KeyReader
     from odin_infer_b200.parts import Mixer, ModelSpec, ParamSpec, PartSpec, ScheduleEntry, register_part

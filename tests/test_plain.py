@@ -1,7 +1,6 @@
 """Known-answer tests of the plain implementation (the oracle has to be right first)."""
 import math
 
-import numpy as np
 import torch
 
 from tests.plain import qwen3_plain as P

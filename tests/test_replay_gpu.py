@@ -10,7 +10,6 @@ import sys
 
 import numpy as np
 import pytest
-import torch
 
 from tests import tiny, traces
 

@@ -7,7 +7,7 @@ import torch
 
 from odin_infer_b200.config import config_from_dict
 from odin_infer_b200.weights import (ModelFiles, SafetensorsError, WeightError, load_weights, model_param_specs,
-                                     write_random_model, write_safetensors)
+                                     write_safetensors)
 from tests import tiny
 
 

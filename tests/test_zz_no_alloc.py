@@ -11,7 +11,6 @@ kernel tests use; it also checks that a request beyond the array's size is refus
 This file sorts after the other tests on purpose: a run that stops at the first
 failure has then already run everything else.
 """
-import ctypes
 from ctypes import c_int, c_longlong, c_void_p
 
 import pytest
