@@ -20,7 +20,7 @@
 //
 // Measured (8B layer sizes, 8 sequences): the products stream their weights faster this way (65
 // against 77 us per layer, boundaries included), but the operations between them no longer overlap
-// the products' ends as co-resident kernels do, a barrier costs 2 to 3 us, and a layer takes 150 us
+// the products' ends as co-resident kernels do, a barrier costs 2 to 3 us, and a layer takes 120 us
 // against 95.  The runtime therefore uses it only on request.
 //
 // Roles (256 threads): warp 0 requests weight tiles (TMA), warp 1 requests activation tiles

@@ -46,7 +46,7 @@ def fuse_sinks() -> bool:
 # instead of a kernel per operation: a layer is then one launch with barriers across the grid
 # between its operations.  Its products stream their weights faster (the requests never stop at
 # an operation's end), but the operations between them no longer overlap the products' ends as
-# co-resident kernels do, and a layer takes 150 us against 95 on the 8B shape.  Off unless
+# co-resident kernels do, and a layer takes 120 us against 95 on the 8B shape.  Off unless
 # ODIN_DECODE_PROGRAM=1; the tests run it both ways.
 DECODE_PROGRAM = os.environ.get("ODIN_DECODE_PROGRAM", "0") == "1"
 
@@ -63,14 +63,16 @@ def context_class_of(longest: int, page: int = 64) -> int:
     return (max(1, (longest + page - 1) // page) + 7) // 8
 
 
-def decode_key_splits(n_seqs: int, n_kv_heads: int, longest: int, page: int = 64, n_sms: int = 148) -> int:
+def decode_key_splits(n_seqs: int, n_kv_heads: int, longest: int, page: int = 64, n_sms: int = 148,
+                      ctas_per_sm: int = 2) -> int:
     """Into how many parts decode attention cuts a sequence's keys.  A CTA's four warps take a
     page each, so up to about four pages per CTA run side by side and more only lengthen the
     chain; the split that finishes last adds the partials up inside the same kernel.  So: two
-    splits per 8 pages of context, as long as all CTAs together fit the GPU twice.  Depends on
+    splits per 8 pages of context, as long as all CTAs together fit the GPU twice (once inside a
+    program's persistent kernel, whose CTAs take the pieces in turns).  Depends on
     the batch bucket and on the context class, never on which sequences are in the batch."""
     want = 2 * context_class_of(longest, page)
-    room = max(1, (2 * n_sms) // max(1, n_seqs * n_kv_heads))
+    room = max(1, (ctas_per_sm * n_sms) // max(1, n_seqs * n_kv_heads))
     return max(1, min(want, room, 16))  # a split that finds no page of its own writes an empty partial
 
 
@@ -205,7 +207,8 @@ class Runtime:
                 and rotary_dim == head_dim and n_kv > 0 and n_q // n_kv <= 16 and write_kv):
             return False
         B = out.shape[0]
-        n_split = decode_key_splits(B, n_kv, step.max_len_after, n_sms=self.n_sms)
+        n_split = decode_key_splits(B, n_kv, step.max_len_after, n_sms=self.n_sms,
+                                    ctas_per_sm=1 if ops.recording() else 2)
         scratch = self.empty(ops.attention_decode_scratch(B, n_q, head_dim, n_split), dtype=torch.float32)
         return ops.attention_decode_fused(qkv, out, n_q, n_kv, head_dim, q_norm, k_norm, eps, cos, sin, rotary_dim,
                                           k_line, v_line, step.tok_pos, step.tok_seq, block_table, window, scratch,
