@@ -6,8 +6,8 @@
 //
 // Roles (192 threads): warp 0 issues TMA loads, warp 1 allocates tensor memory and
 // issues the MMAs (one lane), warps 2..5 read the accumulator back and store.
-// This is the kernel of decode steps (mode 1) and of short prompts; from 256 tokens on
-// the products run on pairs of SMs (gemm_tc2.cu).
+// This is the kernel of steps of up to 128 tokens (mode 1); products of more tokens run on
+// pairs of SMs (gemm_tc2.cu).
 //
 // The product is computed as D = X * Y^T with X on the 128-row side of the MMA and
 // Y on its N side.  Two modes map the matrices to X and Y:

@@ -17,6 +17,10 @@
 //   acc_full[a]  in each CTA: accumulator a is complete (commit to both);
 //   acc_empty[a] in the leader: both CTAs' epilogues have read accumulator a back.
 // DUAL: gate and up products side by side and the SwiGLU in the epilogue, as in gemm_tc.cu.
+// WIDE (129 to 256 tokens): the operands change places: the pair's 256 rows are weight rows, the N
+// side holds the tokens (each CTA loads half of them), K is cut into parts, and the epilogue
+// writes C[token][weight row]: a product of so few tokens is bound by the weights it streams, and
+// tiles of 256 token rows would be too few to occupy the GPU.
 //
 // Every wait is bounded (tc::mbar_wait); a CTA that gives up sets the error flag, and both
 // CTAs of a pair always reach the final cluster barrier, since no wait of either is endless.
@@ -49,6 +53,11 @@ struct Params2 {
     int dual_offset;      // DUAL: first weight row of the up half
     int accumulate;       // float32 out: C += the product (the residual stream takes its update in place)
     int* error;
+    // WIDE (a few hundred tokens): the weights are the operand on the 256-row side (M: weight rows, tiles_m of
+    // them, tiles_n = 1) and the tokens the one on the N side (N: tokens, at most 256); K is cut into n_split
+    // parts, part s written to the slice s of the output, split_stride elements apart, as C[token][weight row].
+    int n_split, kb_per_split;
+    long long split_stride;
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -156,7 +165,7 @@ __device__ __forceinline__ void tile_of(long long w, int tiles_m, int tiles_n, i
     tn = in_band / rows;
 }
 
-template <typename TO, bool DUAL>
+template <typename TO, bool DUAL, bool WIDE = false>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const Params2 p) {
     constexpr int ACC_N = DUAL ? BN / 2 : BN;  // columns of one product of the pair (DUAL: gate and up, 128 each)
@@ -198,7 +207,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t tmem_base = *tmem_slot;
 
     const int n_clusters = (int)(gridDim.x >> 1), cluster_id = (int)(blockIdx.x >> 1);
-    const long long n_tiles = (long long)p.tiles_m * p.tiles_n;
+    static_assert(!(DUAL && WIDE), "the SwiGLU epilogue is for many tokens");
+    const long long n_tiles = WIDE ? (long long)p.tiles_m * p.n_split : (long long)p.tiles_m * p.tiles_n;
 
     if (warp == 0) {
         // ------------------------------------------------------- TMA producer (both CTAs)
@@ -207,10 +217,15 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (long long w = cluster_id; w < n_tiles && ok; w += n_clusters) {
-                int tm, tn;
-                tile_of(w, p.tiles_m, p.tiles_n, tm, tn);
+                int tm, tn, kb0 = 0, kb1 = p.kb_total;
+                if (WIDE) {
+                    tm = (int)(w / p.n_split); tn = 0;
+                    kb0 = (int)(w % p.n_split) * p.kb_per_split; kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                } else {
+                    tile_of(w, p.tiles_m, p.tiles_n, tm, tn);
+                }
                 const int row_a = tm * 2 * BM + (int)rank * BM;
-                for (int kb = 0; kb < p.kb_total; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!tc::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { report2(p.error, 1, (int)w, kb, stage); ok = false; break; }
                     uint8_t* sa = smem + stage * STAGE;
                     uint8_t* sb = sa + STAGE_A;
@@ -250,7 +265,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 if (!tc::mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { report2(p.error, 2, (int)w, -1, (int)acc); ok = false; break; }
                 tc::fence_after_sync();
                 const uint32_t tmem_d = tmem_base + acc * BN;
-                for (int kb = 0; kb < p.kb_total; ++kb) {
+                int kb0 = 0, kb1 = p.kb_total;
+                if (WIDE) { kb0 = (int)(w % p.n_split) * p.kb_per_split; kb1 = min(p.kb_total, kb0 + p.kb_per_split); }
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!tc::mbar_wait(&full[stage], phase, abort_flag)) { report2(p.error, 3, (int)w, kb, stage); ok = false; break; }
                     tc::fence_after_sync();
                     const uint32_t ax = tc::smem_u32(smem + stage * STAGE);
@@ -258,7 +275,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     const uint64_t db = tc::make_smem_desc_sw128(ax + STAGE_A);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma_bf16_pair(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        umma_bf16_pair(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     umma_commit_pair(&empty[stage]);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -274,12 +291,28 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const uint32_t acc_empty_leader0 = map_to_rank(&acc_empty[0], 0);
         for (long long w = cluster_id; w < n_tiles && ok; w += n_clusters, ++local) {
             int tm, tn;
-            tile_of(w, p.tiles_m, p.tiles_n, tm, tn);
+            if (WIDE) { tm = (int)(w / p.n_split); tn = 0; }
+            else tile_of(w, p.tiles_m, p.tiles_n, tm, tn);
             const uint32_t acc = local % ACC_BUFS, acc_phase = (local / ACC_BUFS) & 1;
             if (!tc::mbar_wait(&acc_full[acc], acc_phase, abort_flag)) { if (lane == 0 && quarter == 2) report2(p.error, 4, (int)w, -1, (int)acc); ok = false; break; }
             tc::fence_after_sync();
-            const int i = tm * 2 * BM + (int)rank * BM + quarter * 32 + lane;  // token row
+            const int i = tm * 2 * BM + (int)rank * BM + quarter * 32 + lane;  // token row (WIDE: weight row)
             TO* out = reinterpret_cast<TO*>(p.out);
+            if (WIDE) {
+                // C[token c][weight row i]: the warp writes 32 consecutive elements of a token's row
+                TO* dst = out + (size_t)(w % p.n_split) * p.split_stride + i;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN && c0 < p.N; c0 += 32) {
+                    uint32_t r[32];
+                    tc::tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + c0, r);
+                    tc::tmem_ld_wait();
+                    if (i < p.M) {
+#pragma unroll
+                        for (int c = 0; c < 32; ++c)
+                            if (c0 + c < p.N) dst[(size_t)(c0 + c) * p.ldc] = from_f32<TO>(__uint_as_float(r[c]));
+                    }
+                }
+            } else
 #pragma unroll 1
             for (int c0 = 0; c0 < ACC_N; c0 += 32) {
                 uint32_t r[32];
@@ -384,9 +417,9 @@ int* error_flag2() {
     return flag;
 }
 
-template <typename TO, bool DUAL>
+template <typename TO, bool DUAL, bool WIDE = false>
 int launch2(const CUtensorMap& ma, const CUtensorMap& mw, const Params2& p, cudaStream_t s) {
-    auto kern = gemm_tc2_kernel<TO, DUAL>;
+    auto kern = gemm_tc2_kernel<TO, DUAL, WIDE>;
     static int max_clusters = -1;
     if (max_clusters < 0) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -406,7 +439,7 @@ int launch2(const CUtensorMap& ma, const CUtensorMap& mw, const Params2& p, cuda
         if (e != cudaSuccess || n <= 0) { cudaGetLastError(); return ODIN_ERR_UNSUPPORTED; }
         max_clusters = n;
     }
-    const long long tiles = (long long)p.tiles_m * p.tiles_n;
+    const long long tiles = WIDE ? (long long)p.tiles_m * p.n_split : (long long)p.tiles_m * p.tiles_n;
     const int clusters = (int)(tiles < max_clusters ? tiles : max_clusters);
     cudaLaunchConfig_t cfg;
     std::memset(&cfg, 0, sizeof(cfg));
@@ -443,6 +476,7 @@ extern "C" int odin_gemm_tc2(const void* A, const void* W, void* C, int c_dtype,
     p.tiles_n = (N + BN - 1) / BN;
     p.kb_total = (K + BK - 1) / BK;
     p.dual_offset = 0;
+    p.n_split = 1; p.kb_per_split = p.kb_total; p.split_stride = 0;
     if (accumulate && c_dtype != ODIN_F32) return ODIN_ERR_BAD_ARG;
     p.accumulate = accumulate ? 1 : 0;
     p.error = error_flag2();
@@ -471,6 +505,7 @@ extern "C" int odin_gemm_tc2_swiglu(const void* A, const void* W, void* C, int c
     p.tiles_n = (I + BN / 2 - 1) / (BN / 2);
     p.kb_total = (K + BK - 1) / BK;
     p.dual_offset = I;
+    p.n_split = 1; p.kb_per_split = p.kb_total; p.split_stride = 0;
     p.accumulate = 0;
     p.error = error_flag2();
     CUtensorMap ma, mw;
@@ -480,6 +515,40 @@ extern "C" int odin_gemm_tc2_swiglu(const void* A, const void* W, void* C, int c
     cudaStream_t s = (cudaStream_t)stream;
     if (c_dtype == ODIN_BF16) return launch2<bf16, true>(ma, mw, p, s);
     if (c_dtype == ODIN_F32) return launch2<float, true>(ma, mw, p, s);
+    return ODIN_ERR_UNSUPPORTED;
+}
+
+// A few hundred tokens (M <= 256): C[n_split][M, N] = A[M, K] W[N, K]^T with the weights on the 256-row side
+// of the pair's MMA and the tokens on its N side, each CTA of a pair loading half of the tokens and its 128
+// weight rows (32 KB per K block instead of the 48 KB of one CTA with 256 tokens beside it, which bound that
+// kernel by its traffic from L2).  K is cut into n_split parts; part s goes to the slice s of C, split_stride
+// elements apart (float32 when there is more than one part).
+extern "C" int odin_gemm_tc2_wide(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, long long lda,
+                                  long long ldw, long long ldc, int n_split, long long split_stride, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || n_split < 1) return ODIN_ERR_BAD_ARG;
+    if (M > BN) return ODIN_ERR_UNSUPPORTED;
+    if ((lda % 8) || (ldw % 8) || (K % 8) || (((uintptr_t)A) & 15) || (((uintptr_t)W) & 15)) return ODIN_ERR_UNSUPPORTED;
+    if (n_split > 1 && c_dtype != ODIN_F32) return ODIN_ERR_BAD_ARG;
+    Params2 p;
+    p.out = C; p.ldc = ldc; p.M = N; p.N = M; p.K = K;   // the kernel's M side holds the weight rows
+    p.tiles_m = (N + 2 * BM - 1) / (2 * BM);
+    p.tiles_n = 1;
+    p.kb_total = (K + BK - 1) / BK;
+    if (n_split > p.kb_total) n_split = p.kb_total;
+    p.kb_per_split = (p.kb_total + n_split - 1) / n_split;
+    if ((p.kb_total + p.kb_per_split - 1) / p.kb_per_split != n_split) return ODIN_ERR_BAD_ARG;  // an empty part
+    p.n_split = n_split; p.split_stride = split_stride;
+    p.dual_offset = 0;
+    p.accumulate = 0;
+    p.error = error_flag2();
+    CUtensorMap ma, mw;
+    int rc;
+    if ((rc = make_map2(&ma, W, N, K, ldw, BM))) return rc;
+    if ((rc = make_map2(&mw, A, M, K, lda, BN / 2))) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (c_dtype == ODIN_BF16) return launch2<bf16, false, true>(ma, mw, p, s);
+    if (c_dtype == ODIN_F32) return launch2<float, false, true>(ma, mw, p, s);
     return ODIN_ERR_UNSUPPORTED;
 }
 

@@ -355,6 +355,27 @@ def gemm_tc2(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bo
         _stream()), "gemm_tc2")
 
 
+def gemm_tc2_wide(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_split: int = 1) -> None:
+    """out = a[M, K] @ w[N, K]^T for a few hundred tokens (M <= 256) on pairs of SMs, the weights on the wide
+    side of the MMA: out is [M, N], or float32 [n_split, M, N] partial sums of the K parts (as `gemm_tc`)."""
+    M, K = a.shape
+    N = w.shape[0]
+    if not gemm_tc_supported(a, w) or M > 256:
+        raise KernelError("gemm_tc2_wide: bfloat16 operands with 16-byte aligned rows and at most 256 tokens")
+    assert w.shape[1] == K and out.stride(-1) == 1
+    if out.dim() == 3:
+        assert out.dtype == torch.float32 and tuple(out.shape[1:]) == (M, N)
+        assert out.shape[0] == gemm_tc_splits(K, n_split), "allocate gemm_tc_splits(K, n_split) slices"
+        ldc, stride = out.stride(1), out.stride(0)
+    else:
+        assert tuple(out.shape) == (M, N) and n_split == 1
+        ldc, stride = out.stride(0), 0
+    _check(_fn("gemm_tc", "odin_gemm_tc2_wide")(
+        _ptr(a), _ptr(w), _ptr(out), c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K),
+        c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(ldc), c_int(n_split), c_longlong(stride),
+        _stream()), "gemm_tc2_wide")
+
+
 def gemm_tc2_swiglu_supported(inner: int) -> bool:
     return inner % 64 == 0
 

@@ -50,8 +50,14 @@ def fuse_sinks() -> bool:
 # ODIN_DECODE_PROGRAM=1; the tests run it both ways.
 DECODE_PROGRAM = os.environ.get("ODIN_DECODE_PROGRAM", "0") == "1"
 
-# from this many tokens on a product runs on pairs of SMs (tiles of 256 token rows)
-PAIR_MIN_TOKENS = 256
+# Up to this many tokens a product keeps the weights on the wide side of the MMA and the tokens on
+# its N side (one tile of tokens, K split to fill the SMs): with a few hundred tokens a product is still
+# bound by the weights it streams, and tiles of 256 token rows would be too few to occupy the GPU (the o
+# product of the 8B shape has 16 of them for 74 pairs of SMs).
+WEIGHTS_WIDE_MAX_TOKENS = 256
+
+# above that a product runs on pairs of SMs (tiles of 256 token rows)
+PAIR_MIN_TOKENS = 257
 
 # ring length of a product that shares the SM with a decode attention CTA (see Runtime.linear)
 LIGHT_STAGES = int(os.environ.get("ODIN_GEMM_LIGHT_STAGES", "6"))
@@ -139,13 +145,13 @@ class Runtime:
         M, N, K = rows.shape[0], w.shape[0], rows.shape[1]
         out_dtype = out_dtype or self.dtype
         if M > 0 and ops.gemm_tc_supported(rows, w):
-            if M <= 128:
-                bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
+            if M <= WEIGHTS_WIDE_MAX_TOKENS and not (isinstance(a, NormedRows) and M > 128):
+                bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
                 n_split = choose_k_split((N + 127) // 128, (K + 63) // 64, M, self.n_sms) if may_split else 1
                 n_split = ops.gemm_tc_splits(K, n_split)
                 stages = LIGHT_STAGES if beside_attention else 0
                 scale = dict(row_ssq=a.ssq, row_width=a.width, row_eps=a.eps) if isinstance(a, NormedRows) else {}
-                if (sink is not None and fuse_sinks() and out_dtype == torch.float32 and may_split
+                if (sink is not None and fuse_sinks() and M <= 128 and out_dtype == torch.float32 and may_split
                         and getattr(sink.norm, "weight", None) is not None and sink.norm.weight.numel() == N
                         and tuple(sink.x.shape) == (M, N) and sink.x.dtype == torch.float32):
                     scratch = self.empty(n_split, M, N, dtype=torch.float32) if n_split > 1 else self.empty(M, N, dtype=torch.float32)
@@ -154,6 +160,14 @@ class Runtime:
                     ops.gemm_tc(rows, w, scratch, 1, bn, n_split, stages,
                                 sink=(sink.x, sink.norm.weight, normed, ssq), **scale)
                     return NormedRows(normed, ssq, N, sink.norm.eps, sink.norm)
+                if M > 128:
+                    # a few hundred tokens: on pairs of SMs, which halves what a CTA fetches per K block
+                    n_tiles = (N + 255) // 256
+                    n_split = ops.gemm_tc_splits(K, choose_k_split(n_tiles, (K + 63) // 64, M, self.n_sms // 2)
+                                                 if may_split else 1)
+                    out = self.empty(n_split, M, N, dtype=torch.float32) if n_split > 1 else self.empty(M, N, dtype=out_dtype)
+                    ops.gemm_tc2_wide(rows, w, out, n_split)
+                    return out
                 if n_split > 1 or (may_split and ops.recording()):  # a program's products write 32-bit sums only
                     out = self.empty(n_split, M, N, dtype=torch.float32)
                     ops.gemm_tc(rows, w, out, 1, bn, n_split, stages, **scale)
@@ -184,9 +198,9 @@ class Runtime:
         (which also adds the partial sums of a split product)."""
         M = a.shape[0]
         act = self.empty(M, inner)
-        if M > 128:
+        if M > WEIGHTS_WIDE_MAX_TOKENS:
             a = self.materialize(a)
-        if M > 128 and ops.gemm_tc_supported(a, w_gate_up):
+        if M > WEIGHTS_WIDE_MAX_TOKENS and ops.gemm_tc_supported(a, w_gate_up):
             if M >= PAIR_MIN_TOKENS and ops.gemm_tc2_swiglu_supported(inner):
                 ops.gemm_tc2_swiglu(a, w_gate_up, act)
             else:

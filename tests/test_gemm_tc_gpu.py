@@ -39,6 +39,7 @@ CASES = [
     (129, 1000, 72, 0, 256), (130, 40, 1032, 0, 64), (1000, 384, 4096, 0, 128),
     (1, 128, 64, 1, 16), (1, 384, 96, 1, 16), (8, 6144, 4096, 1, 16), (16, 300, 72, 1, 16), (17, 256, 128, 1, 32),
     (64, 1000, 1032, 1, 64), (100, 512, 256, 1, 128), (33, 12288, 512, 1, 64),
+    (256, 512, 256, 1, 256), (129, 1000, 1032, 1, 256), (200, 300, 72, 1, 256),   # a few hundred tokens, weights wide
 ]
 
 
@@ -66,7 +67,7 @@ def test_ladder(case, out_dtype):
 
 
 @pytest.mark.parametrize("case", [(8, 4096, 12288, 1, 16, 6), (64, 512, 1032, 1, 64, 4), (3, 256, 640, 1, 16, 4),
-                                  (200, 300, 4096, 0, 128, 3), (5, 128, 96, 1, 16, 7)])
+                                  (200, 300, 4096, 0, 128, 3), (5, 128, 96, 1, 16, 7), (250, 1000, 4096, 1, 256, 5)])
 def test_split_k(case):
     M, N, K, mode, bn, n_split = case
     a = torch.randn(M, K, device=DEV).bfloat16()
@@ -181,6 +182,41 @@ def test_pair_kernel_ladder(case, out_dtype):
     one = torch.empty(M, N, device=DEV, dtype=out_dtype)
     ops.gemm_tc(a, w, one, 0, 256)
     close(got, one, 1e-6 if out_dtype == torch.float32 else 8e-3, "against the one-CTA kernel")
+
+
+@pytest.mark.parametrize("case", [(256, 512, 256, 1), (129, 1000, 1032, 3), (200, 300, 72, 1), (250, 4096, 4096, 5),
+                                  (192, 6144, 4096, 3), (1, 256, 64, 1), (130, 40, 640, 10)])
+def test_pair_kernel_weights_wide(case):
+    """The two-CTA kernel for a few hundred tokens (weights on the 256-row side, tokens on the N side, K in
+    parts): structured inputs, then random ones; ragged edges in tokens, weight rows and K; a row's result does
+    not depend on the other rows."""
+    from odin_infer_b200.csrc import ops
+    M, N, K, n_split = case
+    parts = ops.gemm_tc_splits(K, n_split)
+
+    def run_wide(a, w, dtype=torch.float32):
+        m = a.shape[0]
+        out = torch.full((parts, m, N) if parts > 1 else (m, N), float("nan"), device=DEV, dtype=dtype)
+        ops.gemm_tc2_wide(a, w, out, n_split)
+        ops.gemm_tc_check()
+        assert not torch.isnan(out.float()).any()
+        return out.sum(0) if parts > 1 else out
+
+    ones_a = torch.ones(M, K, device=DEV, dtype=torch.bfloat16)
+    ones_w = torch.ones(N, K, device=DEV, dtype=torch.bfloat16)
+    close(run_wide(ones_a, ones_w), torch.full((M, N), float(K)), 1e-6, "ones")
+    ka = ((torch.arange(M, device=DEV)[:, None] * 3 + torch.arange(K, device=DEV)[None, :] * 5) % 11 - 5).bfloat16()
+    kw = ((torch.arange(N, device=DEV)[:, None] * 7 + torch.arange(K, device=DEV)[None, :] * 2) % 13 - 6).bfloat16()
+    close(run_wide(ka, kw), ka.double() @ kw.double().t(), 1e-6, "k-distinct")
+    torch.manual_seed(M + N + K)
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    w = torch.randn(N, K, device=DEV).bfloat16()
+    got = run_wide(a, w)
+    close(got, a.double() @ w.double().t(), 2e-7 * math.sqrt(K), "random")
+    if parts == 1:
+        close(run_wide(a, w, torch.bfloat16), a.double() @ w.double().t(), 5e-3, "random, bfloat16 out")
+    r = M // 2
+    assert torch.equal(run_wide(a[r:r + 1], w)[0], got[r])
 
 
 @pytest.mark.parametrize("case", [(256, 128, 64), (300, 192, 1032), (2048, 1536, 512), (130, 64, 128)])
