@@ -172,7 +172,7 @@ class Engine:
         logits = NotImplemented
         if device_tokens is not None and any(len(e.tokens) != 1 for e in entries):
             raise StepError("tokens from the device: one token per sequence")
-        if self.graphs is not None and all(len(e.tokens) == 1 for e in entries):
+        if self.graphs is not None and self.graphs.takes(entries):
             logits = self.graphs.run(entries, starts, device_tokens)
             self.last_step_h2d_bytes = self.graphs.last_h2d_bytes
         if logits is NotImplemented:

@@ -15,6 +15,11 @@ from .step import StepBatch, StepEntry
 
 BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 
+# A short prompt of one sequence is launch-bound too when it runs eagerly (a few hundred launches of
+# ~25 us of host time each: 8 ms for what the device does in 3): such steps are captured per bucket
+# of their token count as well, padded with rows of sequence -1.
+PROMPT_BUCKETS = (32, 64, 128, 192, 256, 384, 512, 768, 1024)
+
 
 def bucket_for(n: int) -> int | None:
     for b in BUCKETS:
@@ -29,9 +34,40 @@ class DecodeGraphs:
         self._graphs: dict[tuple, tuple] = {}
         self.last_h2d_bytes = 0
 
+    def takes(self, entries: list[StepEntry]) -> bool:
+        """Is this a step that `run` may replay a graph for?"""
+        if all(len(e.tokens) == 1 for e in entries):
+            return True
+        return len(entries) == 1 and 1 < len(entries[0].tokens) <= PROMPT_BUCKETS[-1] and len(entries[0].want) > 0
+
+    def _run_prompt(self, entries: list[StepEntry], starts: list[int]) -> torch.Tensor | None:
+        """One sequence's tokens (a prompt or a piece of one) in a bucket of rows."""
+        n = len(entries[0].tokens)
+        rows = next(b for b in PROMPT_BUCKETS if n <= b)
+        key = ("prompt", rows, len(entries[0].want))
+        hit = self._graphs.get(key)
+        if hit is None:
+            batch = StepBatch(self.cache, entries, starts, self.rt.device, pad_rows_to=rows, pad_seqs_to=1)
+            self.rt.run(self.model, batch)          # once eagerly, as for decode steps
+            torch.cuda.current_stream().synchronize()
+            graph = torch.cuda.CUDAGraph()
+            n0 = ops.launch_count()
+            with torch.cuda.graph(graph):
+                logits = self.rt.run(self.model, batch)
+            self._graphs[key] = (graph, batch, logits, ops.launch_count() - n0)
+        else:
+            hit[1].fill(entries, starts)
+        graph, batch, logits, n_kernels = self._graphs[key]
+        graph.replay()
+        ops.add_launches(n_kernels)
+        self.last_h2d_bytes = batch.h2d_bytes
+        return logits
+
     def run(self, entries: list[StepEntry], starts: list[int], device_tokens=None) -> torch.Tensor | None:
-        """Logits [wanted, vocab] of a one-token-per-sequence step, or NotImplemented if
-        the batch is larger than the largest bucket."""
+        """Logits [wanted, vocab] of a one-token-per-sequence step (or of one sequence's short
+        prompt), or NotImplemented if the batch is larger than the largest bucket."""
+        if len(entries) == 1 and len(entries[0].tokens) > 1:
+            return self._run_prompt(entries, starts)
         bucket = bucket_for(len(entries))
         if bucket is None:
             return NotImplemented

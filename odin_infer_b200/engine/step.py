@@ -149,6 +149,9 @@ class StepBatch:
         self.all_single = all(len(e.tokens) == 1 for e in entries)
         self.all_start = all(p0 == 0 for p0 in start_positions)
         self.max_new = max((len(e.tokens) for e in entries), default=0)
+        if self.n_row_cap > n_tok and not self.all_single:
+            # rows padded for a captured prompt step: the kernels' shapes must hold for any count of tokens up to the rows
+            self.max_new = self.n_row_cap
         self.max_len_after = max(self.lengths_after, default=0)
         for key, g in self.cache.groups.items():
             bt = self._h(("bt", key))

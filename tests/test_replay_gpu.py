@@ -10,6 +10,7 @@ import sys
 
 import numpy as np
 import pytest
+import torch
 
 from tests import tiny, traces
 
@@ -116,6 +117,40 @@ def test_cuts_agree_with_each_other(folders, requests_and_refs, dtype):
     for rid in reqs:
         assert tiny.rel_err(b[rid], a[rid].astype(np.float64)) <= tol
         assert tiny.rel_err(c[rid], a[rid].astype(np.float64)) <= tol
+
+
+def test_short_prompts_replayed_as_graphs(folders):
+    """One sequence's prompt steps of up to 1,024 tokens are captured per bucket of rows and replayed
+    (padding rows of sequence -1): the same logits as the eager step, at bucket edges, for pieces that
+    continue a sequence, with two wanted places; a bucket's graph is used again for another length."""
+    from odin_infer_b200 import Engine, Engine_Opts, StepEntry
+    from odin_infer_b200.csrc import ops
+    raw, _ = tiny.TINIES["D"]
+    out = {}
+    for graphs in (False, True):
+        e = Engine.load(folders["D"], Engine_Opts(max_ctx=1536, max_tokens=4 * 1536, dtype="bfloat16", verbose=False,
+                                                  cuda_graphs=graphs))
+        rows = []
+        try:
+            for i, n in enumerate((2, 31, 32, 33, 64, 65, 100, 129, 300, 1000, 90)):
+                s = e.take_slot()
+                toks = tiny.random_tokens(n + 40, raw["vocab_size"], 700 + i)
+                a = e.step([StepEntry(s, toks[:n], [0, n - 1])])                  # the prompt, two places wanted
+                b = e.step([StepEntry(s, toks[n:], [len(toks) - n - 1])])         # a piece of 40 that continues it
+                rows += [a.float().cpu(), b.float().cpu()]
+                e.give_back_slot(s)
+            torch.cuda.synchronize()
+            ops.gemm_tc_check()
+            ops.attention_prefill_check()
+            if graphs:
+                keys = [k for k in e.graphs._graphs if k[0] == "prompt"]
+                assert len(keys) < 2 * 11, "lengths of one bucket share a graph"
+        finally:
+            e.destroy()
+        out[graphs] = rows
+    for a, b in zip(out[True], out[False]):
+        assert a.shape == b.shape
+        assert (a - b).abs().max().item() <= 2e-2 * b.abs().max().item()
 
 
 def test_trace_run_program(folders, requests_and_refs, tmp_path):

@@ -32,7 +32,8 @@ def test_start_step_tables():
     starts = [m.extend(e.slot, len(e.tokens)) for e in entries]
     b = StepBatch(m, entries, starts, "cpu", pad_rows_to=80, pad_seqs_to=4)
     t = tables(b)
-    assert b.n_seqs == 3 and b.n_tokens == 74 and b.n_rows == 80 and not b.all_single and b.all_start and b.max_new == 70
+    assert b.n_seqs == 3 and b.n_tokens == 74 and b.n_rows == 80 and not b.all_single and b.all_start
+    assert b.max_new == 80   # padded rows (a captured prompt step): launch shapes hold for any count up to the rows
     assert list(t["tok_ids"][:5]) == [5, 6, 7, 9, 0] and list(t["tok_pos"][:6]) == [0, 1, 2, 0, 0, 1]
     assert list(t["tok_seq"][:5]) == [0, 0, 0, 1, 2] and (t["tok_seq"][74:] == -1).all()   # padding rows
     assert list(t["seq_start"]) == [0, 3, 4, 74, 74] and list(t["seq_len_after"]) == [3, 1, 70, 0]
@@ -40,6 +41,7 @@ def test_start_step_tables():
     bt = next(v for k, v in t.items() if isinstance(k, tuple))
     assert (bt[0, 1:] == -1).all() and bt[0, 0] >= 0 and (bt[2, :2] >= 0).all() and (bt[3] == -1).all()
     assert len({int(bt[0, 0]), int(bt[1, 0]), int(bt[2, 0]), int(bt[2, 1])}) == 4          # no page held twice
+    assert StepBatch(m, entries, starts, "cpu").max_new == 70
     with pytest.raises(StepError, match="outside"):
         StepBatch(m, [StepEntry(slots[0], [1], [1])], [3], "cpu")
 
