@@ -15,10 +15,12 @@ from .step import StepBatch, StepEntry
 
 BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 
-# A short prompt of one sequence is launch-bound too when it runs eagerly (a few hundred launches of
-# ~25 us of host time each: 8 ms for what the device does in 3): such steps are captured per bucket
-# of their token count as well, padded with rows of sequence -1.
+# Short prompts are launch-bound too when they run eagerly (a few hundred launches of ~25 us of host
+# time each: 8 ms for what the device does in 3): steps of a few sequences with up to 1,024 tokens in
+# all are captured as well, per bucket of their token count and of their number of sequences, padded
+# with rows of sequence -1 and with empty sequences.
 PROMPT_BUCKETS = (32, 64, 128, 192, 256, 384, 512, 768, 1024)
+PROMPT_SEQ_BUCKETS = (1, 2, 4, 8, 16)
 
 
 def bucket_for(n: int) -> int | None:
@@ -38,16 +40,18 @@ class DecodeGraphs:
         """Is this a step that `run` may replay a graph for?"""
         if all(len(e.tokens) == 1 for e in entries):
             return True
-        return len(entries) == 1 and 1 < len(entries[0].tokens) <= PROMPT_BUCKETS[-1] and len(entries[0].want) > 0
+        return (len(entries) <= PROMPT_SEQ_BUCKETS[-1] and sum(len(e.tokens) for e in entries) <= PROMPT_BUCKETS[-1]
+                and any(e.want for e in entries))
 
     def _run_prompt(self, entries: list[StepEntry], starts: list[int]) -> torch.Tensor | None:
-        """One sequence's tokens (a prompt or a piece of one) in a bucket of rows."""
-        n = len(entries[0].tokens)
+        """A few sequences' tokens (prompts or pieces of them) in a bucket of rows and of sequences."""
+        n = sum(len(e.tokens) for e in entries)
         rows = next(b for b in PROMPT_BUCKETS if n <= b)
-        key = ("prompt", rows, len(entries[0].want))
+        seqs = next(b for b in PROMPT_SEQ_BUCKETS if len(entries) <= b)
+        key = ("prompt", rows, seqs, sum(len(e.want) for e in entries))
         hit = self._graphs.get(key)
         if hit is None:
-            batch = StepBatch(self.cache, entries, starts, self.rt.device, pad_rows_to=rows, pad_seqs_to=1)
+            batch = StepBatch(self.cache, entries, starts, self.rt.device, pad_rows_to=rows, pad_seqs_to=seqs)
             self.rt.run(self.model, batch)          # once eagerly, as for decode steps
             torch.cuda.current_stream().synchronize()
             graph = torch.cuda.CUDAGraph()
@@ -66,7 +70,7 @@ class DecodeGraphs:
     def run(self, entries: list[StepEntry], starts: list[int], device_tokens=None) -> torch.Tensor | None:
         """Logits [wanted, vocab] of a one-token-per-sequence step (or of one sequence's short
         prompt), or NotImplemented if the batch is larger than the largest bucket."""
-        if len(entries) == 1 and len(entries[0].tokens) > 1:
+        if any(len(e.tokens) > 1 for e in entries):
             return self._run_prompt(entries, starts)
         bucket = bucket_for(len(entries))
         if bucket is None:

@@ -256,7 +256,7 @@ class Runtime:
                                  window, scratch, n_split)
             return
         if self.dtype == torch.bfloat16 and not step.all_single and ops.attention_prefill_supported(head_dim):
-            ops.attention_prefill(q, out, step.n_seqs, step.max_new, n_q, n_kv, head_dim, k_line, v_line,
+            ops.attention_prefill(q, out, step.n_seq_cap, step.max_new, n_q, n_kv, head_dim, k_line, v_line,
                                   step.seq_start, step.seq_len_after, block_table, window)
             return
         ops.attention_plain(q, out, n_q, n_kv, head_dim, k_line, v_line, step.tok_pos, step.tok_seq, block_table,

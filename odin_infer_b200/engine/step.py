@@ -52,6 +52,7 @@ class StepBatch:
         self.n_seq_cap = max(len(entries), pad_seqs_to)
         self.n_row_cap = max(sum(len(e.tokens) for e in entries), pad_rows_to)
         self.all_rows_wanted = all_rows_wanted
+        self._for_graph = pad_rows_to > 0 or pad_seqs_to > 0  # fixed buffers of a captured step
         wanted = sum(len(e.want) for e in entries)
         self.n_logit_cap = self.n_row_cap if all_rows_wanted else wanted
         # layout of the arena (int32 counts)
@@ -149,7 +150,7 @@ class StepBatch:
         self.all_single = all(len(e.tokens) == 1 for e in entries)
         self.all_start = all(p0 == 0 for p0 in start_positions)
         self.max_new = max((len(e.tokens) for e in entries), default=0)
-        if self.n_row_cap > n_tok and not self.all_single:
+        if self._for_graph and not self.all_single:
             # rows padded for a captured prompt step: the kernels' shapes must hold for any count of tokens up to the rows
             self.max_new = self.n_row_cap
         self.max_len_after = max(self.lengths_after, default=0)

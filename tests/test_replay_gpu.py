@@ -120,9 +120,10 @@ def test_cuts_agree_with_each_other(folders, requests_and_refs, dtype):
 
 
 def test_short_prompts_replayed_as_graphs(folders):
-    """One sequence's prompt steps of up to 1,024 tokens are captured per bucket of rows and replayed
-    (padding rows of sequence -1): the same logits as the eager step, at bucket edges, for pieces that
-    continue a sequence, with two wanted places; a bucket's graph is used again for another length."""
+    """Prompt steps of up to 1,024 tokens are captured per bucket of rows and of sequences and replayed
+    (padding rows of sequence -1, empty padding sequences): the same logits as the eager step, at bucket
+    edges, for pieces that continue a sequence, with two wanted places, for a few sequences of unequal
+    lengths; a bucket's graph is used again for other lengths."""
     from odin_infer_b200 import Engine, Engine_Opts, StepEntry
     from odin_infer_b200.csrc import ops
     raw, _ = tiny.TINIES["D"]
@@ -139,12 +140,22 @@ def test_short_prompts_replayed_as_graphs(folders):
                 b = e.step([StepEntry(s, toks[n:], [len(toks) - n - 1])])         # a piece of 40 that continues it
                 rows += [a.float().cpu(), b.float().cpu()]
                 e.give_back_slot(s)
+            # a few sequences at once: the same buckets (128 rows, 4 sequences, 3 wanted places), the lengths
+            # spread differently each time, the longest beyond what the graph was captured with
+            for i, lens in enumerate(((5, 60, 20), (70, 3, 10), (1, 1, 97), (40, 40, 40))):
+                slots = [e.take_slot() for _ in lens]
+                toks = [tiny.random_tokens(n, raw["vocab_size"], 800 + 10 * i + j) for j, n in enumerate(lens)]
+                rows.append(e.step([StepEntry(s, t, [len(t) - 1]) for s, t in zip(slots, toks)]).float().cpu())
+                rows.append(e.step([StepEntry(s, [7], [0]) for s in slots]).float().cpu())   # and one token each
+                for s in slots:
+                    e.give_back_slot(s)
             torch.cuda.synchronize()
             ops.gemm_tc_check()
             ops.attention_prefill_check()
             if graphs:
                 keys = [k for k in e.graphs._graphs if k[0] == "prompt"]
                 assert len(keys) < 2 * 11, "lengths of one bucket share a graph"
+                assert sum(1 for k in keys if k[2] == 4) == 1, "the four steps of three sequences share one graph"
         finally:
             e.destroy()
         out[graphs] = rows
