@@ -208,7 +208,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
     const int n_clusters = (int)(gridDim.x >> 1), cluster_id = (int)(blockIdx.x >> 1);
     static_assert(!(DUAL && WIDE), "the SwiGLU epilogue is for many tokens");
-    const long long n_tiles = WIDE ? (long long)p.tiles_m * p.n_split : (long long)p.tiles_m * p.tiles_n;
+    // WIDE: an item is (weight tile, K part, tile of 256 tokens), the tokens' tile running fastest, so that the
+    // items that share a weight tile's K part run at about the same time and the second finds it in L2
+    const long long n_tiles = WIDE ? (long long)p.tiles_m * p.n_split * p.tiles_n : (long long)p.tiles_m * p.tiles_n;
 
     if (warp == 0) {
         // ------------------------------------------------------- TMA producer (both CTAs)
@@ -219,8 +221,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             for (long long w = cluster_id; w < n_tiles && ok; w += n_clusters) {
                 int tm, tn, kb0 = 0, kb1 = p.kb_total;
                 if (WIDE) {
-                    tm = (int)(w / p.n_split); tn = 0;
-                    kb0 = (int)(w % p.n_split) * p.kb_per_split; kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+                    const long long rest = w / p.tiles_n;
+                    tn = (int)(w % p.tiles_n); tm = (int)(rest / p.n_split);
+                    kb0 = (int)(rest % p.n_split) * p.kb_per_split; kb1 = min(p.kb_total, kb0 + p.kb_per_split);
                 } else {
                     tile_of(w, p.tiles_m, p.tiles_n, tm, tn);
                 }
@@ -266,7 +269,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 tc::fence_after_sync();
                 const uint32_t tmem_d = tmem_base + acc * BN;
                 int kb0 = 0, kb1 = p.kb_total;
-                if (WIDE) { kb0 = (int)(w % p.n_split) * p.kb_per_split; kb1 = min(p.kb_total, kb0 + p.kb_per_split); }
+                if (WIDE) { kb0 = (int)((w / p.tiles_n) % p.n_split) * p.kb_per_split; kb1 = min(p.kb_total, kb0 + p.kb_per_split); }
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!tc::mbar_wait(&full[stage], phase, abort_flag)) { report2(p.error, 3, (int)w, kb, stage); ok = false; break; }
                     tc::fence_after_sync();
@@ -291,7 +294,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const uint32_t acc_empty_leader0 = map_to_rank(&acc_empty[0], 0);
         for (long long w = cluster_id; w < n_tiles && ok; w += n_clusters, ++local) {
             int tm, tn;
-            if (WIDE) { tm = (int)(w / p.n_split); tn = 0; }
+            if (WIDE) { tn = (int)(w % p.tiles_n); tm = (int)((w / p.tiles_n) / p.n_split); }
             else tile_of(w, p.tiles_m, p.tiles_n, tm, tn);
             const uint32_t acc = local % ACC_BUFS, acc_phase = (local / ACC_BUFS) & 1;
             if (!tc::mbar_wait(&acc_full[acc], acc_phase, abort_flag)) { if (lane == 0 && quarter == 2) report2(p.error, 4, (int)w, -1, (int)acc); ok = false; break; }
@@ -300,16 +303,17 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             TO* out = reinterpret_cast<TO*>(p.out);
             if (WIDE) {
                 // C[token c][weight row i]: the warp writes 32 consecutive elements of a token's row
-                TO* dst = out + (size_t)(w % p.n_split) * p.split_stride + i;
+                const int tok0 = tn * BN;  // first token of this item's tile
+                TO* dst = out + (size_t)((w / p.tiles_n) % p.n_split) * p.split_stride + (size_t)tok0 * p.ldc + i;
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN && c0 < p.N; c0 += 32) {
+                for (int c0 = 0; c0 < BN && tok0 + c0 < p.N; c0 += 32) {
                     uint32_t r[32];
                     tc::tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + c0, r);
                     tc::tmem_ld_wait();
                     if (i < p.M) {
 #pragma unroll
                         for (int c = 0; c < 32; ++c)
-                            if (c0 + c < p.N) dst[(size_t)(c0 + c) * p.ldc] = from_f32<TO>(__uint_as_float(r[c]));
+                            if (tok0 + c0 + c < p.N) dst[(size_t)(c0 + c) * p.ldc] = from_f32<TO>(__uint_as_float(r[c]));
                     }
                 }
             } else
@@ -439,7 +443,7 @@ int launch2(const CUtensorMap& ma, const CUtensorMap& mw, const Params2& p, cuda
         if (e != cudaSuccess || n <= 0) { cudaGetLastError(); return ODIN_ERR_UNSUPPORTED; }
         max_clusters = n;
     }
-    const long long tiles = WIDE ? (long long)p.tiles_m * p.n_split : (long long)p.tiles_m * p.tiles_n;
+    const long long tiles = WIDE ? (long long)p.tiles_m * p.n_split * p.tiles_n : (long long)p.tiles_m * p.tiles_n;
     const int clusters = (int)(tiles < max_clusters ? tiles : max_clusters);
     cudaLaunchConfig_t cfg;
     std::memset(&cfg, 0, sizeof(cfg));
@@ -518,7 +522,7 @@ extern "C" int odin_gemm_tc2_swiglu(const void* A, const void* W, void* C, int c
     return ODIN_ERR_UNSUPPORTED;
 }
 
-// A few hundred tokens (M <= 256): C[n_split][M, N] = A[M, K] W[N, K]^T with the weights on the 256-row side
+// Some hundred tokens (in tiles of 256): C[n_split][M, N] = A[M, K] W[N, K]^T with the weights on the 256-row side
 // of the pair's MMA and the tokens on its N side, each CTA of a pair loading half of the tokens and its 128
 // weight rows (32 KB per K block instead of the 48 KB of one CTA with 256 tokens beside it, which bound that
 // kernel by its traffic from L2).  K is cut into n_split parts; part s goes to the slice s of C, split_stride
@@ -527,13 +531,12 @@ extern "C" int odin_gemm_tc2_wide(const void* A, const void* W, void* C, int c_d
                                   long long ldw, long long ldc, int n_split, long long split_stride, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || n_split < 1) return ODIN_ERR_BAD_ARG;
-    if (M > BN) return ODIN_ERR_UNSUPPORTED;
     if ((lda % 8) || (ldw % 8) || (K % 8) || (((uintptr_t)A) & 15) || (((uintptr_t)W) & 15)) return ODIN_ERR_UNSUPPORTED;
     if (n_split > 1 && c_dtype != ODIN_F32) return ODIN_ERR_BAD_ARG;
     Params2 p;
     p.out = C; p.ldc = ldc; p.M = N; p.N = M; p.K = K;   // the kernel's M side holds the weight rows
     p.tiles_m = (N + 2 * BM - 1) / (2 * BM);
-    p.tiles_n = 1;
+    p.tiles_n = (M + BN - 1) / BN;  // tiles of 256 tokens
     p.kb_total = (K + BK - 1) / BK;
     if (n_split > p.kb_total) n_split = p.kb_total;
     p.kb_per_split = (p.kb_total + n_split - 1) / n_split;

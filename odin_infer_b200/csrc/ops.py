@@ -356,12 +356,13 @@ def gemm_tc2(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bo
 
 
 def gemm_tc2_wide(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n_split: int = 1) -> None:
-    """out = a[M, K] @ w[N, K]^T for a few hundred tokens (M <= 256) on pairs of SMs, the weights on the wide
-    side of the MMA: out is [M, N], or float32 [n_split, M, N] partial sums of the K parts (as `gemm_tc`)."""
+    """out = a[M, K] @ w[N, K]^T for some hundred tokens on pairs of SMs, the weights on the wide side of the
+    MMA and the tokens in tiles of 256 on its N side: out is [M, N], or float32 [n_split, M, N] partial sums of
+    the K parts (as `gemm_tc`)."""
     M, K = a.shape
     N = w.shape[0]
-    if not gemm_tc_supported(a, w) or M > 256:
-        raise KernelError("gemm_tc2_wide: bfloat16 operands with 16-byte aligned rows and at most 256 tokens")
+    if not gemm_tc_supported(a, w):
+        raise KernelError("gemm_tc2_wide: operands must be bfloat16 with 16-byte aligned rows (K and strides multiples of 8)")
     assert w.shape[1] == K and out.stride(-1) == 1
     if out.dim() == 3:
         assert out.dtype == torch.float32 and tuple(out.shape[1:]) == (M, N)

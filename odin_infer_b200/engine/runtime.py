@@ -60,8 +60,8 @@ WEIGHTS_WIDE_MAX_TOKENS = 256
 PAIR_MIN_TOKENS = 257
 
 # up to this many tokens a product whose weight has few tiles still goes through the weights-wide
-# kernel, 256 tokens at a time (see Runtime.linear)
-WIDE_CHUNKS_MAX_TOKENS = int(os.environ.get("ODIN_WIDE_CHUNKS_MAX_TOKENS", "512"))  # measured: faster up to ~600
+# kernel, in tiles of 256 tokens (see Runtime.linear)
+WIDE_CHUNKS_MAX_TOKENS = int(os.environ.get("ODIN_WIDE_CHUNKS_MAX_TOKENS", "1024"))  # measured: faster up to there
 
 # ring length of a product that shares the SM with a decode attention CTA (see Runtime.linear)
 LIGHT_STAGES = int(os.environ.get("ODIN_GEMM_LIGHT_STAGES", "6"))
@@ -184,13 +184,12 @@ class Runtime:
                 and (N + 255) // 256 < self.n_sms // 2):
             # Some hundred tokens and a weight of few 256-row tiles: tiles of 256 x 256 would leave most pairs
             # of SMs idle (the o product of the 8B shape: 16 tiles per 256 tokens for 74 pairs).  The tokens
-            # go through the weights-wide kernel 256 at a time instead, K in parts; the weight passes by once
-            # per piece, the second time mostly from L2.
-            n_split = ops.gemm_tc_splits(K, choose_k_split((N + 255) // 256, (K + 63) // 64, 256, self.n_sms // 2))
+            # go through the weights-wide kernel instead, in tiles of 256 tokens and K in parts; items that share
+            # a weight tile run one after the other, so the second finds it in L2.
+            items = ((N + 255) // 256) * ((M + 255) // 256)
+            n_split = ops.gemm_tc_splits(K, choose_k_split(items, (K + 63) // 64, 256, self.n_sms // 2))
             out = self.empty(n_split, M, N, dtype=torch.float32) if n_split > 1 else self.empty(M, N, dtype=out_dtype)
-            for r0 in range(0, M, 256):
-                piece = out[:, r0:r0 + 256] if n_split > 1 else out[r0:r0 + 256]
-                ops.gemm_tc2_wide(a[r0:r0 + 256], w, piece, n_split)
+            ops.gemm_tc2_wide(a, w, out, n_split)
             return out
         if M > 0 and ops.gemm_tc_supported(a, w):
             if (M >= PAIR_MIN_TOKENS and N > 128 and sink is not None and out_dtype == torch.float32

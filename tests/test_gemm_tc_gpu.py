@@ -185,7 +185,8 @@ def test_pair_kernel_ladder(case, out_dtype):
 
 
 @pytest.mark.parametrize("case", [(256, 512, 256, 1), (129, 1000, 1032, 3), (200, 300, 72, 1), (250, 4096, 4096, 5),
-                                  (192, 6144, 4096, 3), (1, 256, 64, 1), (130, 40, 640, 10)])
+                                  (192, 6144, 4096, 3), (1, 256, 64, 1), (130, 40, 640, 10),
+                                  (257, 512, 256, 2), (512, 4096, 1024, 4), (700, 300, 1032, 3)])   # several tiles of tokens
 def test_pair_kernel_weights_wide(case):
     """The two-CTA kernel for a few hundred tokens (weights on the 256-row side, tokens on the N side, K in
     parts): structured inputs, then random ones; ragged edges in tokens, weight rows and K; a row's result does
