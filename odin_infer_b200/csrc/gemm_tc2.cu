@@ -17,9 +17,9 @@
 //   acc_full[a]  in each CTA: accumulator a is complete (commit to both);
 //   acc_empty[a] in the leader: both CTAs' epilogues have read accumulator a back.
 // DUAL: gate and up products side by side and the SwiGLU in the epilogue, as in gemm_tc.cu.
-// WIDE (129 to 256 tokens): the operands change places: the pair's 256 rows are weight rows, the N
-// side holds the tokens (each CTA loads half of them), K is cut into parts, and the epilogue
-// writes C[token][weight row]: a product of so few tokens is bound by the weights it streams, and
+// WIDE (some hundred tokens): the operands change places: the pair's 256 rows are weight rows, the N
+// side holds a tile of 256 tokens (each CTA loads half of it), K is cut into parts, an item is (weight
+// tile, K part, tile of tokens), and the epilogue writes C[token][weight row]: a product of so few tokens is bound by the weights it streams, and
 // tiles of 256 token rows would be too few to occupy the GPU.
 //
 // Every wait is bounded (tc::mbar_wait); a CTA that gives up sets the error flag, and both
