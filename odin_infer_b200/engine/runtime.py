@@ -59,6 +59,9 @@ WEIGHTS_WIDE_MAX_TOKENS = 256
 # above that a product runs on pairs of SMs (tiles of 256 token rows)
 PAIR_MIN_TOKENS = 257
 
+# from this many tokens on the gate|up product carries the SwiGLU in its epilogue (see gated_linear)
+SWIGLU_FUSED_FROM = int(os.environ.get("ODIN_SWIGLU_FUSED_FROM", "129"))
+
 # up to this many tokens a product whose weight has few tiles still goes through the weights-wide
 # kernel, in tiles of 256 tokens (see Runtime.linear)
 WIDE_CHUNKS_MAX_TOKENS = int(os.environ.get("ODIN_WIDE_CHUNKS_MAX_TOKENS", "1024"))  # measured: faster up to there
@@ -213,10 +216,14 @@ class Runtime:
         (which also adds the partial sums of a split product)."""
         M = a.shape[0]
         act = self.empty(M, inner)
-        if M > WEIGHTS_WIDE_MAX_TOKENS:
+        # From 129 tokens on the pair kernel with the SwiGLU in its epilogue: the gate|up weight has tiles
+        # enough for the pairs of SMs even beside one tile of 256 tokens, and no partial sums are written
+        # (measured against the weights-wide kernel + SwiGLU kernel: 8 to 10 % of the step at 129 to 256 tokens).
+        fused_from = SWIGLU_FUSED_FROM
+        if M >= fused_from:
             a = self.materialize(a)
-        if M > WEIGHTS_WIDE_MAX_TOKENS and ops.gemm_tc_supported(a, w_gate_up):
-            if M >= PAIR_MIN_TOKENS and ops.gemm_tc2_swiglu_supported(inner):
+        if M >= fused_from and ops.gemm_tc_supported(a, w_gate_up):
+            if M > 128 and ops.gemm_tc2_swiglu_supported(inner):
                 ops.gemm_tc2_swiglu(a, w_gate_up, act)
             else:
                 ops.gemm_tc_swiglu(a, w_gate_up, act)
