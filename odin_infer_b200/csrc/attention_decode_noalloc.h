@@ -20,7 +20,10 @@
  *   device current).  Make that first call before any stream capture begins.
  * - The counters on which the key splits of a launch meet, and the library's error flag,
  *   are fixed arrays in the device image too (for every entry point of the library), so
- *   that this one stays free of allocations on every path.
+ *   that this one stays free of allocations on every path.  Because of them the same rule
+ *   holds for ALL decode-attention launches of a process, through whichever entry point: two
+ *   launches that overlap on the GPU mix their arrivals on the counters.  Keep them in stream
+ *   order.
  * - All calls share the one array.  Nothing in it has to be cleared between calls:
  *   each call writes every element it later reads.  But two calls that overlap on
  *   the GPU (different streams, no ordering between them) race on it; keep calls on

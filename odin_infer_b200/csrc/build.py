@@ -24,7 +24,7 @@ import time
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 
-# group -> sources; every group also depends on the headers in HEADERS
+# group -> sources; every group also depends on every header of this folder
 GROUPS = {
     "elementwise": ["elementwise.cu"],
     "gemm_plain": ["gemm_plain.cu"],
@@ -33,10 +33,8 @@ GROUPS = {
     "sampling": ["sampling.cu"],
     "gemm_tc": ["gemm_tc.cu", "gemm_tc2.cu"],
     "attention_decode": ["attention_decode.cu"],
-    "decode_program": ["decode_program.cu"],
-    "attention_prefill": ["attention_prefill.cu", "attention_prefill_tc.cu"],
+    "attention_prefill": ["attention_prefill_tc.cu"],
 }
-HEADERS = ["common.cuh"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -363,34 +363,6 @@ extern "C" int odin_swiglu(const void* gu, int in_dtype, int n_split, long long 
     return 0;
 }
 
-// ------------------------------------------------- a norm's factor, applied late
-// rows: [n, d] bfloat16, weighted by a norm but not yet scaled; ssq: [n, parts] the shares of
-// each row's sum of squares.  out[j] = rows[j] / sqrt(sum(ssq[j]) / width + eps): what a product
-// applies to its sums itself when it can (gemm_tc.cu), for consumers that cannot.
-__global__ void scale_rows_kernel(const bf16* __restrict__ rows, const float* __restrict__ ssq, int parts, int width,
-                                  float eps, bf16* __restrict__ out, int d) {
-    pdl_trigger();
-    pdl_wait();
-    const int j = blockIdx.x;
-    float ss = 0.f;
-    for (int t = 0; t < parts; ++t) ss += ssq[(size_t)j * parts + t];
-    ss /= (float)width;
-    ss += eps;
-    const float f = 1.0f / sqrtf(ss);
-    for (int i = threadIdx.x; i < d; i += blockDim.x)
-        out[(size_t)j * d + i] = __float2bfloat16_rn(__bfloat162float(rows[(size_t)j * d + i]) * f);
-}
-
-extern "C" int odin_scale_rows(const void* rows, const float* ssq, int parts, int width, float eps, void* out, int n,
-                               int d, void* stream) {
-    if (n <= 0) return 0;
-    if (parts < 1 || width < 1) return ODIN_ERR_BAD_ARG;
-    odin_launch(scale_rows_kernel, dim3(n), dim3(256), 0, (cudaStream_t)stream, (const bf16*)rows, ssq, parts, width, eps,
-                (bf16*)out, d);
-    ODIN_LAUNCH_CHECK();
-    return 0;
-}
-
 // ---------------------------------------------------------------------- cast
 template <typename TI, typename TO>
 __global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {

@@ -21,11 +21,6 @@
 // them in a fixed order.  Which part a CTA takes never depends on M, so a token's
 // result does not depend on what else is in the batch.
 //
-// Mode 1 has two optional ends (GemmParams): its input rows may still lack their norm's
-// factor, which is then applied to the sums; and its output may go on into the residual
-// stream and through the next norm's weights, done by the CTA that writes a tile's last
-// partial sum.
-//
 // In the reference this is the weight-times-activation product of every layer
 // (infer/matmul.odin:77-109, one row-dot per thread on the CPU; gemv kernels in
 // infer/metal.odin:76-109 on the GPU).
@@ -41,7 +36,6 @@ constexpr int BM = 128;  // rows of X per tile (MMA M)
 constexpr int BK = 64;   // K elements per stage: 128 bytes, one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int ACC_BUFS = 2;
-constexpr int MAX_SINK_TILES = 4096;
 
 struct GemmParams {
     void* out;             // C (or the partial-sum slices)
@@ -54,23 +48,6 @@ struct GemmParams {
     int dual_offset;       // DUAL: first row of the second Y tile's matrix half
     int stages;            // length of the ring of stages (0: as many as fit)
     int* error;            // set when a wait runs out
-    // Mode 1, few tokens.  The input may be rows that still lack their norm's factor: row j of Y
-    // is to be read as Y[j] / sqrt(sum_t in_ssq[j][t] / in_width + in_eps); the factor is applied
-    // to the sums as they are written.
-    const float* in_ssq;   // [rows_y][in_ssq_parts] sums of squares, or null
-    int in_ssq_parts, in_width;
-    float in_eps;
-    // The output may go on into the residual stream and the norm that follows (SINK): the CTA that
-    // writes a tile's last partial sum adds all of them to res[j][i], stores that, stores
-    // normed[j][i] = res[j][i] * norm_w[i] in bfloat16 (the norm's factor is left to the next
-    // product, see above) and the tile's share of each row's sum of squares in out_ssq[j][tile].
-    float* res;            // [rows_y][rows_x] 32-bit residual stream, row stride res_ld
-    long long res_ld;
-    VecRef norm_w;
-    bf16* normed;          // [rows_y][rows_x], row stride normed_ld
-    long long normed_ld;
-    float* out_ssq;        // [rows_y][tiles_x]
-    int* counters;         // [tiles_x], zero between launches
 };
 
 // DUAL: two Y tiles per stage (rows [j, j+BN) and [dual_offset + j, dual_offset + j + BN) of Y) and
@@ -85,8 +62,7 @@ struct Cfg {
     static constexpr int STAGE = STAGE_X + STAGE_Y;
     static constexpr int STAGES = (196608 / STAGE) > 10 ? 10 : (196608 / STAGE);
     static constexpr int TMEM_COLS = (ACC_BUFS * ACC_W) < 32 ? 32 : (ACC_BUFS * ACC_W);
-    static constexpr int EXTRA = 512 /*row factors*/ + 2048 /*sums of squares per warp*/;
-    static constexpr int SMEM = STAGES * STAGE + 1024 /*alignment*/ + 256 /*barriers*/ + EXTRA;
+    static constexpr int SMEM = STAGES * STAGE + 1024 /*alignment*/ + 256 /*barriers*/;
 };
 
 // The first wait that runs out records who it was: [which wait, block, work item, K block, stage or
@@ -134,13 +110,12 @@ __device__ __forceinline__ void store_vec<bf16>(bf16* dst, const uint32_t* r, in
     }
 }
 
-template <int BN, int MODE, typename TO, bool DUAL = false, bool SINK = false>
+template <int BN, int MODE, typename TO, bool DUAL = false>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                const GemmParams p) {
     using C = Cfg<BN, DUAL>;
     static_assert(!DUAL || MODE == 0, "the SwiGLU epilogue exists for mode 0 only");
-    static_assert(!SINK || (MODE == 1 && std::is_same<TO, float>::value && BN <= 128), "the sink is for few tokens");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t n_stages = (uint32_t)p.stages;  // at most C::STAGES: the ring may be shorter to leave shared memory to a neighbour
@@ -151,9 +126,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     uint64_t* acc_empty = acc_full + ACC_BUFS;    // [ACC_BUFS] accumulator read back
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_BUFS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    int* last_flag = reinterpret_cast<int*>(tmem_slot + 2);
-    float* s_factor = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);  // [128] per row of Y
-    float* s_ssq = s_factor + 128;                                                         // [4 warps][128]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_trigger();  // the next kernel may take its place; it waits for this one before it touches memory
@@ -324,26 +296,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         // ------------------------------------------------------------ epilogue
         const int quarter = warp & 3;  // the TMEM lanes this warp may read: [32*quarter, +32)
         pdl_wait();  // the output may be memory that the previous kernel still reads
-        const int et = (int)threadIdx.x - 64;  // 0..127 among the epilogue's threads
-        const bool scaled = (MODE == 1) && p.in_ssq != nullptr;
-        if (scaled) {
-            // the norm's factor of every row of Y: 1 / sqrt(sum of squares / width + eps), the parts in order
-            if (et < p.rows_y && et < 128) {
-                const float* q = p.in_ssq + (size_t)et * p.in_ssq_parts;
-                float ss = 0.f;
-                for (int t0 = 0; t0 < p.in_ssq_parts; t0 += 8) {
-                    float v[8];
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) v[u] = (t0 + u < p.in_ssq_parts) ? __ldcg(q + t0 + u) : 0.f;
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) ss += v[u];
-                }
-                ss /= (float)p.in_width;
-                ss += p.in_eps;
-                s_factor[et] = 1.0f / sqrtf(ss);
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-        }
         uint32_t local = 0;
         bool ok = true;
         for (long long w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++local) {
@@ -394,9 +346,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll
                         for (int c = 0; c < CH; ++c) {
                             if (j0 + c < p.rows_y) {
-                                float v = __uint_as_float(r[c]);
-                                if (scaled) v *= s_factor[(j0 + c) & 127];
-                                out[(size_t)(j0 + c) * p.ldc + i] = from_f32<TO>(v);
+                                out[(size_t)(j0 + c) * p.ldc + i] = from_f32<TO>(__uint_as_float(r[c]));
                             }
                         }
                     }
@@ -405,57 +355,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             tc::fence_before_sync();
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(&acc_empty[acc]);
-            if (SINK) {
-                // the tile's partial sums meet: whoever writes the last one takes the tile on
-                __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (et == 0) *last_flag = (atomicAdd(&p.counters[tx], 1) == p.n_split - 1);
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (*last_flag) {
-                    __threadfence();
-                    const float* parts = reinterpret_cast<const float*>(p.out);
-                    const bool in_range = i < p.rows_x;
-                    const float wn = in_range ? p.norm_w.at(i) : 0.f;
-                    for (int j0 = 0; j0 < p.rows_y; j0 += 4) {
-                        float v[4], sq[4];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u)
-                            v[u] = (in_range && j0 + u < p.rows_y) ? p.res[(size_t)(j0 + u) * p.res_ld + i] : 0.f;
-                        for (int s0 = 0; s0 < p.n_split; s0 += 4) {
-                            float d[4][4];
-#pragma unroll
-                            for (int a = 0; a < 4; ++a)
-#pragma unroll
-                                for (int u = 0; u < 4; ++u)
-                                    d[a][u] = (in_range && s0 + a < p.n_split && j0 + u < p.rows_y)
-                                                  ? __ldcg(parts + (size_t)(s0 + a) * p.split_stride + (size_t)(j0 + u) * p.ldc + i)
-                                                  : 0.f;
-#pragma unroll
-                            for (int a = 0; a < 4; ++a)
-#pragma unroll
-                                for (int u = 0; u < 4; ++u) v[u] += d[a][u];  // x, then the parts in order
-                        }
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            if (in_range && j0 + u < p.rows_y) {
-                                p.res[(size_t)(j0 + u) * p.res_ld + i] = v[u];
-                                p.normed[(size_t)(j0 + u) * p.normed_ld + i] = __float2bfloat16_rn(wn * v[u]);
-                            }
-                            sq[u] = warp_sum(v[u] * v[u]);
-                        }
-                        if (lane == 0) {
-#pragma unroll
-                            for (int u = 0; u < 4; ++u) s_ssq[quarter * 128 + ((j0 + u) & 127)] = sq[u];
-                        }
-                    }
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                    if (et < p.rows_y && et < 128)
-                        p.out_ssq[(size_t)et * p.tiles_x + tx] =
-                            ((s_ssq[et] + s_ssq[128 + et]) + s_ssq[256 + et]) + s_ssq[384 + et];
-                    if (et == 0) p.counters[tx] = 0;
-                    asm volatile("bar.sync 1, 128;" ::: "memory");  // s_ssq and last_flag are free again
-                }
-            }
         }
     }
 
@@ -552,20 +451,10 @@ int sm_count() {
     return n;
 }
 
-int* tile_counters() {  // for the sink: one per 128-row tile of the weight, zero between launches
-    static int* c = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        if (cudaMalloc(&c, MAX_SINK_TILES * sizeof(int)) == cudaSuccess) cudaMemset(c, 0, MAX_SINK_TILES * sizeof(int));
-        else c = nullptr;
-    });
-    return c;
-}
-
-template <int BN, int MODE, typename TO, bool DUAL = false, bool SINK = false>
+template <int BN, int MODE, typename TO, bool DUAL = false>
 int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, cudaStream_t s) {
     using C = Cfg<BN, DUAL>;
-    auto kern = gemm_tc_kernel<BN, MODE, TO, DUAL, SINK>;
+    auto kern = gemm_tc_kernel<BN, MODE, TO, DUAL>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
@@ -582,16 +471,6 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, cu
     return 0;
 }
 
-int dispatch_sink(int bn, const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, cudaStream_t s) {
-    switch (bn) {
-        case 16: return launch<16, 1, float, false, true>(mx, my, p, s);
-        case 32: return launch<32, 1, float, false, true>(mx, my, p, s);
-        case 64: return launch<64, 1, float, false, true>(mx, my, p, s);
-        case 128: return launch<128, 1, float, false, true>(mx, my, p, s);
-        default: return ODIN_ERR_UNSUPPORTED;
-    }
-}
-
 template <int MODE, typename TO>
 int dispatch_bn(int bn, const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, cudaStream_t s) {
     switch (bn) {
@@ -606,24 +485,6 @@ int dispatch_bn(int bn, const CUtensorMap& mx, const CUtensorMap& my, const Gemm
 
 }  // namespace
 
-// What a product of few tokens (mode 1) may do beside the product; all pointers may be null.
-// in_ssq: the rows of A still lack their norm's factor 1 / sqrt(sum(in_ssq[j][0..parts)) / in_width + in_eps),
-// which is applied to the sums.  res ...: the sums go on into the 32-bit residual stream res[M][N] (+=),
-// normed[M][N] = res * norm_w in bfloat16, and out_ssq[M][ceil(N/128)] receives each 128-column tile's share
-// of the rows' sums of squares: the input of the next product, with its in_ssq.
-struct OdinGemmExtras {
-    const float* in_ssq;
-    int in_ssq_parts, in_width;
-    float in_eps;
-    float* res;
-    long long res_ld;
-    const void* norm_w;
-    int norm_w_dtype;
-    void* normed;
-    long long normed_ld;
-    float* out_ssq;
-};
-
 // A: [M, K] bfloat16, row stride lda; W: [N, K] bfloat16, row stride ldw; C: [M, N] of
 // c_dtype, row stride ldc, or with n_split > 1: float32 partial sums [n_split][M][ldc...]
 // split_stride elements apart.  mode 0: tokens on the 128-row side; mode 1: weights on
@@ -631,20 +492,9 @@ struct OdinGemmExtras {
 // of 8 elements and the pointers 16-byte aligned (TMA), else ODIN_ERR_UNSUPPORTED.
 // stages: the length of the ring of shared-memory stages; 0: as many as fit (the product then has the SM to
 // itself), fewer to let a CTA of the kernel before or after it share the SM.
-extern "C" int odin_gemm_tc_ex(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, long long lda,
-                               long long ldw, long long ldc, int mode, int bn, int n_split, long long split_stride,
-                               int stages, const OdinGemmExtras* extras, void* stream);
-
 extern "C" int odin_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, long long lda,
                             long long ldw, long long ldc, int mode, int bn, int n_split, long long split_stride,
                             int stages, void* stream) {
-    return odin_gemm_tc_ex(A, W, C, c_dtype, M, N, K, lda, ldw, ldc, mode, bn, n_split, split_stride, stages, nullptr,
-                           stream);
-}
-
-extern "C" int odin_gemm_tc_ex(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, long long lda,
-                               long long ldw, long long ldc, int mode, int bn, int n_split, long long split_stride,
-                               int stages, const OdinGemmExtras* extras, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || n_split < 1) return ODIN_ERR_BAD_ARG;
     if ((lda % 8) || (ldw % 8) || (K % 8) || (((uintptr_t)A) & 15) || (((uintptr_t)W) & 15)) return ODIN_ERR_UNSUPPORTED;
@@ -663,29 +513,6 @@ extern "C" int odin_gemm_tc_ex(const void* A, const void* W, void* C, int c_dtyp
     p.dual_offset = 0;
     p.stages = stages;
     p.error = error_flag();
-    p.in_ssq = nullptr; p.in_ssq_parts = 0; p.in_width = 1; p.in_eps = 0.f;
-    p.res = nullptr; p.res_ld = 0; p.norm_w = VecRef{nullptr, 0}; p.normed = nullptr; p.normed_ld = 0;
-    p.out_ssq = nullptr; p.counters = nullptr;
-    bool sink = false;
-    if (extras != nullptr) {
-        if (mode != 1 || M > bn || M > 128) return ODIN_ERR_UNSUPPORTED;  // few tokens, one tile of them
-        if (extras->in_ssq != nullptr) {
-            if (extras->in_ssq_parts < 1 || extras->in_width < 1) return ODIN_ERR_BAD_ARG;
-            p.in_ssq = extras->in_ssq; p.in_ssq_parts = extras->in_ssq_parts; p.in_width = extras->in_width;
-            p.in_eps = extras->in_eps;
-        }
-        if (extras->res != nullptr) {
-            if (c_dtype != ODIN_F32 || extras->normed == nullptr || extras->out_ssq == nullptr || extras->norm_w == nullptr)
-                return ODIN_ERR_BAD_ARG;
-            if ((N + BM - 1) / BM > MAX_SINK_TILES) return ODIN_ERR_UNSUPPORTED;
-            p.res = extras->res; p.res_ld = extras->res_ld;
-            p.norm_w = VecRef{extras->norm_w, extras->norm_w_dtype == ODIN_BF16};
-            p.normed = (bf16*)extras->normed; p.normed_ld = extras->normed_ld; p.out_ssq = extras->out_ssq;
-            p.counters = tile_counters();
-            if (p.counters == nullptr) return ODIN_ERR_UNSUPPORTED;
-            sink = true;
-        }
-    }
     CUtensorMap mx, my;
     int rc;
     if (mode == 0) {
@@ -701,7 +528,6 @@ extern "C" int odin_gemm_tc_ex(const void* A, const void* W, void* C, int c_dtyp
     }
     p.tiles_x = (p.rows_x + BM - 1) / BM;
     p.tiles_y = (p.rows_y + bn - 1) / bn;
-    if (sink) return dispatch_sink(bn, mx, my, p, s);
     if (c_dtype == ODIN_F32)
         return mode == 0 ? dispatch_bn<0, float>(bn, mx, my, p, s) : dispatch_bn<1, float>(bn, mx, my, p, s);
     if (c_dtype == ODIN_BF16)
@@ -727,9 +553,6 @@ extern "C" int odin_gemm_tc_swiglu(const void* A, const void* W, void* C, int c_
     p.kb_per_split = p.kb_total;
     p.n_split = 1;
     p.stages = 0;
-    p.in_ssq = nullptr; p.in_ssq_parts = 0; p.in_width = 1; p.in_eps = 0.f;
-    p.res = nullptr; p.res_ld = 0; p.norm_w = VecRef{nullptr, 0}; p.normed = nullptr; p.normed_ld = 0;
-    p.out_ssq = nullptr; p.counters = nullptr;
     p.dual_offset = I;
     p.error = error_flag();
     p.rows_x = M;
@@ -762,11 +585,7 @@ extern "C" int odin_gemm_tc_error() {
     if (f == nullptr) return 0;
     int v = 0;
     if (cudaMemcpy(&v, f, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-    if (v) {
-        cudaMemset(f, 0, sizeof(int));
-        // partial sums of the failed launch may never have met: their counters start from zero again
-        if (int* c = tile_counters()) cudaMemset(c, 0, MAX_SINK_TILES * sizeof(int));
-    }
+    if (v) cudaMemset(f, 0, sizeof(int));
     return v;
 }
 

@@ -67,7 +67,6 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--width", type=int, default=4096)
-    ap.add_argument("--variant", default="tc", choices=["tc", "mma"], help="prefill-attention kernel")
     ap.add_argument("--iters", type=int, default=20)
     args = ap.parse_args(argv)
     out: dict = {"kernel": args.kernel}
@@ -114,10 +113,10 @@ def main(argv=None) -> int:
         o = torch.empty_like(q)
         ss = torch.tensor([0, T], dtype=torch.int32, device=DEV)
         sl = torch.tensor([T], dtype=torch.int32, device=DEV)
-        ms = timeit(lambda: ops.attention_prefill(q, o, 1, T, hq, hkv, hd, k, v, ss, sl, bt, 0, variant=args.variant),
+        ms = timeit(lambda: ops.attention_prefill(q, o, 1, T, hq, hkv, hd, k, v, ss, sl, bt, 0),
                     args.iters)
         ops.attention_prefill_check()
-        out.update(tokens=T, variant=args.variant, us=round(ms * 1e3, 2), tflops=round(4 * hq * hd * (T * (T + 1) / 2) / ms / 1e9, 1))
+        out.update(tokens=T, us=round(ms * 1e3, 2), tflops=round(4 * hq * hd * (T * (T + 1) / 2) / ms / 1e9, 1))
     else:
         n, d, s = args.rows, args.width, max(args.split, 1)
         x = torch.randn(n, d, device=DEV)

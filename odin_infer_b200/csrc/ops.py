@@ -67,99 +67,10 @@ def _check(code: int, what: str, kernels: int = 1) -> None:
 
 
 def _fn(group: str, name: str):
-    """A launcher of the kernel libraries.  While a program is being recorded, every kernel that
-    is not part of it runs after what has been recorded so far."""
-    if _program_bn and group != "decode_program":
-        program_flush()
+    """A launcher of the kernel libraries."""
     f = getattr(build.load(group), name)
     f.restype = c_int
     return f
-
-
-# ---------------------------------------------------------------------------- programs
-# A decode step of few tokens can run as a program: while one is being recorded, the wrappers
-# below hand the operations that a program can hold (products of few tokens with 32-bit partial
-# sums, residual add + RMSNorm, SwiGLU of partial sums, decode attention with head preparation)
-# to the persistent kernel of decode_program.cu instead of launching a kernel each.  Whatever
-# else is launched in between flushes the program first, so the order of the stream is kept.
-_program_bn = 0  # > 0: the token bucket of the program being recorded
-
-
-def recording() -> bool:
-    return _program_bn > 0
-
-
-def _prog(name: str):
-    f = getattr(build.load("decode_program"), name)
-    f.restype = c_int
-    return f
-
-
-def _program_count() -> None:
-    """Programs launched since the last call count as kernels."""
-    global _launches, _program_seen
-    f = build.load("decode_program").odin_prog_launches
-    f.restype = c_longlong
-    n = int(f())
-    _launches += n - _program_seen
-    _program_seen = n
-
-
-_program_seen = 0
-
-
-def program_flush() -> None:
-    code = _prog("odin_prog_flush")(_stream())
-    _program_count()
-    _check(code, "decode program", kernels=0)
-
-
-class program:
-    """`with ops.program(bn):` records the operations of a step of at most bn tokens (16, 32 or
-    64) and launches them as programs; only kernels of this package may run inside (a torch
-    operation between two of them would run ahead of the recorded ones)."""
-
-    def __init__(self, bn: int):
-        self.bn = bn
-
-    def __enter__(self):
-        global _program_bn
-        if _program_bn:
-            raise KernelError("a program is already being recorded")
-        _check(_prog("odin_prog_begin")(c_int(self.bn)), "decode program", kernels=0)
-        _program_bn = self.bn
-        return self
-
-    def __exit__(self, *exc):
-        global _program_bn
-        _program_bn = 0
-        code = _prog("odin_prog_end")(_stream())
-        _program_count()
-        if exc[0] is None:
-            _check(code, "decode program", kernels=0)
-        return False
-
-
-def program_bucket(n_tokens: int) -> int:
-    """The token bucket of a program for n_tokens, 0 if there is none."""
-    return 16 if n_tokens <= 16 else 32 if n_tokens <= 32 else 64 if n_tokens <= 64 else 0
-
-
-def program_check() -> None:
-    detail = (c_int * 8)()
-    v = _prog("odin_prog_error")(detail)
-    if v != 0:
-        raise KernelError(f"decode program: a device-side wait ran out; results are invalid (wait, block, operation, "
-                          f"item, K block, slot, grid: {list(detail)[:7]})")
-
-
-def _recorded(code: int, what: str) -> bool:
-    """The answer of an odin_prog_* call: recorded, or to be launched as a kernel of its own."""
-    if code == -1:
-        return False
-    _program_count()
-    _check(code, what, kernels=0)
-    return True
 
 
 # ----------------------------------------------------------------------------
@@ -196,11 +107,6 @@ def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tenso
     else:
         assert rows.dtype == torch.int32 and rows.numel() == n_rows
     assert weight.numel() == d
-    if (_program_bn and rows is None and out.dtype == torch.bfloat16 and (delta is None or delta.dtype == torch.float32)
-            and _recorded(_prog("odin_prog_add_rmsnorm")(
-                _ptr(x), _ptr(delta), c_int(n_split), c_longlong(stride), _ptr(weight), c_int(dtype_code(weight.dtype)),
-                c_float(eps), _ptr(out), c_int(n_rows), c_int(d), _stream()), "add_rmsnorm")):
-        return
     _check(_fn("elementwise", "odin_add_rmsnorm")(
         _ptr(x), _ptr(delta), c_int(dtype_code(delta.dtype) if delta is not None else 0), c_int(n_split),
         c_longlong(stride), _ptr(weight), c_int(dtype_code(weight.dtype)), c_float(eps), _ptr(out),
@@ -213,22 +119,9 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     T, I = out.shape
     assert gate_up.is_contiguous() and out.is_contiguous() and tuple(gate_up.shape[-2:]) == (T, 2 * I)
     n_split, stride = (gate_up.shape[0], T * 2 * I) if gate_up.dim() == 3 else (1, 0)
-    if (_program_bn and gate_up.dtype == torch.float32 and out.dtype == torch.bfloat16
-            and _recorded(_prog("odin_prog_swiglu")(_ptr(gate_up), c_int(n_split), c_longlong(stride), _ptr(out),
-                                                    c_int(T), c_int(I), _stream()), "swiglu")):
-        return
     _check(_fn("elementwise", "odin_swiglu")(
         _ptr(gate_up), c_int(dtype_code(gate_up.dtype)), c_int(n_split), c_longlong(stride), _ptr(out),
         c_int(dtype_code(out.dtype)), c_int(T), c_int(I), _stream()), "swiglu")
-
-
-def scale_rows(rows: torch.Tensor, ssq: torch.Tensor, width: int, eps: float, out: torch.Tensor) -> None:
-    """out[j] = rows[j] / sqrt(sum(ssq[j]) / width + eps) for bfloat16 rows [n, d] (see gemm_tc's sink)."""
-    assert rows.dtype == out.dtype == torch.bfloat16 and rows.is_contiguous() and out.is_contiguous()
-    assert ssq.dtype == torch.float32 and ssq.is_contiguous() and ssq.shape[0] == rows.shape[0]
-    _check(_fn("elementwise", "odin_scale_rows")(
-        _ptr(rows), _ptr(ssq), c_int(ssq.shape[1]), c_int(width), c_float(eps), _ptr(out), c_int(rows.shape[0]),
-        c_int(rows.shape[1]), _stream()), "scale_rows")
 
 
 def cast(src: torch.Tensor, dst: torch.Tensor) -> None:
@@ -264,15 +157,8 @@ def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-class _GemmExtras(ctypes.Structure):
-    _fields_ = [("in_ssq", c_void_p), ("in_ssq_parts", c_int), ("in_width", c_int), ("in_eps", c_float),
-                ("res", c_void_p), ("res_ld", c_longlong), ("norm_w", c_void_p), ("norm_w_dtype", c_int),
-                ("normed", c_void_p), ("normed_ld", c_longlong), ("out_ssq", c_void_p)]
-
-
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, bn: int, n_split: int = 1,
-            stages: int = 0, row_ssq: torch.Tensor | None = None, row_width: int = 0, row_eps: float = 0.0,
-            sink: tuple | None = None) -> None:
+            stages: int = 0) -> None:
     """out = a[M, K] @ w[N, K]^T on the tcgen05 tensor cores (bfloat16 in, 32-bit accumulation).
 
     mode 0: tokens on the 128-row side of the MMA, tiles of bn weight rows.
@@ -280,13 +166,6 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, bn: 
     n_split > 1: out is float32 [n_split, M, N]; slice s holds the partial sum of K part s.
     stages: length of the kernel's ring of shared-memory stages; 0: as many as fit, fewer to
     leave room on the SM for a CTA of the neighbouring kernel.
-    row_ssq (mode 1): [M, parts] float32; row j of a still lacks its norm's factor
-    1 / sqrt(sum(row_ssq[j]) / row_width + row_eps), which is applied to the sums.
-    sink (mode 1, float32 out): (res, norm_w, normed, out_ssq): the product is added to the
-    32-bit residual stream res [M, N] by the CTA that writes a tile's last partial sum;
-    normed [M, N] bfloat16 = res * norm_w (without the norm's factor) and out_ssq
-    [M, ceil(N/128)] the tiles' shares of each row's sum of squares: what the next product
-    takes as (a, row_ssq).  out then holds scratch only.
     """
     M, K = a.shape
     N = w.shape[0]
@@ -300,32 +179,10 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, bn: 
     else:
         assert tuple(out.shape) == (M, N)
         ldc, stride = out.stride(0), 0
-    if (_program_bn and mode == 1 and out.dtype == torch.float32 and out.dim() == 3 and row_ssq is None and sink is None
-            and _recorded(_prog("odin_prog_gemm")(
-                _ptr(a), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K), c_longlong(a.stride(0)),
-                c_longlong(w.stride(0)), c_longlong(out.stride(1)), c_int(out.shape[0]), c_longlong(out.stride(0)),
-                _stream()), "gemm_tc")):
-        return
-    extras = None
-    if row_ssq is not None or sink is not None:
-        extras = _GemmExtras()
-        if row_ssq is not None:
-            assert row_ssq.dtype == torch.float32 and row_ssq.is_contiguous() and row_ssq.shape[0] == M and row_width > 0
-            extras.in_ssq, extras.in_ssq_parts = row_ssq.data_ptr(), row_ssq.shape[1]
-            extras.in_width, extras.in_eps = row_width, row_eps
-        if sink is not None:
-            res, norm_w, normed, out_ssq = sink
-            assert res.dtype == torch.float32 and tuple(res.shape) == (M, N) and res.stride(1) == 1
-            assert normed.dtype == torch.bfloat16 and tuple(normed.shape) == (M, N) and normed.stride(1) == 1
-            assert out_ssq.dtype == torch.float32 and out_ssq.is_contiguous() and tuple(out_ssq.shape) == (M, (N + 127) // 128)
-            assert norm_w.numel() == N and norm_w.is_contiguous() and out.dtype == torch.float32
-            extras.res, extras.res_ld = res.data_ptr(), res.stride(0)
-            extras.norm_w, extras.norm_w_dtype = norm_w.data_ptr(), dtype_code(norm_w.dtype)
-            extras.normed, extras.normed_ld, extras.out_ssq = normed.data_ptr(), normed.stride(0), out_ssq.data_ptr()
-    _check(_fn("gemm_tc", "odin_gemm_tc_ex")(
+    _check(_fn("gemm_tc", "odin_gemm_tc")(
         _ptr(a), _ptr(w), _ptr(out), c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K),
         c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(ldc), c_int(mode), c_int(bn), c_int(n_split),
-        c_longlong(stride), c_int(stages), ctypes.byref(extras) if extras is not None else None, _stream()), "gemm_tc")
+        c_longlong(stride), c_int(stages), _stream()), "gemm_tc")
 
 
 def gemm_tc_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:
@@ -482,7 +339,11 @@ def attention_decode_scratch(n_tokens: int, n_q: int, head_dim: int, n_split: in
 def attention_decode(q: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
                      k_cache: torch.Tensor, v_cache: torch.Tensor, tok_pos: torch.Tensor, tok_seq: torch.Tensor,
                      block_table: torch.Tensor, window: int, scratch: torch.Tensor, n_split: int) -> None:
-    """One query token per row over its sequence's bfloat16 cache, keys split n_split ways."""
+    """One query token per row over its sequence's bfloat16 cache, keys split n_split ways.
+
+    The counters on which a launch's key splits meet are one array of the library: all
+    decode-attention launches of a process must be ordered on the GPU (one stream, or events
+    between streams); two that overlap would mix their arrivals."""
     B = q.shape[0]
     assert q.dtype == out.dtype == k_cache.dtype == torch.bfloat16
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
@@ -524,14 +385,6 @@ def attention_decode_fused(qkv: torch.Tensor, out: torch.Tensor, n_q: int, n_kv:
                          and k_norm.numel() == head_dim):
         return False
     assert scratch.dtype == torch.float32 and scratch.numel() >= attention_decode_scratch(B, n_q, head_dim, n_split)
-    if (_program_bn and qkv.dtype == torch.float32 and _recorded(_prog("odin_prog_attention")(
-            _ptr(qkv), c_int(parts), c_longlong(part_stride), c_longlong(row_stride), _ptr(out),
-            c_longlong(out.stride(0)), c_int(B), c_int(n_q), c_int(n_kv), c_int(head_dim), _ptr(q_norm), _ptr(k_norm),
-            c_int(dtype_code(q_norm.dtype) if has_norm else 0), c_int(1 if has_norm else 0), c_float(eps), _ptr(cos),
-            _ptr(sin), c_int(rotary_dim), c_int(cos.shape[0]), _ptr(k_cache), _ptr(v_cache), c_int(PAGE),
-            c_int(k_cache.shape[0]), _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table), c_int(block_table.stride(0)),
-            c_int(window), _ptr(scratch), c_int(n_split), c_int(1 if write_kv else 0), _stream()), "attention")):
-        return True
     code = _fn("attention_decode", "odin_attention_decode_fused")(
         _ptr(qkv), c_int(dtype_code(qkv.dtype)), c_int(parts), c_longlong(part_stride), c_longlong(row_stride),
         _ptr(out), c_longlong(out.stride(0)), c_int(B), c_int(n_q), c_int(n_kv), c_int(head_dim), _ptr(q_norm),
@@ -558,18 +411,16 @@ def attention_prefill_supported(head_dim: int) -> bool:
 
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new: int, n_q: int, n_kv: int,
                       head_dim: int, k_cache: torch.Tensor, v_cache: torch.Tensor, seq_start: torch.Tensor,
-                      seq_len_after: torch.Tensor, block_table: torch.Tensor, window: int = 0,
-                      variant: str = "tc") -> None:
+                      seq_len_after: torch.Tensor, block_table: torch.Tensor, window: int = 0) -> None:
     """Flash attention of each sequence's new tokens (rows seq_start[b]..seq_start[b+1] of q) over its
-    bfloat16 cache, which already holds this step's keys and values.  variant "tc": tcgen05.mma with
-    accumulators in tensor memory (128 query rows per CTA); "mma": mma.sync (64 rows per CTA)."""
+    bfloat16 cache, which already holds this step's keys and values: tcgen05.mma with accumulators in
+    tensor memory."""
     T = q.shape[0]
     assert q.dtype == out.dtype == k_cache.dtype == torch.bfloat16
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == n_q * head_dim and out.shape == (T, n_q * head_dim)
     assert tuple(k_cache.shape[1:]) == (n_kv, PAGE, head_dim) and k_cache.is_contiguous() and v_cache.is_contiguous()
     assert seq_start.dtype == torch.int32 and seq_len_after.dtype == torch.int32 and block_table.dtype == torch.int32
-    name = {"tc": "odin_attention_prefill_tc", "mma": "odin_attention_prefill"}[variant]
-    _check(_fn("attention_prefill", name)(
+    _check(_fn("attention_prefill", "odin_attention_prefill_tc")(
         _ptr(q), c_longlong(q.stride(0)), _ptr(out), c_longlong(out.stride(0)), c_int(n_seqs), c_int(max_new),
         c_int(n_q), c_int(n_kv), c_int(head_dim), _ptr(k_cache), _ptr(v_cache), c_int(k_cache.shape[0]),
         _ptr(seq_start), _ptr(seq_len_after), _ptr(block_table), c_int(block_table.stride(0)), c_int(window),
@@ -579,7 +430,7 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new: 
 def attention_prefill_check() -> None:
     detail = (c_int * 32)()
     build.load("attention_prefill").odin_attention_prefill_tc_error_detail(detail)
-    for name in ("odin_attention_prefill_error", "odin_attention_prefill_tc_error"):
+    for name in ("odin_attention_prefill_tc_error",):
         f = getattr(build.load("attention_prefill"), name)
         f.restype = c_int
         code = f()

@@ -98,7 +98,13 @@ class Engine:
         self.cache.zero_state = (lambda slot: self.cache.state[slot].zero_()) if nstate else None
         # decode steps replay CUDA graphs in the serving precision; the 32-bit path stays eager
         self.last_step_h2d_bytes = 0
-        self.graphs = DecodeGraphs(self.rt, self.model, self.cache) if (opts.cuda_graphs and self.rt.dtype == torch.bfloat16) else None
+        self.graphs = None
+        if opts.cuda_graphs and self.rt.dtype == torch.bfloat16:
+            if self.model.graph_safe:
+                self.graphs = DecodeGraphs(self.rt, self.model, self.cache)
+            elif opts.verbose:
+                print("odin_infer_b200: steps run eagerly, not as CUDA graphs: these parts do not declare graph_safe: "
+                      + ", ".join(self.model.parts_not_graph_safe()), file=sys.stderr, flush=True)
         if opts.verbose:
             print(self.summary(), file=sys.stderr, flush=True)
 
@@ -160,27 +166,32 @@ class Engine:
             for t in e.tokens:
                 if not (0 <= t < self.vocab_size):  # infer/forward.odin:26-29
                     raise StepError(f"slot {e.slot}: token {t} is out of range (vocab {self.vocab_size})")
+            for w in e.want:
+                if not (0 <= w < len(e.tokens)):
+                    raise StepError(f"slot {e.slot}: wanted place {w} is outside its {len(e.tokens)} token(s)")
+        if device_tokens is not None and any(len(e.tokens) != 1 for e in entries):
+            raise StepError("tokens from the device: one token per sequence")
         starts, grown = [], []
         try:
             for e in entries:
                 starts.append(self.cache.extend(e.slot, len(e.tokens)))
                 grown.append(e)
+            logits = NotImplemented
+            if self.graphs is not None and self.graphs.takes(entries):
+                logits = self.graphs.run(entries, starts, device_tokens)
+                self.last_step_h2d_bytes = self.graphs.last_h2d_bytes
+            if logits is NotImplemented:
+                batch = StepBatch(self.cache, entries, starts, self.rt.device)
+                if device_tokens is not None:
+                    batch.take_tokens(*device_tokens)
+                logits = self.rt.run(self.model, batch)
+                self.last_step_h2d_bytes = batch.h2d_bytes
         except Exception:
-            for e, s in zip(grown, starts):  # leave the cache as it was
+            # a step that did not run leaves lengths and pages as they were (what kernels may have
+            # written lies beyond every sequence's length and is written again by the next step)
+            for e, s in zip(grown, starts):
                 self._shrink(e.slot, s)
             raise
-        logits = NotImplemented
-        if device_tokens is not None and any(len(e.tokens) != 1 for e in entries):
-            raise StepError("tokens from the device: one token per sequence")
-        if self.graphs is not None and self.graphs.takes(entries):
-            logits = self.graphs.run(entries, starts, device_tokens)
-            self.last_step_h2d_bytes = self.graphs.last_h2d_bytes
-        if logits is NotImplemented:
-            batch = StepBatch(self.cache, entries, starts, self.rt.device)
-            if device_tokens is not None:
-                batch.take_tokens(*device_tokens)
-            logits = self.rt.run(self.model, batch)
-            self.last_step_h2d_bytes = batch.h2d_bytes
         for e in entries:
             self.cache.after_step(e.slot)
         return logits

@@ -5,6 +5,11 @@ kernels; at small batches the launches cost more than the kernels.  Such steps
 are captured once per batch-size bucket and replayed: the step's integer tables
 live in fixed device buffers that are refilled before every replay, padding rows
 (sequence -1) make up the difference to the bucket size and change no result.
+
+Only a model whose parts all say `graph_safe` is captured (the engine asks before it
+builds this object).  A step that finds no graph yet runs eagerly, and that run IS the
+step: the capture that follows records the same launches for later steps without
+executing them, so nothing (keys, values, a mixer's fixed-size state) is applied twice.
 """
 from __future__ import annotations
 
@@ -52,18 +57,29 @@ class DecodeGraphs:
         hit = self._graphs.get(key)
         if hit is None:
             batch = StepBatch(self.cache, entries, starts, self.rt.device, pad_rows_to=rows, pad_seqs_to=seqs)
-            self.rt.run(self.model, batch)          # once eagerly, as for decode steps
-            torch.cuda.current_stream().synchronize()
-            graph = torch.cuda.CUDAGraph()
-            n0 = ops.launch_count()
-            with torch.cuda.graph(graph):
-                logits = self.rt.run(self.model, batch)
-            self._graphs[key] = (graph, batch, logits, ops.launch_count() - n0)
-        else:
-            hit[1].fill(entries, starts)
-        graph, batch, logits, n_kernels = self._graphs[key]
+            return self._first_run(key, batch)
+        graph, batch, logits, n_kernels = hit
+        batch.fill(entries, starts)
         graph.replay()
         ops.add_launches(n_kernels)
+        self.last_h2d_bytes = batch.h2d_bytes
+        return logits
+
+    def _first_run(self, key, batch: StepBatch, device_tokens=None) -> torch.Tensor | None:
+        """The step itself, eagerly (first-use set-up of the kernels - function attributes, tensor
+        maps, error flags, the allocator's pools - must not fall into a capture), then the capture
+        of the same launches for the steps to come.  Returns the eager run's logits."""
+        if device_tokens is not None:
+            batch.take_tokens(*device_tokens)
+        logits = self.rt.run(self.model, batch)
+        torch.cuda.current_stream().synchronize()
+        graph = torch.cuda.CUDAGraph()
+        n0 = ops.launch_count()
+        with torch.cuda.graph(graph):
+            captured = self.rt.run(self.model, batch)
+        n_kernels = ops.launch_count() - n0
+        ops.add_launches(-n_kernels)          # recorded, not launched
+        self._graphs[key] = (graph, batch, captured, n_kernels)
         self.last_h2d_bytes = batch.h2d_bytes
         return logits
 
@@ -83,25 +99,15 @@ class DecodeGraphs:
         if hit is None:
             batch = StepBatch(self.cache, entries, starts, self.rt.device, pad_rows_to=bucket[0], pad_seqs_to=bucket[0],
                               all_rows_wanted=True)
-            # once eagerly: first-use set-up of the kernels (function attributes, tensor maps,
-            # error flags, the allocator's pools) must not fall into the capture
-            self.rt.run(self.model, batch)
-            torch.cuda.current_stream().synchronize()
-            graph = torch.cuda.CUDAGraph()
-            n0 = ops.launch_count()
-            with torch.cuda.graph(graph):
-                logits = self.rt.run(self.model, batch)
-            self._graphs[bucket] = (graph, batch, logits, ops.launch_count() - n0)
-            # the eager run and the capture have written this step's keys already; a replay writes them again
+            logits = self._first_run(bucket, batch, device_tokens)
         else:
-            batch = hit[1]
+            graph, batch, logits, n_kernels = hit
             batch.fill(entries, starts)
-        graph, batch, logits, n_kernels = self._graphs[bucket]
-        if device_tokens is not None:  # the tokens come from the device: into the tables after their copy
-            batch.take_tokens(*device_tokens)
-        graph.replay()
-        ops.add_launches(n_kernels)
-        self.last_h2d_bytes = batch.h2d_bytes
+            if device_tokens is not None:  # the tokens come from the device: into the tables after their copy
+                batch.take_tokens(*device_tokens)
+            graph.replay()
+            ops.add_launches(n_kernels)
+            self.last_h2d_bytes = batch.h2d_bytes
         rows = batch.wanted_rows
         if not rows:
             return None

@@ -42,9 +42,18 @@ class DecoderModel:
         return set().union(*(p.kernel_groups() for p in self._all_parts()))
 
     @property
-    def kernels_only(self) -> bool:
-        """Do all parts launch kernels of this package only (see Part.kernels_only)?"""
-        return all(p.kernels_only for p in self._all_parts())
+    def graph_safe(self) -> bool:
+        """May a step of this model be captured in a CUDA graph and replayed (see Part.graph_safe)?"""
+        return all(p.graph_safe for p in self._all_parts())
+
+    def parts_not_graph_safe(self) -> list[str]:
+        out = []
+        for p in self._all_parts():
+            inner = getattr(p, "_parts", None)
+            for q in (inner() if inner is not None else [p]):
+                if not q.graph_safe:
+                    out.append(type(q).__name__)
+        return sorted(set(out))
 
     def bind(self, tensors: dict[str, torch.Tensor], rt, n_positions: int) -> None:
         for part in self._all_parts():
@@ -67,15 +76,8 @@ class DecoderModel:
         for pe in self.position_encodings.values():
             pe.on_embedding(rt, step, x)
         pending = None
-        sched = self.spec.schedule
-        for idx, e in enumerate(sched):
-            block = self.layers[e.layer]
-            if block.takes_next_norm:
-                # the norm that will take this block's update: the next block's first one
-                nxt = self.layers[sched[idx + 1].layer].first_norm if idx + 1 < len(sched) else None
-                x, pending = block.forward(rt, step, x, pending, idx, next_norm=nxt)
-            else:
-                x, pending = block.forward(rt, step, x, pending, idx)
+        for idx, e in enumerate(self.spec.schedule):
+            x, pending = self.layers[e.layer].forward(rt, step, x, pending, idx)
         if step.n_logit_rows == 0:
             return None
         h = self.final_norm.forward(rt, x, pending, rows=step.logit_rows)

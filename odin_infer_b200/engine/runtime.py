@@ -8,7 +8,7 @@ import os
 import torch
 
 from ..csrc import ops
-from ..parts.base import NormedRows, ResidualAdded
+from ..parts.base import ResidualAdded
 
 
 def choose_k_split(n_tiles: int, k_blocks: int, m: int, n_sms: int = 148, max_split: int = 16) -> int:
@@ -30,25 +30,6 @@ def choose_k_split(n_tiles: int, k_blocks: int, m: int, n_sms: int = 148, max_sp
             best, best_cost = parts, cost
     return best
 
-
-# Products of few tokens can carry out the residual add and the next norm's weighting themselves
-# (`ResidualSink`): two launches fewer per layer, and yet 10 % slower on the 8B shape, because the
-# add+RMSNorm kernel between two products is where the second one fetches its first weights.  Off
-# unless ODIN_FUSE_SINKS=1; the tests run it both ways.
-FUSE_SINKS = os.environ.get("ODIN_FUSE_SINKS", "0") == "1"
-
-
-def fuse_sinks() -> bool:
-    return FUSE_SINKS
-
-
-# Decode steps of few tokens can run as programs of one persistent kernel (csrc/decode_program.cu)
-# instead of a kernel per operation: a layer is then one launch with barriers across the grid
-# between its operations.  Its products stream their weights faster (the requests never stop at
-# an operation's end), but the operations between them no longer overlap the products' ends as
-# co-resident kernels do, and a layer takes 120 us against 95 on the 8B shape.  Off unless
-# ODIN_DECODE_PROGRAM=1; the tests run it both ways.
-DECODE_PROGRAM = os.environ.get("ODIN_DECODE_PROGRAM", "0") == "1"
 
 # Up to this many tokens a product keeps the weights on the wide side of the MMA and the tokens on
 # its N side (one tile of tokens, K split to fill the SMs): with a few hundred tokens a product is still
@@ -81,8 +62,7 @@ def decode_key_splits(n_seqs: int, n_kv_heads: int, longest: int, page: int = 64
     """Into how many parts decode attention cuts a sequence's keys.  A CTA's four warps take a
     page each, so up to about four pages per CTA run side by side and more only lengthen the
     chain; the split that finishes last adds the partials up inside the same kernel.  So: two
-    splits per 8 pages of context, as long as all CTAs together fit the GPU twice (once inside a
-    program's persistent kernel, whose CTAs take the pieces in turns).  Depends on
+    splits per 8 pages of context, as long as all CTAs together fit the GPU twice.  Depends on
     the batch bucket and on the context class, never on which sequences are in the batch."""
     want = 2 * context_class_of(longest, page)
     room = max(1, (ctas_per_sm * n_sms) // max(1, n_seqs * n_kv_heads))
@@ -101,37 +81,22 @@ class Runtime:
         """Kernel libraries the runtime itself may launch, beside those of the parts."""
         if self.dtype != torch.bfloat16:
             return set()
-        groups = {"gemm_tc", "attention_decode", "attention_prefill"}
-        return groups | {"decode_program"} if DECODE_PROGRAM else groups  # else built when first asked for
+        return {"gemm_tc", "attention_decode", "attention_prefill"}
 
     def context_class(self, longest: int) -> int:
         """Contexts of one class launch the same kernels (see decode_key_splits)."""
         return context_class_of(longest)
 
     def run(self, model, batch):
-        """Run one step of `model` eagerly; returns the logits at the wanted rows.  One token per
-        sequence, bfloat16, a model whose parts launch kernels of this package only: the step's
-        operations are recorded and run as programs."""
-        bucket = ops.program_bucket(batch.n_rows) if batch.all_single else 0
-        if DECODE_PROGRAM and self.dtype == torch.bfloat16 and bucket and getattr(model, "kernels_only", False):
-            with ops.program(bucket):
-                return model.forward(self, batch)
+        """Run one step of `model`; returns the logits at the wanted rows."""
         return model.forward(self, batch)
 
     def empty(self, *shape, dtype: torch.dtype | None = None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
 
     # ---- matrix product: out[M, N] = a[M, K] @ w[N, K]^T -----------------
-    def materialize(self, h):
-        """`NormedRows` as ordinary rows (their norm's factor applied); anything else unchanged."""
-        if not isinstance(h, NormedRows):
-            return h
-        out = self.empty(*h.rows.shape)
-        ops.scale_rows(h.rows, h.ssq, h.width, h.eps, out)
-        return out
-
     def linear(self, a, w: torch.Tensor, out_dtype: torch.dtype | None = None,
-               may_split: bool = False, beside_attention: bool = False, sink=None):
+               may_split: bool = False, beside_attention: bool = False, add_to: torch.Tensor | None = None):
         """bfloat16 operands that TMA can read go to the tcgen05 kernel, everything else
         (the 32-bit path, odd widths, tensors stored in 32-bit) to the CUDA-core kernel.
 
@@ -143,46 +108,31 @@ class Runtime:
         fits on the SM beside it and can fetch its pages (or this product its weights) while
         the other still runs.
 
-        a may be `NormedRows` (rows that still lack their norm's factor): a product of few
-        tokens applies the factor to its sums, any other path scales the rows first.
-        sink: a `ResidualSink`; a product of few tokens may then add its result to the
-        residual stream itself and weight it for the sink's norm, and returns `NormedRows`
-        (the norm's output, to be handed to that norm) instead of the update."""
-        rows = a.rows if isinstance(a, NormedRows) else a
-        M, N, K = rows.shape[0], w.shape[0], rows.shape[1]
+        add_to: the 32-bit residual stream [M, N] that the result is meant for; a product of many
+        tokens then adds to it in its epilogue and returns `ResidualAdded()` instead of the update."""
+        M, N, K = a.shape[0], w.shape[0], a.shape[1]
         out_dtype = out_dtype or self.dtype
-        if M > 0 and ops.gemm_tc_supported(rows, w):
-            if M <= WEIGHTS_WIDE_MAX_TOKENS and not (isinstance(a, NormedRows) and M > 128):
+        if M > 0 and ops.gemm_tc_supported(a, w):
+            if M <= WEIGHTS_WIDE_MAX_TOKENS:
                 bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
                 n_split = choose_k_split((N + 127) // 128, (K + 63) // 64, M, self.n_sms) if may_split else 1
                 n_split = ops.gemm_tc_splits(K, n_split)
                 stages = LIGHT_STAGES if beside_attention else 0
-                scale = dict(row_ssq=a.ssq, row_width=a.width, row_eps=a.eps) if isinstance(a, NormedRows) else {}
-                if (sink is not None and fuse_sinks() and M <= 128 and out_dtype == torch.float32 and may_split
-                        and getattr(sink.norm, "weight", None) is not None and sink.norm.weight.numel() == N
-                        and tuple(sink.x.shape) == (M, N) and sink.x.dtype == torch.float32):
-                    scratch = self.empty(n_split, M, N, dtype=torch.float32) if n_split > 1 else self.empty(M, N, dtype=torch.float32)
-                    normed = self.empty(M, N)
-                    ssq = self.empty(M, (N + 127) // 128, dtype=torch.float32)
-                    ops.gemm_tc(rows, w, scratch, 1, bn, n_split, stages,
-                                sink=(sink.x, sink.norm.weight, normed, ssq), **scale)
-                    return NormedRows(normed, ssq, N, sink.norm.eps, sink.norm)
                 if M > 128:
                     # a few hundred tokens: on pairs of SMs, which halves what a CTA fetches per K block
                     n_tiles = (N + 255) // 256
                     n_split = ops.gemm_tc_splits(K, choose_k_split(n_tiles, (K + 63) // 64, M, self.n_sms // 2)
                                                  if may_split else 1)
                     out = self.empty(n_split, M, N, dtype=torch.float32) if n_split > 1 else self.empty(M, N, dtype=out_dtype)
-                    ops.gemm_tc2_wide(rows, w, out, n_split)
+                    ops.gemm_tc2_wide(a, w, out, n_split)
                     return out
-                if n_split > 1 or (may_split and ops.recording()):  # a program's products write 32-bit sums only
+                if n_split > 1:
                     out = self.empty(n_split, M, N, dtype=torch.float32)
-                    ops.gemm_tc(rows, w, out, 1, bn, n_split, stages, **scale)
+                    ops.gemm_tc(a, w, out, 1, bn, n_split, stages)
                     return out
                 out = self.empty(M, N, dtype=out_dtype)
-                ops.gemm_tc(rows, w, out, 1, bn, 1, stages, **scale)
+                ops.gemm_tc(a, w, out, 1, bn, 1, stages)
                 return out
-        a = self.materialize(a)
         if (M > 0 and PAIR_MIN_TOKENS <= M <= WIDE_CHUNKS_MAX_TOKENS and may_split and ops.gemm_tc_supported(a, w)
                 and (N + 255) // 256 < self.n_sms // 2):
             # Some hundred tokens and a weight of few 256-row tiles: tiles of 256 x 256 would leave most pairs
@@ -195,10 +145,10 @@ class Runtime:
             ops.gemm_tc2_wide(a, w, out, n_split)
             return out
         if M > 0 and ops.gemm_tc_supported(a, w):
-            if (M >= PAIR_MIN_TOKENS and N > 128 and sink is not None and out_dtype == torch.float32
-                    and tuple(sink.x.shape) == (M, N) and sink.x.dtype == torch.float32 and sink.x.stride(1) == 1):
+            if (M >= PAIR_MIN_TOKENS and N > 128 and add_to is not None and out_dtype == torch.float32
+                    and tuple(add_to.shape) == (M, N) and add_to.dtype == torch.float32 and add_to.stride(1) == 1):
                 # many tokens: the product's epilogue adds to the residual stream in place
-                ops.gemm_tc2(a, w, sink.x, accumulate=True)
+                ops.gemm_tc2(a, w, add_to, accumulate=True)
                 return ResidualAdded()
             out = self.empty(M, N, dtype=out_dtype)
             if M >= PAIR_MIN_TOKENS and N > 128:
@@ -220,8 +170,6 @@ class Runtime:
         # enough for the pairs of SMs even beside one tile of 256 tokens, and no partial sums are written
         # (measured against the weights-wide kernel + SwiGLU kernel: 8 to 10 % of the step at 129 to 256 tokens).
         fused_from = SWIGLU_FUSED_FROM
-        if M >= fused_from:
-            a = self.materialize(a)
         if M >= fused_from and ops.gemm_tc_supported(a, w_gate_up):
             if M > 128 and ops.gemm_tc2_swiglu_supported(inner):
                 ops.gemm_tc2_swiglu(a, w_gate_up, act)
@@ -243,8 +191,7 @@ class Runtime:
                 and rotary_dim == head_dim and n_kv > 0 and n_q // n_kv <= 16 and write_kv):
             return False
         B = out.shape[0]
-        n_split = decode_key_splits(B, n_kv, step.max_len_after, n_sms=self.n_sms,
-                                    ctas_per_sm=1 if ops.recording() else 2)
+        n_split = decode_key_splits(B, n_kv, step.max_len_after, n_sms=self.n_sms)
         scratch = self.empty(ops.attention_decode_scratch(B, n_q, head_dim, n_split), dtype=torch.float32)
         return ops.attention_decode_fused(qkv, out, n_q, n_kv, head_dim, q_norm, k_norm, eps, cos, sin, rotary_dim,
                                           k_line, v_line, step.tok_pos, step.tok_seq, block_table, window, scratch,

@@ -177,9 +177,20 @@ class StepBatch:
         last = getattr(self, "_last_starts", None)
         if (last is None or not self.all_single or len(entries) != self.n_seqs
                 or any(len(e.tokens) != 1 or e.slot != s for e, s in zip(entries, self.slots))
-                or any(p != q + 1 for p, q in zip(start_positions, last))
-                or (not self.all_rows_wanted and any(e.want != [0] for e in entries))):
+                or any(p != q + 1 for p, q in zip(start_positions, last))):
             return False
+        # which logits are wanted may change from step to step: with every row computed
+        # (a captured graph) only the list of rows to hand back changes; with fixed logit rows the
+        # tables are written anew
+        rows = []
+        for b, e in enumerate(entries):
+            for w in e.want:
+                if w != 0:
+                    raise StepError(f"slot {e.slot}: wanted place {w} is outside its 1 token(s)")
+                rows.append(b)
+        if not self.all_rows_wanted and rows != self.wanted_rows:
+            return False
+        self.wanted_rows = rows
         n = self.n_seqs
         self._h("tok_ids")[:n] = [e.tokens[0] for e in entries]
         self._h("tok_pos")[:n] += 1

@@ -19,7 +19,7 @@ class GQAttention(Mixer):
     The three projection matrices are fused into one at load time.
     """
 
-    kernels_only = True
+    graph_safe = True
 
     def __init__(self, width: int, n_q_heads: int, n_kv_heads: int, head_dim: int, names: dict,
                  position_encoding: str | None = None, qk_norm: bool = True, eps: float = 1e-6,
@@ -69,9 +69,9 @@ class GQAttention(Mixer):
     def kernel_groups(self):
         return {"head_prep", "attention_plain", "gemm_plain"}
 
-    takes_sinks = True
+    takes_residual = True
 
-    def forward(self, rt, step, h, entry, sink=None):
+    def forward(self, rt, step, h, entry, residual=None):
         T = h.shape[0]
         qkv = rt.linear(h, self.w_qkv, may_split=True, beside_attention=True)
         k_line, v_line, block_table = step.kv(entry)
@@ -84,7 +84,7 @@ class GQAttention(Mixer):
                 step, qkv, o, self.n_q, self.n_kv, self.hd, self.q_norm if self.qk_norm else None,
                 self.k_norm if self.qk_norm else None, self.eps, cos, sin, rot_dim, k_line, v_line, block_table,
                 self.window, writes):
-            return rt.linear(o, self.w_o, out_dtype=torch.float32, may_split=True, beside_attention=True, sink=sink)
+            return rt.linear(o, self.w_o, out_dtype=torch.float32, may_split=True, beside_attention=True, add_to=residual)
         # a product of few tokens may come back as partial sums: they are added here
         q_out = rt.empty(T, self.n_q * self.hd) if qkv.dim() == 3 else None
         q = ops.head_prep(qkv, self.n_q, 0 if self.kv_shared else self.n_kv, self.hd,
@@ -92,4 +92,4 @@ class GQAttention(Mixer):
                           cos, sin, rot_dim, step.tok_pos, step.tok_seq, block_table, k_line, v_line,
                           write_kv=writes, q_out=q_out)
         rt.attention(step, q, o, self.n_q, self.n_kv, self.hd, k_line, v_line, block_table, self.window)
-        return rt.linear(o, self.w_o, out_dtype=torch.float32, may_split=True, beside_attention=True, sink=sink)
+        return rt.linear(o, self.w_o, out_dtype=torch.float32, may_split=True, beside_attention=True, add_to=residual)

@@ -11,6 +11,15 @@ Life of a part:
   3. `bind(tensors, rt)`                 it takes them (and may fuse or drop them);
   4. `forward(...)`                      once per step, enqueueing kernels on the
                                          current stream; no host synchronisation.
+
+A part that says `graph_safe = True` promises that its `forward` may be captured in a
+CUDA graph once and replayed for other steps of the same shape: it reads sequence
+numbers, slots, positions and page tables from the step's DEVICE tensors only (the host
+copies change between replays), sizes its launches by what holds for every replay
+(`step.n_rows` token rows, `step.n_seq_cap` sequences, some of them padding), skips rows
+of sequence -1, keeps nothing on the host from one call to the next, and calls nothing
+that synchronises or allocates outside torch's stream-ordered allocator.  The default is
+False: a model with one such part runs every step eagerly, which is always right.
 """
 from __future__ import annotations
 
@@ -55,61 +64,25 @@ class Part:
     def bind(self, tensors: dict[str, torch.Tensor], rt) -> None:
         pass
 
-    # True for a part whose forward launches kernels of this package only (through `ops` and the
-    # runtime) and calls nothing that would put other work on the stream: only then may the
-    # runtime record a decode step's operations and run them as programs of one persistent
-    # kernel, where the order of launches is no longer the order of execution for anything else.
-    kernels_only = False
+    # May this part's forward be captured in a CUDA graph and replayed (see the module's text)?
+    graph_safe = False
 
     def kernel_groups(self) -> set[str]:
         """Kernel libraries this part launches (compiled before the first step)."""
         return set()
 
 
-@dataclasses.dataclass
-class NormedRows:
-    """Rows that a norm has weighted but not yet scaled: row j stands for
-    rows[j] / sqrt(sum(ssq[j]) / width + eps).  What a product with a `ResidualSink` hands to
-    the norm it was made for; a product that takes it as input applies the factor to its sums
-    (`Runtime.linear`), anything else asks the runtime to `materialize` it."""
-    rows: torch.Tensor   # [n, width] in the runtime's element type
-    ssq: torch.Tensor    # [n, parts] 32-bit shares of the rows' sums of squares
-    width: int
-    eps: float
-    norm: Any            # the norm part these rows are the output of
-
-    @property
-    def shape(self):
-        return self.rows.shape
-
-
-@dataclasses.dataclass
-class ResidualSink:
-    """Where a part's last product may put its result itself: added to the residual stream x,
-    and on through `norm` (see `Runtime.linear`).  A part that is handed a sink and cannot use
-    it ignores it and returns its update as usual."""
-    x: torch.Tensor
-    norm: Any
-
-
 class ResidualAdded:
-    """What a product returns that has added its result to the sink's residual stream already:
-    nothing is left to add, the norm still has to be taken."""
+    """The answer of `Runtime.linear(..., add_to=x)` when the product has added its result to
+    the residual stream x itself (in its epilogue): nothing is left to add.  A block turns it
+    into "no pending update" before the next norm sees it."""
 
 
 class Norm(Part):
-    def sink(self, x: torch.Tensor) -> ResidualSink | None:
-        """A sink through which the product before this norm may carry out the norm's add and
-        weighting itself, or None if this norm cannot finish such rows."""
-        return None
-
-
-    def forward(self, rt, x: torch.Tensor, delta, rows: torch.Tensor | None = None, unscaled_ok: bool = False):
+    def forward(self, rt, x: torch.Tensor, delta, rows: torch.Tensor | None = None):
         """x: the 32-bit residual stream [n, width], updated in place by `delta`
         (None, [n, width] or [splits, n, width]); returns the normalised rows in
-        the runtime's element type.  rows: gather these rows only (x untouched).
-        delta may be the `NormedRows` that a product made through this norm's sink (x is then
-        up to date already); they are returned as they are if `unscaled_ok`, else scaled."""
+        the runtime's element type.  rows: gather these rows only (x untouched)."""
         raise NotImplementedError
 
 
@@ -135,9 +108,10 @@ class Mixer(Part):
         """Bytes of fixed-size state this mixer keeps per sequence."""
         return 0
 
-    # A mixer or feed-forward that sets this takes `NormedRows` as h (it passes them to
-    # `Runtime.linear` / `gated_linear` only) and a keyword `sink=` for its last product.
-    takes_sinks = False
+    # A mixer or feed-forward that sets this also takes a keyword `residual=` (the 32-bit
+    # residual stream its update is meant for) and may pass it to its last product as
+    # `Runtime.linear(..., add_to=residual)`, returning whatever that returns.
+    takes_residual = False
 
     def forward(self, rt, step, h: torch.Tensor, entry: int) -> torch.Tensor:
         """h: [T, width] normalised input.  entry: index of the schedule entry being run
@@ -147,26 +121,17 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    takes_sinks = False  # as for Mixer
+    takes_residual = False  # as for Mixer
 
     def forward(self, rt, step, h: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
 
 class Block(Part):
-    # a block that sets this takes `next_norm=` (the norm that will consume its pending update,
-    # or None) and may hand that norm's sink to its last part
-    takes_next_norm = False
-
     def forward(self, rt, step, x: torch.Tensor, pending, entry: int):
-        """x: residual stream (in place); pending: an update not yet added to it (or the
-        `NormedRows` of this block's first norm).  Returns (x, pending)."""
+        """x: residual stream (in place); pending: an update not yet added to it (None, [n, width]
+        or [splits, n, width]).  Returns (x, pending)."""
         raise NotImplementedError
-
-    @property
-    def first_norm(self):
-        """The norm that takes this block's input, if the block before may feed it through a sink."""
-        return None
 
     @property
     def mixer(self) -> Mixer:

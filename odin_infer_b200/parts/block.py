@@ -1,7 +1,7 @@
 """How a layer's parts are arranged."""
 from __future__ import annotations
 
-from .base import Block, NormedRows, PartSpec, build_part, register_part
+from .base import Block, PartSpec, ResidualAdded, build_part, register_part
 
 
 @register_part("block", "prenorm")
@@ -34,31 +34,14 @@ class PreNormBlock(Block):
     def kernel_groups(self):
         return set().union(*(p.kernel_groups() for p in self._parts()))
 
-    takes_next_norm = True
-
     @property
-    def kernels_only(self):
-        return all(p.kernels_only for p in self._parts())
+    def graph_safe(self):
+        return all(p.graph_safe for p in self._parts())
 
-    @property
-    def first_norm(self):
-        return self.norm_mixer
-
-    def forward(self, rt, step, x, pending, entry, next_norm=None):
-        """A part that takes sinks may carry out the add and the weighting of the norm after it
-        inside its last product (few tokens); what it returns then is that norm's output."""
+    def forward(self, rt, step, x, pending, entry):
         mixer, ffn = self._mixer, self.ffn
-        # rows that came through a sink may stay unscaled for a part that takes them so
-        late = {"unscaled_ok": True} if isinstance(pending, NormedRows) and mixer.takes_sinks else {}
-        h = self.norm_mixer.forward(rt, x, pending, **late)
-        if mixer.takes_sinks:
-            delta = mixer.forward(rt, step, h, entry, sink=self.norm_ffn.sink(x))
-        else:
-            delta = mixer.forward(rt, step, h, entry)
-        late = {"unscaled_ok": True} if isinstance(delta, NormedRows) and ffn.takes_sinks else {}
-        h = self.norm_ffn.forward(rt, x, delta, **late)
-        if ffn.takes_sinks:
-            delta = ffn.forward(rt, step, h, sink=next_norm.sink(x) if next_norm is not None else None)
-        else:
-            delta = ffn.forward(rt, step, h)
-        return x, delta
+        h = self.norm_mixer.forward(rt, x, pending)
+        delta = mixer.forward(rt, step, h, entry, residual=x) if mixer.takes_residual else mixer.forward(rt, step, h, entry)
+        h = self.norm_ffn.forward(rt, x, None if isinstance(delta, ResidualAdded) else delta)
+        delta = ffn.forward(rt, step, h, residual=x) if ffn.takes_residual else ffn.forward(rt, step, h)
+        return x, (None if isinstance(delta, ResidualAdded) else delta)

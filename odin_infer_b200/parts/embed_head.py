@@ -11,7 +11,7 @@ from .base import Embedding, Head, ParamSpec, register_part
 class TokenEmbedding(Embedding):
     """x = E[token], no scaling (infer/forward.odin:43)."""
 
-    kernels_only = True
+    graph_safe = True
 
     def __init__(self, vocab_size: int, width: int, weight: str):
         self.vocab_size, self.width, self.weight_name = vocab_size, width, weight
@@ -37,7 +37,7 @@ class LinearHead(Head):
     """logits = W h, 32-bit out; W is its own tensor or, when `tied_to` is given and
     the folder has no such tensor, the embedding table (infer/model.odin:150-158)."""
 
-    kernels_only = True
+    graph_safe = True
 
     def __init__(self, vocab_size: int, width: int, weight: str, tied_to: str | None = None):
         self.vocab_size, self.width, self.weight_name, self.tied_to = vocab_size, width, weight, tied_to

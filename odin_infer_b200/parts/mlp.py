@@ -11,7 +11,7 @@ class SwiGLU(FeedForward):
     """down( silu(gate(x)) * up(x) ), no bias (infer/forward.odin:125-135).  The gate
     and up matrices are fused into one at load time."""
 
-    kernels_only = True
+    graph_safe = True
 
     def __init__(self, width: int, inner: int, names: dict):
         self.width, self.inner, self.names = width, inner, dict(names)
@@ -33,8 +33,8 @@ class SwiGLU(FeedForward):
     def kernel_groups(self):
         return {"elementwise", "gemm_plain"}
 
-    takes_sinks = True
+    takes_residual = True
 
-    def forward(self, rt, step, h, sink=None):
+    def forward(self, rt, step, h, residual=None):
         act = rt.gated_linear(h, self.w_gate_up, self.inner)
-        return rt.linear(act, self.w_down, out_dtype=torch.float32, may_split=True, sink=sink)
+        return rt.linear(act, self.w_down, out_dtype=torch.float32, may_split=True, add_to=residual)

@@ -4,14 +4,14 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
-from .base import Norm, NormedRows, ParamSpec, ResidualAdded, ResidualSink, register_part
+from .base import Norm, ParamSpec, register_part
 
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Norm):
     """o = w * (x / sqrt(mean(x^2) + eps)), in 32-bit (infer/ops.odin:7-19)."""
 
-    kernels_only = True
+    graph_safe = True
 
     def __init__(self, width: int, eps: float, weight: str):
         self.width, self.eps, self.weight_name = width, float(eps), weight
@@ -26,16 +26,7 @@ class RMSNorm(Norm):
     def kernel_groups(self):
         return {"elementwise"}
 
-    def sink(self, x):
-        return ResidualSink(x, self)
-
-    def forward(self, rt, x, delta, rows=None, unscaled_ok=False):
-        if isinstance(delta, NormedRows):
-            if delta.norm is not self or rows is not None:
-                raise ValueError("rows made through another norm's sink cannot be finished by this one")
-            return delta if unscaled_ok else rt.materialize(delta)
-        if isinstance(delta, ResidualAdded):
-            delta = None
+    def forward(self, rt, x, delta, rows=None):
         n = x.shape[0] if rows is None else rows.numel()
         out = rt.empty(n, self.width)
         ops.add_rmsnorm(x, delta, self.weight, self.eps, out, rows)

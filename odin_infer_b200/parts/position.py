@@ -14,7 +14,7 @@ class RotaryEncoding(PositionEncoding):
     32-bit as the reference does (infer/forward.odin:67-70); cos and sin of that
     angle are tabulated on the host, so every kernel reads the same values."""
 
-    kernels_only = True
+    graph_safe = True
 
     def __init__(self, rotary_dim: int, theta: float):
         if rotary_dim % 2:
@@ -39,4 +39,4 @@ class RotaryEncoding(PositionEncoding):
 class NoEncoding(PositionEncoding):
     """No position information beyond the causal mask."""
 
-    kernels_only = True
+    graph_safe = True

@@ -236,55 +236,6 @@ def test_pair_kernel_swiglu(case):
     close(out, g * torch.sigmoid(g) * u, 8e-3, "swiglu")
 
 
-@pytest.mark.parametrize("case", [(8, 4096, 4096, 16, 4), (1, 384, 512, 16, 2), (16, 1000, 1032, 16, 3), (40, 4096, 12288, 64, 9),
-                                  (128, 640, 256, 128, 1), (5, 200, 128, 16, 1)])
-def test_sink_and_row_factor_against_the_separate_kernels(case):
-    """A product of few tokens that goes on into the residual stream and the following norm inside
-    its own kernel, and the next product that applies the norm's factor to its sums: against the
-    product, the add+RMSNorm kernel and the plain product run one after the other."""
-    from odin_infer_b200.csrc import ops
-    M, N, K, bn, n_split = case
-    torch.manual_seed(N + K + M)
-    a = torch.randn(M, K, device=DEV).bfloat16()
-    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).bfloat16()
-    x0 = torch.randn(M, N, device=DEV)
-    norm_w = (1 + 0.2 * torch.randn(N, device=DEV)).bfloat16()
-    eps = 1e-5
-    parts = ops.gemm_tc_splits(K, n_split)
-    shape = (parts, M, N) if parts > 1 else (M, N)
-    # the separate kernels
-    delta = torch.empty(shape, device=DEV, dtype=torch.float32)
-    ops.gemm_tc(a, w, delta, 1, bn, n_split)
-    x_ref = x0.clone()
-    h_ref = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
-    ops.add_rmsnorm(x_ref, delta, norm_w, eps, h_ref)
-    # the sink
-    x = x0.clone()
-    scratch = torch.empty(shape, device=DEV, dtype=torch.float32)
-    normed = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
-    ssq = torch.full((M, (N + 127) // 128), float("nan"), device=DEV)
-    for _ in range(2):  # twice: the counters are back at zero after a launch
-        x.copy_(x0)
-        ops.gemm_tc(a, w, scratch, 1, bn, n_split, sink=(x, norm_w, normed, ssq))
-    ops.gemm_tc_check()
-    assert torch.equal(x, x_ref), "the residual stream: x, then the parts in order, as the norm kernel adds them"
-    close(ssq.sum(1), (x_ref.double() ** 2).sum(1), 1e-5, "sums of squares")
-    factor = 1.0 / torch.sqrt(ssq.double().sum(1) / N + eps)
-    close(normed.double() * factor[:, None], h_ref, 1.2e-2, "normed rows with their factor")
-    # the next product with the factor applied to its sums
-    N2 = 264
-    w2 = (torch.randn(N2, N, device=DEV) / math.sqrt(N)).bfloat16()
-    if N % 8 == 0:
-        ref2 = torch.empty(M, N2, device=DEV, dtype=torch.float32)
-        ops.gemm_tc(h_ref, w2, ref2, 1, bn)
-        for n2 in (1, 2):
-            p2 = ops.gemm_tc_splits(N, n2)
-            got2 = torch.empty((p2, M, N2) if p2 > 1 else (M, N2), device=DEV, dtype=torch.float32)
-            ops.gemm_tc(normed, w2, got2, 1, bn, n2, row_ssq=ssq, row_width=N, row_eps=eps)
-            ops.gemm_tc_check()
-            close(got2.sum(0) if p2 > 1 else got2, ref2, 1.2e-2, "next product")
-
-
 @pytest.mark.parametrize("case", [(256, 256, 64), (300, 1000, 1032), (2048, 4096, 512)])
 def test_pair_kernel_adds_in_place(case):
     """C += A W^T in the epilogue: exactly the separate product added to C."""

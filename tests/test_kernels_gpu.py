@@ -526,8 +526,7 @@ def test_attention_decode_window_and_far_key():
 
 @pytest.mark.parametrize("geom", [(4, 2, 64), (8, 8, 64), (4, 1, 128), (6, 2, 128), (32, 8, 128)])
 @pytest.mark.parametrize("window", [0, 50])
-@pytest.mark.parametrize("variant", ["tc", "mma"])
-def test_attention_prefill_against_plain_kernel_and_reference(geom, window, variant):
+def test_attention_prefill_against_plain_kernel_and_reference(geom, window):
     """The flash kernel: prompts of unequal lengths that start at 0 or continue from a
     non-zero position, pages scrambled, lengths around the tile and page sizes; unwritten
     cache slots hold NaN, which must never reach a result."""
@@ -555,7 +554,7 @@ def test_attention_prefill_against_plain_kernel_and_reference(geom, window, vari
     tok_seq = torch.tensor([s for s, (a, b) in enumerate(parts) for _ in range(b)], dtype=torch.int32, device=DEV)
     out = torch.empty(T, n_q * hd, device=DEV, dtype=torch.bfloat16)
     ops.attention_prefill(q, out, B, max(b for _, b in parts), n_q, n_kv, hd, k_cache, v_cache, seq_start,
-                          seq_len_after, bt, window, variant=variant)
+                          seq_len_after, bt, window)
     ops.attention_prefill_check()
     assert not torch.isnan(out.float()).any()
     plain = torch.empty_like(out)
@@ -579,8 +578,7 @@ def test_attention_prefill_against_plain_kernel_and_reference(geom, window, vari
         r += b
 
 
-@pytest.mark.parametrize("variant", ["tc", "mma"])
-def test_attention_prefill_long_prompt_far_key(variant):
+def test_attention_prefill_long_prompt_far_key():
     """2,048 tokens: one key early in the prompt is made to dominate every later query."""
     from odin_infer_b200.csrc import ops
     n_q, n_kv, hd, n = 4, 2, 128, 2048
@@ -601,7 +599,7 @@ def test_attention_prefill_long_prompt_far_key(variant):
     seq_start = torch.tensor([0, n], dtype=torch.int32, device=DEV)
     seq_len_after = torch.tensor([n], dtype=torch.int32, device=DEV)
     ops.attention_prefill(q.reshape(n, -1).bfloat16(), out, 1, n, n_q, n_kv, hd, k_cache, v_cache, seq_start,
-                          seq_len_after, bt, 0, variant=variant)
+                          seq_len_after, bt, 0)
     ops.attention_prefill_check()
     got = out.float().view(n, n_q, hd)
     for t in (far, far + 1, 777, n - 1):

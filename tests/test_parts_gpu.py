@@ -234,6 +234,58 @@ def register_toy():
                 state[slot, self.width] = cnt[-1]
             return out
 
+    # ---- the same three parts written to the contract of `graph_safe`: indices from the step's
+    # device tensors only, launches sized by the padded row count, rows of sequence -1 skipped
+    @register_part("feed_forward", "toy_top1_experts_dense")
+    class Top1ExpertsDense(Top1Experts):
+        """Every expert runs on every row and the chosen one's result is kept: no shape depends on the data."""
+        graph_safe = True
+
+        def forward(self, rt, step, h):
+            hf = h.float()
+            choice = torch.argmax(hf @ self.router.float().t(), dim=1)
+            out = torch.zeros(h.shape[0], self.width, dtype=torch.float32, device=h.device)
+            for e, (g, u, d) in enumerate(self.w):
+                a = torch.nn.functional.silu(hf @ g.float().t()) * (hf @ u.float().t())
+                out = torch.where((choice == e)[:, None], a.to(h.dtype).float() @ d.float().t(), out)
+            return out
+
+    @register_part("position_encoding", "toy_learned_by_rows")
+    class LearnedPositionsByRows(LearnedPositions):
+        graph_safe = True
+
+        def on_embedding(self, rt, step, x):
+            n = x.shape[0]
+            real = (step.tok_seq[:n] >= 0)[:, None]
+            x += torch.where(real, self.table[step.tok_pos[:n].long()].float(), torch.zeros((), device=x.device))
+
+    @register_part("mixer", "toy_running_mean_by_rows")
+    class RunningMeanByRows(RunningMean):
+        """The same running mean with every index taken from the device: a segmented cumulative sum
+        over the rows (sum up to a row minus the sum before its sequence's first row), the state
+        gathered by `seq_slots`, and written back by the last row of each sequence as an increment
+        (rows that are not the last, and padding rows, add zero)."""
+        graph_safe = True
+
+        def forward(self, rt, step, h, entry):
+            state = step.state(entry).view(torch.float32)      # [slots, width + 1]
+            n, w = h.shape[0], self.width
+            seq = step.tok_seq[:n].long()
+            real = seq >= 0
+            seq0 = seq.clamp(min=0)
+            hf = torch.where(real[:, None], h.float(), torch.zeros((), device=h.device))
+            cs = torch.cumsum(hf, 0)
+            first = step.seq_start.long()[seq0]                 # first row of the row's sequence
+            before = torch.where((first > 0)[:, None], cs[(first - 1).clamp(min=0)], torch.zeros((), device=h.device))
+            old = state[step.seq_slots.long()[seq0]]            # [n, width + 1]
+            sums = old[:, :w] + (cs - before)
+            cnt = old[:, w] + (torch.arange(n, device=h.device) - first + 1).float()
+            out = torch.where(real[:, None], (sums / cnt[:, None]) @ self.w.float().t(), torch.zeros((), device=h.device))
+            last = real & (torch.arange(1, n + 1, device=h.device) == step.seq_start.long()[seq0 + 1])
+            inc = torch.cat([sums, cnt[:, None]], 1) - old
+            state.index_add_(0, step.seq_slots.long()[seq0], torch.where(last[:, None], inc, torch.zeros((), device=h.device)))
+            return out
+
     @dataclasses.dataclass(frozen=True)
     class ToyConfig(ModelConfig):
         width: int = 0
@@ -245,6 +297,7 @@ def register_toy():
         window: int = 0
         experts: int = 0
         max_positions: int = 0
+        by_rows: int = 0     # 1: the parts written for CUDA graphs
         eps: float = 1e-6
         theta: float = 1e4
 
@@ -253,6 +306,7 @@ def register_toy():
             r = KeyReader(raw, where)
             vals = {k: r.get(k, int) for k in ("width", "vocab", "heads", "kv_heads", "head_dim", "inner", "window",
                                                "experts", "max_positions")}
+            vals["by_rows"] = r.get("by_rows", int, 0)
             r.finish()
             return cls(architecture=raw["architectures"][0], **vals)
 
@@ -272,18 +326,19 @@ def register_toy():
             ffn = PartSpec("swiglu", dict(width=cfg.width, inner=cfg.inner,
                                           names={k: f"l{l}.ffn.{k}" for k in ("gate", "up", "down")}))
             if routed:
-                ffn = PartSpec("toy_top1_experts", dict(width=cfg.width, inner=cfg.inner, experts=cfg.experts, prefix=f"l{l}.moe"))
+                ffn = PartSpec("toy_top1_experts_dense" if cfg.by_rows else "toy_top1_experts", dict(width=cfg.width, inner=cfg.inner, experts=cfg.experts, prefix=f"l{l}.moe"))
             n1 = PartSpec("rmsnorm", dict(width=cfg.width, eps=cfg.eps, weight=f"l{l}.n1"))
             n2 = PartSpec("rmsnorm", dict(width=cfg.width, eps=cfg.eps, weight=f"l{l}.n2"))
             return PartSpec("prenorm", dict(mixer=mixer, feed_forward=ffn, norm_mixer=n1, norm_feed_forward=n2))
         layers = (block(0, attn("l0.att")), block(1, attn("l1.att", window=cfg.window)),
                   block(2, attn("l2.att", shared=True)),
-                  block(3, PartSpec("toy_running_mean", dict(width=cfg.width, weight="l3.mix")), routed=True))
+                  block(3, PartSpec("toy_running_mean_by_rows" if cfg.by_rows else "toy_running_mean",
+                                    dict(width=cfg.width, weight="l3.mix")), routed=True))
         return ModelSpec(
             width=cfg.width, vocab_size=cfg.vocab,
             embedding=PartSpec("token_table", dict(vocab_size=cfg.vocab, width=cfg.width, weight="emb")),
             position_encodings={"rope": PartSpec("rope", dict(rotary_dim=cfg.head_dim, theta=cfg.theta)),
-                                "learned": PartSpec("toy_learned", dict(width=cfg.width, max_positions=cfg.max_positions,
+                                "learned": PartSpec("toy_learned_by_rows" if cfg.by_rows else "toy_learned", dict(width=cfg.width, max_positions=cfg.max_positions,
                                                                         weight="pos"))},
             layers=layers,
             # layer 0 runs twice (each run keeps its own cache); layer 2 reads the cache of the first run
@@ -349,18 +404,25 @@ def toy_plain(w, cfg, tokens):
     return P.linear(P.rmsnorm(x, w["final"], eps), w["emb"]), (top2[:, 0] - top2[:, 1]) / router.abs().max()
 
 
+@pytest.mark.parametrize("by_rows", [0, 1])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_toy_architecture_registers_builds_and_steps(tmp_path, dtype):
+def test_toy_architecture_registers_builds_and_steps(tmp_path, dtype, by_rows):
+    """With the engine's default options.  by_rows = 0: the parts written the natural way (host
+    copies of slots and row ranges, shapes that follow the data): the engine runs such a model
+    eagerly.  by_rows = 1: the same parts written to the contract of `graph_safe`: the bfloat16
+    steps are captured and replayed, also across a page border and a border of context classes."""
     register_toy()
     from odin_infer_b200 import Engine, Engine_Opts
     from odin_infer_b200.config import config_from_dict
     from odin_infer_b200.engine.trace import replay
     from odin_infer_b200.weights import write_random_model
-    folder = write_random_model(str(tmp_path / "toy"), config_from_dict(TOY), seed=21)
+    raw = dict(TOY, by_rows=by_rows, max_positions=640 if by_rows else 256)
+    folder = write_random_model(str(tmp_path / "toy"), config_from_dict(raw), seed=21)
     _, w = P.read_model_folder(folder, torch.float64)
     assert "l2.att.k" not in w and "head" not in w and "l3.mix" in w      # shared kv: no k/v; tied head
-    assert "l3.moe.e2.down" in w and "l3.ffn.gate" not in w and tuple(w["pos"].shape) == (256, 64)
-    reqs = {f"r{i}": tiny.random_tokens(n, TOY["vocab"], 50 + i) for i, n in enumerate([3, 70, 150, 41])}
+    assert "l3.moe.e2.down" in w and "l3.ffn.gate" not in w and tuple(w["pos"].shape) == (raw["max_positions"], 64)
+    lengths = [3, 70, 150, 41] + ([530] if by_rows else [])              # 530: from context class 1 into class 2
+    reqs = {f"r{i}": tiny.random_tokens(n, TOY["vocab"], 50 + i) for i, n in enumerate(lengths)}
     refs, leads = {}, {}
     for rid, toks in reqs.items():
         logits, lead = toy_plain(w, TOY, toks)
@@ -368,19 +430,22 @@ def test_toy_architecture_registers_builds_and_steps(tmp_path, dtype):
     assert sum(int((l > 0.05).sum()) for l in leads.values()) > 150, "most positions have a clear choice of expert"
     tol = tiny.TOL[dtype]
     for what, recs in (("whole", traces.whole(reqs)), ("tail", traces.tail_one_by_one(reqs, 32)),
-                       ("batches", traces.batches(reqs, 2))):
+                       ("batches", traces.batches(reqs, 2)), ("joining", traces.joining(reqs, 3))):
         n = traces.max_live_tokens(recs)
-        e = Engine.load(folder, Engine_Opts(max_ctx=n, max_tokens=n, dtype=dtype, verbose=False, cuda_graphs=False))
+        e = Engine.load(folder, Engine_Opts(max_ctx=n, max_tokens=n, dtype=dtype, verbose=False))
         assert len(e.cache.groups) == 2                     # all keys / a window of them: storage of their own
         assert e.cache.line_of[3] == e.cache.line_of[0]     # the reading entry has no line of its own
         assert e.cache.line_of[2] != e.cache.line_of[0]     # the second run of layer 0 has
         assert e.cache.state_bytes_per_slot >= 4 * 65
+        assert (e.graphs is not None) == (bool(by_rows) and dtype == "bfloat16")
         got = traces.collect(recs, replay(e, recs))
         e.cache.check()
+        if e.graphs is not None:
+            assert len(e.graphs._graphs) >= (1 if what == "whole" else 2), "steps were captured and replayed"
         for rid, ref in refs.items():
             for pos in range(ref.shape[0]):
                 if leads[rid][pos] <= 0.05:  # a near tie between experts: rounding may decide it the other way
                     continue
                 err = tiny.rel_err(got[rid][pos], ref[pos])
-                assert err <= tol, f"toy {what} {dtype}: request {rid} first differs at position {pos}: {err:.3e}"
+                assert err <= tol, f"toy {what} {dtype} by_rows={by_rows}: request {rid} first differs at position {pos}: {err:.3e}"
         e.destroy()

@@ -37,16 +37,16 @@ def requests_and_refs(folders):
     return out
 
 
-def run(folder, dtype, recs):
+def run(folder, dtype, recs, graphs=True, collect=traces.collect):
     from odin_infer_b200 import Engine, Engine_Opts
     from odin_infer_b200.engine.trace import replay
     n = traces.max_live_tokens(recs)
-    engine = Engine.load(folder, Engine_Opts(max_ctx=n, max_tokens=n, dtype=dtype, verbose=False))
+    engine = Engine.load(folder, Engine_Opts(max_ctx=n, max_tokens=n, dtype=dtype, verbose=False, cuda_graphs=graphs))
     try:
         results = replay(engine, recs)
         engine.cache.check()
         assert all(g.pool.n_held == 0 for g in engine.cache.groups.values())
-        return traces.collect(recs, results)
+        return collect(recs, results)
     finally:
         engine.destroy()
 
@@ -76,26 +76,6 @@ def test_last_32_one_by_one(folders, requests_and_refs, name, dtype):
     check(run(folders[name], dtype, traces.tail_one_by_one(reqs, 32)), refs, dtype, "last32")
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
-def test_last_32_one_by_one_with_sinks(folders, requests_and_refs, name, monkeypatch):
-    """The same with the products of few tokens adding to the residual stream and weighting for the
-    next norm themselves (off by default): the decoded tokens go through that path."""
-    from odin_infer_b200.engine import runtime
-    monkeypatch.setattr(runtime, "FUSE_SINKS", True)
-    reqs, refs = requests_and_refs[name]
-    check(run(folders[name], "bfloat16", traces.tail_one_by_one(reqs, 32)), refs, "bfloat16", "sinks")
-
-
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
-def test_last_32_one_by_one_as_programs(folders, requests_and_refs, name, monkeypatch):
-    """The same with each decode step run as programs of one persistent kernel (off by default)."""
-    from odin_infer_b200.engine import runtime
-    monkeypatch.setattr(runtime, "DECODE_PROGRAM", True)
-    reqs, refs = requests_and_refs[name]
-    check(run(folders[name], "bfloat16", traces.tail_one_by_one(reqs, 32)), refs, "bfloat16", "programs")
-    check(run(folders[name], "bfloat16", traces.batches(reqs, 3)), refs, "bfloat16", "programs, batches of 3")
-
-
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_unequal_batches_slots_reused(folders, requests_and_refs, name, dtype):
@@ -103,6 +83,40 @@ def test_unequal_batches_slots_reused(folders, requests_and_refs, name, dtype):
     check(run(folders[name], dtype, traces.batches(reqs, 3)), refs, dtype, "batches of 3")
     check(run(folders[name], dtype, traces.batches(reqs, 2, first_part=lambda n: max(1, n - 5))), refs, dtype,
           "batches of 2")
+
+
+@pytest.mark.parametrize("graphs", [True, False])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "D", "E"])
+def test_want_lists_that_change_from_step_to_step(folders, requests_and_refs, name, dtype, graphs):
+    """One-token steps whose entries want their logits in some steps and not in others (a step may
+    want nothing): exactly the wanted places come back, each equal to the plain implementation's."""
+    reqs, refs = requests_and_refs[name]
+    recs = traces.one_by_one_sparse_wants(reqs, 3)
+    got = run(folders[name], dtype, recs, graphs, traces.collect_places)
+    asked = {rid: set() for rid in reqs}
+    seen = {rid: 0 for rid in reqs}
+    for rec in recs:
+        for e in rec["entries"]:
+            asked[e["id"]] |= {seen[e["id"]] + w for w in e["want"]}
+            seen[e["id"]] += len(e["tokens"])
+    for rid, ref in refs.items():
+        assert set(got.get(rid, {})) == asked[rid], (rid, sorted(got.get(rid, {})), sorted(asked[rid]))
+        assert len(ref) - 1 in asked[rid]
+        for pos, row in got[rid].items():
+            err = tiny.rel_err(row, ref[pos])
+            assert err <= tiny.TOL[dtype], f"sparse wants {dtype}: request {rid} position {pos}: {err:.3e}"
+
+
+@pytest.mark.parametrize("graphs", [True, False])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "D", "E"])
+def test_requests_join_a_running_batch(folders, requests_and_refs, name, dtype, graphs):
+    """Steps that mix one-token continuations with whole prompts and pieces of prompts; ends free the
+    slots and pages that the joiners take."""
+    reqs, refs = requests_and_refs[name]
+    check(run(folders[name], dtype, traces.joining(reqs, 3), graphs), refs, dtype, "joining, 3 wide")
+    check(run(folders[name], dtype, traces.joining(reqs, 2, tail=20), graphs), refs, dtype, "joining, 2 wide")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

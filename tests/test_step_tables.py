@@ -74,3 +74,57 @@ def test_decode_steps_in_place_equal_tables_written_anew(window):
         if step == 70:                            # a sequence leaves: the next fill is not the usual step
             m.give_back_slot(slots.pop(1))
     m.check()
+
+
+def test_wanted_rows_follow_each_steps_want_lists():
+    """A batch that is refilled in place (a captured decode graph) hands back the rows that THIS
+    step's entries want: want lists may change from one one-token step to the next."""
+    m = manager()
+    slots = [m.take_slot() for _ in range(3)]
+    for s in slots:
+        m.extend(s, 4)
+        m.after_step(s)
+    wants = [([0], [0], [0]), ([0], [], [0]), ([], [], []), ([], [0], []), ([0], [0], [0]), ([], [], [0, 0])]
+    graph_like = None
+    for ws in wants:
+        entries = [StepEntry(s, [7], list(w)) for s, w in zip(slots, ws)]
+        starts = [m.extend(s, 1) for s in slots]
+        if graph_like is None:
+            graph_like = StepBatch(m, entries, starts, "cpu", pad_rows_to=4, pad_seqs_to=4, all_rows_wanted=True)
+        else:
+            graph_like.fill(entries, starts)
+        anew = StepBatch(m, entries, starts, "cpu")
+        assert graph_like.wanted_rows == anew.wanted_rows == [b for b, w in enumerate(ws) for _ in w]
+        for s in slots:
+            m.after_step(s)
+    entries = [StepEntry(s, [7], [0]) for s in slots]
+    entries[1].want = [1]
+    starts = [m.extend(s, 1) for s in slots]
+    with pytest.raises(StepError, match="outside"):
+        graph_like.fill(entries, starts)
+
+
+def test_fixed_logit_rows_are_rewritten_when_the_wants_move():
+    """Without `all_rows_wanted` the logit rows are part of the tables: a one-token step whose
+    wants differ from the step before is written anew, or refused if the count changed."""
+    m = manager()
+    slots = [m.take_slot() for _ in range(2)]
+    for s in slots:
+        m.extend(s, 2)
+        m.after_step(s)
+    def step(ws, b=None):
+        entries = [StepEntry(s, [3], list(w)) for s, w in zip(slots, ws)]
+        starts = [m.extend(s, 1) for s in slots]
+        if b is None:
+            b = StepBatch(m, entries, starts, "cpu")
+        else:
+            b.fill(entries, starts)
+        for s in slots:
+            m.after_step(s)
+        return b
+    b = step(([0], []))
+    assert list(tables(b)["logit_rows"]) == [0]
+    step(([], [0]), b)
+    assert list(tables(b)["logit_rows"]) == [1] and b.wanted_rows == [1]
+    with pytest.raises(StepError, match="number of wanted rows"):
+        step(([0], [0]), b)
