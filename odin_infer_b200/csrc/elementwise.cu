@@ -228,7 +228,9 @@ static int launch_add_rmsnorm(float* x, const void* delta, int n_split, size_t s
     if (vec) {
         // few rows (decoding): the whole row in one pass of a large block, a chain of latencies;
         // more rows: smaller blocks, more of them per SM, two passes each
-        const bool big = d >= 4096 && n_rows <= 256;
+        // (32-bit out: one block size per width, so that a row's sum of squares is added in the same
+        // order in a prompt and in a decode step, and the 32-bit path's cuts agree bit for bit)
+        const bool big = !std::is_same<TO, float>::value && d >= 4096 && n_rows <= 256;
         const int threads = big ? 1024 : (d >= 2048 ? 512 : (d >= 1024 ? 256 : 128));
         auto kern = big ? add_rmsnorm_kernel<TD, TO, true, 1024> : add_rmsnorm_kernel<TD, TO, true, 512>;
         if (smem > 48 * 1024) {
@@ -357,6 +359,45 @@ extern "C" int odin_swiglu(const void* gu, int in_dtype, int n_split, long long 
     } else if (in_dtype == ODIN_F32 && out_dtype == ODIN_BF16)
         odin_launch(swiglu_kernel<float, bf16>, dim3((int)blocks), dim3(threads), 0, s, (const float*)gu, n_split,
                     (size_t)split_stride, (bf16*)out, I, total);
+    else
+        return ODIN_ERR_UNSUPPORTED;
+    ODIN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ------------------------------------------------------------ random weights
+// Element i of a stream is a function of (key, i) alone: two steps of splitmix64 on key + 2 i and
+// key + 2 i + 1, the sum of their eight 16-bit fields, centred and scaled: a sum of eight uniforms
+// computed in integers, so the host restatement (weights/random_init.py) gives the same bits.
+// The product and the sum are single rounded operations (no fused multiply-add).
+__device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+template <typename T>
+__global__ void random_fill_kernel(T* __restrict__ out, long long n, unsigned long long key, float mean, float scale) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const unsigned long long h1 = mix64(key + 2ull * (unsigned long long)i);
+        const unsigned long long h2 = mix64(key + 2ull * (unsigned long long)i + 1ull);
+        int s = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) s += (int)((h1 >> (16 * k)) & 0xFFFFull) + (int)((h2 >> (16 * k)) & 0xFFFFull);
+        const float c = (float)(s - 4 * 65535);
+        out[i] = from_f32<T>(__fadd_rn(mean, __fmul_rn(c, scale)));
+    }
+}
+
+extern "C" int odin_random_fill(void* out, int dtype, long long n, unsigned long long key, float mean, float scale,
+                                void* stream) {
+    if (n <= 0) return 0;
+    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    if (dtype == ODIN_F32)
+        random_fill_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((float*)out, n, key, mean, scale);
+    else if (dtype == ODIN_BF16)
+        random_fill_kernel<bf16><<<blocks, 256, 0, (cudaStream_t)stream>>>((bf16*)out, n, key, mean, scale);
     else
         return ODIN_ERR_UNSUPPORTED;
     ODIN_LAUNCH_CHECK();

@@ -124,6 +124,15 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
         c_int(dtype_code(out.dtype)), c_int(T), c_int(I), _stream()), "swiglu")
 
 
+def random_fill(out: torch.Tensor, key: int, mean: float, scale: float) -> None:
+    """out.flatten()[i] = mean + scale * (centred sum of eight 16-bit uniforms of stream `key` at i): the
+    device side of the counter-based random weights (weights/random_init.py has the host side)."""
+    assert out.is_contiguous()
+    _check(_fn("elementwise", "odin_random_fill")(
+        _ptr(out), c_int(dtype_code(out.dtype)), c_longlong(out.numel()), ctypes.c_ulonglong(key & ((1 << 64) - 1)),
+        c_float(mean), c_float(scale), _stream()), "random_fill")
+
+
 def cast(src: torch.Tensor, dst: torch.Tensor) -> None:
     assert src.is_contiguous() and dst.is_contiguous() and src.numel() == dst.numel()
     _check(_fn("elementwise", "odin_cast")(

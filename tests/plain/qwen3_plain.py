@@ -178,8 +178,9 @@ def normalise_config(cfg: dict) -> dict:
     return cfg
 
 
-def forward_whole(cfg: dict, w: dict, tokens) -> torch.Tensor:
-    """Logits [T, V] at every position of one whole sequence.  infer/forward.odin:17-146.
+def forward_whole(cfg: dict, w: dict, tokens, positions=None) -> torch.Tensor:
+    """Logits [T, V] at every position of one whole sequence (or [len(positions), V] at the
+    given ones: the final norm and the head act on single rows).  infer/forward.odin:17-146.
 
     The head is lm_head.weight if the folder has it, else the embedding table
     (infer/model.odin:150-158).
@@ -191,6 +192,8 @@ def forward_whole(cfg: dict, w: dict, tokens) -> torch.Tensor:
     x = embedding(w["model.embed_tokens.weight"], tokens)
     for l in range(cfg["num_hidden_layers"]):
         x = decoder_layer(x, w, l, cfg, cos, sin)
+    if positions is not None:
+        x = x[torch.as_tensor(list(positions), dtype=torch.long)]
     x = rmsnorm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
     head = w.get("lm_head.weight", w["model.embed_tokens.weight"])
     return linear(x, head)

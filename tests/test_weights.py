@@ -97,3 +97,26 @@ def test_broken_files(tmp_path):
     os.remove(path)
     with pytest.raises(WeightError, match="no model.safetensors"):
         load_weights(folder, specs_of(tiny.TINY_A), torch.bfloat16, "cpu")
+
+
+def test_counter_based_random_weights():
+    """Element i of a tensor depends on (seed, name, i) alone: rows can be regenerated on their
+    own, other tensors do not matter, and a scalar restatement of the formula gives the same bits."""
+    from odin_infer_b200.parts.base import ParamSpec
+    from odin_infer_b200.weights.random_init import host_tensor, random_tensor
+    from tests.plain import random_weights_plain as R
+    spec = ParamSpec("model.layers.3.mlp.up_proj.weight", (37, 24))
+    full = random_tensor(spec, 5, torch.float32)
+    assert torch.equal(host_tensor(spec.name, spec.shape, "matrix", 5, torch.float32, first_row=11, n_rows=9), full[11:20])
+    bf = random_tensor(spec, 5, torch.bfloat16)
+    assert torch.equal(bf, full.bfloat16())                      # the storage type is a rounding of the same values
+    for i in (0, 1, 23, 24, 500, 37 * 24 - 1):
+        v = R.element(5, spec.name, i, 0.0, 0.02)
+        assert full.flatten()[i].item() == v and bf.flatten()[i].item() == R.to_bf16(v), i
+    norm = random_tensor(ParamSpec("n.weight", (50,), init="norm"), 5, torch.float32)
+    assert norm[7].item() == R.element(5, "n.weight", 7, 1.0, 0.1)
+    assert not torch.equal(full, random_tensor(spec, 6, torch.float32))
+    assert not torch.equal(full, random_tensor(ParamSpec("other", (37, 24)), 5, torch.float32))
+    big = random_tensor(ParamSpec("big", (1 << 21,)), 1, torch.float32)          # across the host's chunks of 2^20
+    assert abs(big.std().item() - 0.02) < 2e-4 and abs(big.mean().item()) < 1e-4 and big.abs().max().item() < 0.02 * 4.9
+    assert big[(1 << 20) + 3].item() == R.element(1, "big", (1 << 20) + 3, 0.0, 0.02)
