@@ -4,8 +4,8 @@
 //   argmax: the first maximum wins (strict >, :79-89);
 //   temperature: logits / T, softmax with the maximum subtracted, one coin in
 //     [0,1) per token, walk of the cumulative sum in index order (:91-100, :179-185);
-//   top-p: keep the most probable tokens until their sum first exceeds topp
-//     (:106-139), then draw among the kept ones;
+//   top-p: keep the most probable tokens until their sum first exceeds topp, scale the
+//     coin by that sum and walk the kept ones in order of falling probability (:106-139);
 //   repetition penalty: each distinct recent token has a positive logit divided
 //     and a negative one multiplied (:143-160).
 // The logits are never modified by the sampling kernels (the reference
@@ -83,6 +83,50 @@ __device__ __forceinline__ float masked_sum(const float* row, int V, float inv_t
     return block_sum(s, red);
 }
 
+// The largest t in [lo, hi] (bit patterns of positive floats, which order like the floats) with
+// S(t) = sum of e_i >= t  >  target, given S(lo) > target.  S falls as t grows.  Eight probes per
+// pass over the row, so 2^30 candidates take ten passes instead of thirty.
+__device__ unsigned search_threshold(const float* row, int V, float inv_t, float m, float target, unsigned lo,
+                                     unsigned hi, float* red) {
+    constexpr int P = 8;
+    while (lo < hi) {
+        const unsigned span = hi - lo;  // probes lo < p_0 < ... <= hi
+        unsigned probe[P];
+        float acc[P];
+#pragma unroll
+        for (int q = 0; q < P; ++q) {
+            probe[q] = lo + (unsigned)(((unsigned long long)span * (q + 1) + P - 1) / P);
+            acc[q] = 0.f;
+        }
+        for (int i = threadIdx.x; i < V; i += SB) {
+            const float e = expf(row[i] * inv_t - m);
+#pragma unroll
+            for (int q = 0; q < P; ++q)
+                if (e >= __uint_as_float(probe[q])) acc[q] += e;
+        }
+        int best = -1;
+#pragma unroll
+        for (int q = 0; q < P; ++q) {
+            const float sq = block_sum(acc[q], red);
+            if (sq > target) best = q;  // S is monotone: the last probe that still exceeds the target
+        }
+        if (best < 0) hi = probe[0] - 1;
+        else {
+            if (best + 1 < P) hi = probe[best + 1] - 1;
+            lo = probe[best];
+        }
+    }
+    return lo;
+}
+
+// Temperature draw.  Without top-p: the cumulative sum is walked in index order (sample_mult,
+// sampler/sampler.odin:91-100).  With 0 < top_p < 1 the reference sorts the candidates by falling
+// probability, cuts after the first whose cumulative sum exceeds topp, scales the coin by that sum and
+// walks the sorted list (sample_topp, :106-139).  Here nothing is sorted: the token at which a walk in
+// falling order crosses a mark r is the one with the largest value u such that the tokens of at least
+// that value sum to more than r, which a search over u finds (ties: in index order).  So the same coin
+// gives the reference's token, up to the rounding of the sums and the order among exactly equal
+// probabilities, which the reference's unstable sort leaves open.
 __global__ void __launch_bounds__(SB) sample_kernel(const float* __restrict__ logits, size_t ld, int V,
                                                     float temperature, float top_p,
                                                     const float* __restrict__ coins, int* __restrict__ out) {
@@ -97,39 +141,87 @@ __global__ void __launch_bounds__(SB) sample_kernel(const float* __restrict__ lo
     for (int i = threadIdx.x; i < V; i += SB) mx = fmaxf(mx, row[i] * inv_t);
     mx = block_max(mx, red);
     const float total = masked_sum(row, V, inv_t, mx, 0.f, red);
+    const int per = (V + SB - 1) / SB;  // contiguous chunk of the row per thread, for walks in index order
+    const int c0 = min(V, (int)threadIdx.x * per), c1 = min(V, c0 + per);
+    if (threadIdx.x == 0) chosen = -1;
 
-    // threshold on e (unnormalised probability): keep e_i >= thr
-    float thr = 0.f;
     if (top_p > 0.f && top_p < 1.f && V > 1) {
+        // everything in units of e (unnormalised probabilities)
         const float cutoff = (1.0f - top_p) / (float)(V - 1) * total;
         const float target = top_p * total;
-        if (masked_sum(row, V, inv_t, mx, cutoff, red) <= target) {
-            thr = cutoff;  // the candidates together do not exceed topp: keep them all
-        } else {
-            // largest thr with sum(e >= thr) > target; positive floats order like their bits
-            unsigned lo = __float_as_uint(cutoff), hi = __float_as_uint(1.0f);  // e <= 1
-            // invariant: S(lo) > target, S(hi+) may not
-            while (lo < hi) {
-                const unsigned mid = lo + (hi - lo + 1) / 2;
-                if (masked_sum(row, V, inv_t, mx, __uint_as_float(mid), red) > target) lo = mid;
-                else hi = mid - 1;
-            }
-            thr = __uint_as_float(lo);
+        const float s_cut = masked_sum(row, V, inv_t, mx, cutoff, red);
+        unsigned lo = __float_as_uint(fmaxf(cutoff, 1e-45f));
+        float cumulative = s_cut;  // the candidates together do not exceed topp: all of them stay
+        if (s_cut > target) {
+            // v: the value of the candidate at which the cumulative sum first exceeds topp
+            lo = search_threshold(row, V, inv_t, mx, target, lo, __float_as_uint(1.0f), red);
+            const float v = __uint_as_float(lo);
+            const float above = masked_sum(row, V, inv_t, mx, __uint_as_float(lo + 1), red);
+            const float ties = floorf((target - above) / v) + 1.0f;  // how many of value v it takes
+            cumulative = above + fmaxf(ties, 1.0f) * v;
         }
+        const float r = coins[blockIdx.x] * cumulative;
+        unsigned ub = lo;
+        float u = __uint_as_float(lo);
+        int nth = 0x7fffffff;  // which of the tokens of value u, in index order (beyond their number: the last)
+        if (masked_sum(row, V, inv_t, mx, u, red) > r) {
+            ub = search_threshold(row, V, inv_t, mx, r, lo, __float_as_uint(1.0f), red);
+            u = __uint_as_float(ub);
+            const float above = masked_sum(row, V, inv_t, mx, __uint_as_float(ub + 1), red);
+            nth = (int)fminf(floorf(fmaxf(r - above, 0.f) / u), 2.0e9f);
+        }
+        // the nth token (from 0) whose e is exactly u, else the last such one; if u is below every
+        // candidate (the coin scaled to the whole sum), the smallest candidate's last occurrence
+        float cnt = 0.f;
+        for (int i = c0; i < c1; ++i) cnt += (expf(row[i] * inv_t - mx) == u) ? 1.f : 0.f;
+        chunk_sum[threadIdx.x] = cnt;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int seen = 0, owner = -1, last_owner = -1;
+            for (int t = 0; t < SB; ++t) {
+                const int c = (int)chunk_sum[t];
+                if (c > 0) last_owner = t;
+                if (owner < 0 && seen + c > nth) { owner = t; break; }
+                seen += c;
+            }
+            if (owner < 0) { owner = last_owner; seen = 0x7fffffff; }
+            if (owner >= 0) {
+                const int o0 = min(V, owner * per), o1 = min(V, o0 + per);
+                int pick = -1;
+                for (int i = o0; i < o1; ++i) {
+                    if (expf(row[i] * inv_t - mx) == u) {
+                        pick = i;
+                        if (seen != 0x7fffffff && seen++ == nth) break;
+                    }
+                }
+                chosen = pick;
+            }
+        }
+        __syncthreads();
+        if (chosen < 0) {
+            // no token of value u (u was the cutoff itself): the smallest candidate, the reference's last_idx
+            float best = CUDART_INF_F;
+            for (int i = threadIdx.x; i < V; i += SB) {
+                const float e = expf(row[i] * inv_t - mx);
+                if (e >= u) best = fminf(best, e);
+            }
+            best = -block_max(-best, red);
+            int last = -1;
+            for (int i = threadIdx.x; i < V; i += SB)
+                if (expf(row[i] * inv_t - mx) == best) last = max(last, i);
+            const float lf = block_max((float)last, red);
+            if (threadIdx.x == 0) chosen = (int)lf;
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) out[blockIdx.x] = max(chosen, 0);
+        return;
     }
-    const float kept = (thr > 0.f) ? masked_sum(row, V, inv_t, mx, thr, red) : total;
-    const float target = coins[blockIdx.x] * kept;
 
-    // cumulative walk in index order: contiguous chunk per thread, then a scan
-    const int per = (V + SB - 1) / SB;
-    const int c0 = min(V, (int)threadIdx.x * per), c1 = min(V, c0 + per);
+    // ---- all tokens, cumulative walk in index order: contiguous chunk per thread, then a scan
+    const float target = coins[blockIdx.x] * total;
     float cs = 0.f;
-    for (int i = c0; i < c1; ++i) {
-        const float e = expf(row[i] * inv_t - mx);
-        if (e >= thr) cs += e;
-    }
+    for (int i = c0; i < c1; ++i) cs += expf(row[i] * inv_t - mx);
     chunk_sum[threadIdx.x] = cs;
-    if (threadIdx.x == 0) chosen = -1;
     __syncthreads();
     if (threadIdx.x == 0) {
         // serial exclusive scan over 1024 chunk sums: fixed order
@@ -143,31 +235,17 @@ __global__ void __launch_bounds__(SB) sample_kernel(const float* __restrict__ lo
         if (owner >= 0) {
             const int o0 = min(V, owner * per), o1 = min(V, o0 + per);
             float cdf = run;
-            int pick = -1, last_kept = -1;
+            int pick = -1;
             for (int i = o0; i < o1; ++i) {
-                const float e = expf(row[i] * inv_t - mx);
-                if (e >= thr) {
-                    cdf += e;
-                    last_kept = i;
-                    if (target < cdf) { pick = i; break; }
-                }
+                cdf += expf(row[i] * inv_t - mx);
+                if (target < cdf) { pick = i; break; }
             }
-            chosen = (pick >= 0) ? pick : last_kept;
+            chosen = (pick >= 0) ? pick : o1 - 1;
         }
     }
     __syncthreads();
-    if (chosen < 0) {
-        // rounding left the coin beyond the last sum: the last kept token (reference: n - 1)
-        int last = -1;
-        for (int i = threadIdx.x; i < V; i += SB) {
-            const float e = expf(row[i] * inv_t - mx);
-            if (e >= thr) last = max(last, i);
-        }
-        float lf = block_max((float)last, red);
-        if (threadIdx.x == 0) chosen = (int)lf;
-        __syncthreads();
-    }
-    if (threadIdx.x == 0) out[blockIdx.x] = max(chosen, 0);
+    // rounding left the coin beyond the last sum: the last token (reference: n - 1)
+    if (threadIdx.x == 0) out[blockIdx.x] = (chosen >= 0) ? chosen : V - 1;
 }
 
 extern "C" int odin_sample(const float* logits, long long ld, int B, int V, float temperature, float top_p,

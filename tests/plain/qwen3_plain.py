@@ -242,6 +242,34 @@ def top_p_keep(probs: torch.Tensor, topp: float) -> set:
     return keep
 
 
+def sample_topp(probs, topp: float, coin: float):
+    """The reference's top-p draw: candidates with p >= (1 - topp) / (n - 1), sorted by falling
+    probability, cut after the first whose cumulative sum exceeds topp, the coin scaled by that
+    sum, and a walk of the sorted list.  sampler/sampler.odin:106-139.
+
+    Returns (token, margin): margin is how far (in probability) the scaled coin lies from the
+    nearer end of the chosen token's interval; a draw with a tiny margin may go to the neighbour
+    under another rounding of the sums."""
+    n = len(probs)
+    cutoff = (1.0 - topp) / (n - 1)
+    cand = [(float(p), i) for i, p in enumerate(probs) if float(p) >= cutoff]
+    cand.sort(key=lambda t: -t[0])           # stable: equal probabilities stay in index order
+    cumulative, last_idx = 0.0, len(cand) - 1
+    for j, (p, _) in enumerate(cand):
+        cumulative += p
+        if cumulative > topp:
+            last_idx = j
+            break
+    r = coin * cumulative
+    cdf = 0.0
+    for j in range(last_idx + 1):
+        before = cdf
+        cdf += cand[j][0]
+        if r < cdf:
+            return cand[j][1], (cdf - r) if j == 0 else min(r - before, cdf - r)
+    return cand[last_idx][1], 0.0
+
+
 def repetition_penalty(logits: torch.Tensor, recent, penalty: float) -> torch.Tensor:
     """Each distinct recent token: divide a positive logit, multiply a negative
     one.  sampler/sampler.odin:143-160."""

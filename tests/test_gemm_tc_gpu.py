@@ -47,6 +47,14 @@ CASES = [
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_ladder(case, out_dtype):
     M, N, K, mode, bn = case
+    ladder(lambda a, w: run(a, w, mode, bn, out_dtype), M, N, K, out_dtype)
+
+
+def ladder(run_product, M, N, K, out_dtype):
+    """Structured inputs first, random ones last (gemm_harness/gemm_test.odin:1063-1072)."""
+    def run(a, w, *_):
+        return run_product(a, w)
+    mode = bn = None
     exact = 1e-6 if out_dtype == torch.float32 else 4e-3
     ones_a = torch.ones(M, K, device=DEV, dtype=torch.bfloat16)
     ones_w = torch.ones(N, K, device=DEV, dtype=torch.bfloat16)
@@ -251,3 +259,53 @@ def test_pair_kernel_adds_in_place(case):
     ops.gemm_tc2(a, w, x, accumulate=True)
     ops.gemm_tc_check()
     assert torch.equal(x, x0 + prod)
+
+
+# A product with the fault that the reference keeps beside its kernels to prove that its ladder can fail
+# (gemm_harness/gemm_test.odin:322-338, "K-step-16 reproduces the old 2048 bug"): the loop over K advances
+# by two blocks and multiplies one.  Compiled here, from this string, at test time; it is in no library.
+KNOWN_BAD = r"""
+#include <cuda_bf16.h>
+__global__ void bad_product(const __nv_bfloat16* A, const __nv_bfloat16* W, float* C, int M, int N, int K) {
+    const int n = blockIdx.x * blockDim.x + threadIdx.x, m = blockIdx.y;
+    if (n >= N || m >= M) return;
+    float acc = 0.f;
+    for (int k0 = 0; k0 < K; k0 += 16)                       // the fault: 16 instead of 8
+        for (int k = k0; k < k0 + 8 && k < K; ++k)
+            acc = fmaf(__bfloat162float(A[(size_t)m * K + k]), __bfloat162float(W[(size_t)n * K + k]), acc);
+    C[(size_t)m * N + n] = acc;
+}
+extern "C" int bad_product_launch(const void* A, const void* W, float* C, int M, int N, int K, void* stream) {
+    bad_product<<<dim3((N + 127) / 128, M), 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)A, (const __nv_bfloat16*)W, C, M, N, K);
+    return (int)cudaGetLastError();
+}
+"""
+
+
+def test_ladder_catches_a_known_bad_product(tmp_path):
+    """The regression guard of the ladder itself: a product that skips every second block of K must
+    fail at the first rung (all ones gives K/2), and with the names of the later rungs too."""
+    import ctypes
+    import subprocess
+    from odin_infer_b200.csrc import build
+    src, lib = tmp_path / "bad.cu", tmp_path / "libbad.so"
+    src.write_text(KNOWN_BAD)
+    nvcc = build._nvcc()
+    assert nvcc is not None, "nvcc is needed to build the known-bad variant"
+    subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-Xcompiler", "-fPIC", "-shared",
+                    "-o", str(lib), str(src)], check=True, capture_output=True)
+    fn = ctypes.CDLL(str(lib)).bad_product_launch
+
+    def bad(a, w):
+        out = torch.empty(a.shape[0], w.shape[0], device=DEV)
+        rc = fn(ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(w.data_ptr()), ctypes.c_void_p(out.data_ptr()),
+                a.shape[0], w.shape[0], a.shape[1], ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        assert rc == 0
+        return out
+    ones = torch.ones(8, 4096, device=DEV, dtype=torch.bfloat16)
+    assert bad(ones, ones)[0, 0].item() == 2048.0             # the reference's "old 2048 bug"
+    with pytest.raises(AssertionError, match="ones"):
+        ladder(bad, 64, 64, 4096, torch.float32)
+    with pytest.raises(AssertionError, match="ones"):
+        ladder(bad, 8, 8, 16, torch.float32)
+    ladder(bad, 8, 8, 8, torch.float32)                       # one block of K: nothing is skipped yet, as in the reference's first rung

@@ -345,6 +345,38 @@ def test_argmax_and_sampling():
     assert (freq.cpu() - torch.softmax(small[0].double().cpu(), 0)).abs().max() < 0.03
 
 
+@pytest.mark.parametrize("V", [1003, 151936])
+def test_top_p_draws_the_references_token(V):
+    """With top-p the reference walks the kept tokens in order of falling probability with the coin
+    scaled by their sum: for the same coin the kernel gives that very token (a coin within rounding
+    of a boundary may give the neighbour in that order), also with exact ties inside the kept set and
+    at the cut, where index order decides."""
+    from odin_infer_b200.csrc import ops
+    from tests.plain import qwen3_plain as P
+    torch.manual_seed(V)
+    rows = [torch.randn(V) * 4, torch.randn(V) * 1.5, torch.randn(V) * 0.3, torch.zeros(V)]
+    rows[3][:8] = torch.tensor([5.0, 5.0, 4.0, 5.0, 4.0, 3.0, 3.0, 3.0])      # ties of three, two, three
+    rows.append(torch.cat([torch.full((6,), 2.0), torch.full((V - 6,), -30.0)]))  # six equal tokens carry everything
+    logits = torch.stack(rows).to(DEV)
+    B = logits.shape[0]
+    out = torch.empty(B, dtype=torch.int32, device=DEV)
+    checked = 0
+    small = V < 10000   # the plain walk over a large vocabulary is slow: fewer draws there
+    near = 1e-5 if small else 1e-6   # how close to a boundary a scaled coin may lie and still be compared
+    for temp, tp in (((1.0, 0.9), (0.7, 0.5), (1.3, 0.95), (1.0, 0.999), (1.0, 0.05)) if small else ((0.7, 0.9), (1.0, 0.5))):
+        probs = [P.temperature_probs(logits[b].double().cpu(), temp) for b in range(B)]
+        for coin in ((0.0, 0.013, 0.2, 0.37, 0.5, 0.77, 0.93, 0.9999) if small else (0.0, 0.2, 0.5, 0.93)):
+            ops.sample(logits, temp, tp, torch.full((B,), coin, device=DEV), out)
+            got = out.tolist()
+            for b in range(B):
+                tok, margin = P.sample_topp(probs[b], tp, coin)
+                assert got[b] in P.top_p_keep(probs[b], tp) or margin < near, (V, temp, tp, coin, b)
+                if margin > near:
+                    assert got[b] == tok, (V, temp, tp, coin, b, got[b], tok)
+                    checked += 1
+    assert checked > (150 if small else 25)
+
+
 def test_repetition_penalty():
     from odin_infer_b200.csrc import ops
     from tests.plain import qwen3_plain as P

@@ -94,3 +94,23 @@ def test_sampler_pieces():
     assert keep <= {1, 2} and len(keep) >= 1
     pen = P.repetition_penalty(torch.tensor([1.0, -1.0, 3.0]), [0, 1, 1], 2.0)
     assert pen.tolist() == [0.5, -2.0, 3.0]
+
+
+import pytest
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+def test_two_independent_restatements_of_the_reference_agree(tmp_path, name):
+    """The whole-sequence restatement (torch, matrix products) against the token-by-token one (numpy,
+    the reference's own loop structure with key and value arrays): float64 rounding apart, the same
+    logits at every position.  The oracle of the GPU tests therefore rests on two readings."""
+    import numpy as np
+    from tests.plain import qwen3_stepwise as S
+    raw, seed = tiny.TINIES[name]
+    folder = tiny.make_folder(tmp_path, raw, seed)
+    cfg, w = P.read_model_folder(folder, torch.float64)
+    toks = tiny.random_tokens(14 if raw["vocab_size"] > 500 else 20, raw["vocab_size"], 40)
+    whole = P.forward_whole(cfg, w, toks).numpy()
+    steps = S.logits_token_by_token(cfg, {k: v.numpy() for k, v in w.items()}, toks)
+    assert steps.shape == whole.shape
+    assert tiny.rel_err(steps, whole) < 1e-12
