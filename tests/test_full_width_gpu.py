@@ -32,21 +32,6 @@ def wanted_positions(n: int) -> list[int]:
     return picked[:16] if n - 1 in picked[:16] else picked[:15] + [n - 1]
 
 
-def restrict(recs, wanted: dict):
-    """The same schedule with logits asked for at the wanted absolute positions only."""
-    seen: dict = {}
-    out = []
-    for rec in recs:
-        ents = []
-        for e in rec["entries"]:
-            base = seen.get(e["id"], 0)
-            ents.append({"id": e["id"], "tokens": e["tokens"],
-                         "want": [w for w in range(len(e["tokens"])) if base + w in wanted[e["id"]]]})
-            seen[e["id"]] = base + len(e["tokens"])
-        out.append({"step": rec["step"], "entries": ents, "end": rec["end"]})
-    return out
-
-
 @pytest.fixture(scope="module")
 def case():
     """Requests, wanted places and the plain implementation's logits there (float32 on the CPU, on the
@@ -87,9 +72,9 @@ def run(dtype, recs):
 
 
 def schedules(reqs, wanted):
-    return {"whole": restrict(traces.whole(reqs), wanted),
-            "last 32 one by one": restrict(traces.tail_one_by_one(reqs, 32), wanted),
-            "unequal batch": restrict(traces.batches(reqs, 3, first_part=lambda n: max(1, n - 40)), wanted)}
+    return {"whole": traces.restrict(traces.whole(reqs), wanted),
+            "last 32 one by one": traces.restrict(traces.tail_one_by_one(reqs, 32), wanted),
+            "unequal batch": traces.restrict(traces.batches(reqs, 3, first_part=lambda n: max(1, n - 40)), wanted)}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

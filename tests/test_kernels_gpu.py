@@ -523,27 +523,29 @@ def test_attention_decode_with_head_prep_equals_the_two_kernels(geom, parts):
     ops.attention_decode_check()
 
 
-def test_attention_decode_window_and_far_key():
+@pytest.mark.parametrize("hd,n,far", [(64, 300, 67), (128, 9000, 70), (128, 9000, 8191), (128, 8300, 4096), (64, 8193, 8128)])
+def test_attention_decode_window_and_far_key(hd, n, far):
+    """One key among hundreds or thousands is made to dominate; whichever page, warp or key split it
+    falls to, the output must be its value (block tables of up to 141 pages, up to 16 splits)."""
     from odin_infer_b200.csrc import ops
-    n_q, n_kv, hd, n = 4, 2, 64, 300
+    n_q, n_kv = 4, 2
     torch.manual_seed(5)
     k_cache, v_cache, bt = paged_cache(1, [n], n_kv, hd, torch.bfloat16)
     keys = 0.1 * torch.randn(n, n_kv, hd, device=DEV)
     vals = torch.randn(n, n_kv, hd, device=DEV)
-    far = 67
     keys[far] = 0.0
     keys[far, :, 0] = 40.0
     q = 0.1 * torch.randn(1, n_q, hd, device=DEV)
     q[0, :, 0] = 40.0 / math.sqrt(hd) * 2
-    for p in range(n):
-        page = int(bt[0, p // 64])
-        k_cache[page, :, p % 64] = keys[p].bfloat16()
-        v_cache[page, :, p % 64] = vals[p].bfloat16()
+    for pg in range((n + 63) // 64):
+        page, m = int(bt[0, pg]), min(64, n - pg * 64)
+        k_cache[page, :, :m] = keys[pg * 64:pg * 64 + m].transpose(0, 1).bfloat16()
+        v_cache[page, :, :m] = vals[pg * 64:pg * 64 + m].transpose(0, 1).bfloat16()
     tok_pos = torch.tensor([n - 1], dtype=torch.int32, device=DEV)
     tok_seq = torch.zeros(1, dtype=torch.int32, device=DEV)
     qf = q.reshape(1, n_q * hd).bfloat16()
     out = torch.empty(1, n_q * hd, device=DEV, dtype=torch.bfloat16)
-    for n_split in (1, 4, 7):
+    for n_split in (1, 4, 7, 16):
         scratch = torch.empty(ops.attention_decode_scratch(1, n_q, hd, n_split), device=DEV)
         ops.attention_decode(qf, out, n_q, n_kv, hd, k_cache, v_cache, tok_pos, tok_seq, bt, 0, scratch, n_split)
         close(out.float().view(n_q, hd)[0], vals[far, 0].bfloat16().float(), 2e-2)
@@ -610,15 +612,15 @@ def test_attention_prefill_against_plain_kernel_and_reference(geom, window):
         r += b
 
 
-def test_attention_prefill_long_prompt_far_key():
-    """2,048 tokens: one key early in the prompt is made to dominate every later query."""
+@pytest.mark.parametrize("n,far", [(2048, 100), (8448, 100), (8448, 8191)])
+def test_attention_prefill_long_prompt_far_key(n, far):
+    """Thousands of tokens: one key of the prompt is made to dominate every later query."""
     from odin_infer_b200.csrc import ops
-    n_q, n_kv, hd, n = 4, 2, 128, 2048
+    n_q, n_kv, hd = 4, 2, 128
     torch.manual_seed(9)
     k_cache, v_cache, bt = paged_cache(1, [n], n_kv, hd, torch.bfloat16)
     keys = 0.05 * torch.randn(n, n_kv, hd, device=DEV)
     vals = torch.randn(n, n_kv, hd, device=DEV)
-    far = 100
     keys[far] = 0.0
     keys[far, :, 5] = 30.0
     q = 0.05 * torch.randn(n, n_q, hd, device=DEV)
@@ -634,7 +636,7 @@ def test_attention_prefill_long_prompt_far_key():
                           seq_len_after, bt, 0)
     ops.attention_prefill_check()
     got = out.float().view(n, n_q, hd)
-    for t in (far, far + 1, 777, n - 1):
+    for t in (far, far + 1, min(far + 777, n - 2), n - 1):
         for h in range(n_q):
             close(got[t, h], vals[far, h // 2].bfloat16().float(), 2e-2)
     assert (got[far - 1, 0] - vals[far, 0]).abs().max() > 0.1   # causal: the key is not yet visible

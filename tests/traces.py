@@ -159,3 +159,19 @@ def joining(requests: dict[str, list[int]], width: int = 3, tail: int = 6):
         recs.append({"step": n, "entries": ents, "end": end})
         n += 1
     return recs
+
+
+def restrict(recs, wanted: dict):
+    """The same schedule with logits asked for at the wanted absolute positions only
+    (wanted: {request id: positions})."""
+    seen: dict = {}
+    out = []
+    for rec in recs:
+        ents = []
+        for e in rec["entries"]:
+            base = seen.get(e["id"], 0)
+            ents.append({"id": e["id"], "tokens": e["tokens"],
+                         "want": [w for w in range(len(e["tokens"])) if base + w in wanted[e["id"]]]})
+            seen[e["id"]] = base + len(e["tokens"])
+        out.append({"step": rec["step"], "entries": ents, "end": rec["end"]})
+    return out
