@@ -123,7 +123,9 @@ __global__ void __launch_bounds__(MAX_THREADS, MAX_THREADS > 512 ? 1 : 3) add_rm
             ss += v * v;
         }
     }
+    odin_trace_mark(2);  // loads done
     ss = block_sum(ss, red);
+    odin_trace_mark(3);  // sum known
     ss /= (float)d;
     ss += eps;
     const float rs = 1.0f / sqrtf(ss);
@@ -142,6 +144,7 @@ __global__ void __launch_bounds__(MAX_THREADS, MAX_THREADS > 512 ? 1 : 3) add_rm
             o[j] = from_f32<TO>(w.at(j) * (rs * v));
         }
     }
+    odin_trace_mark(4);  // stores issued
 }
 
 // Many rows (prompts), bfloat16 out: a block of 256 threads per row that keeps its NV groups of four

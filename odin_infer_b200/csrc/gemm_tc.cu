@@ -197,6 +197,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     if (++stage == n_stages) { stage = 0; phase ^= 1; }
                 }
             }
+            odin_trace_mark(6, true);  // every load of this CTA is requested
             if (!ok) {
                 // aborted: let the copies already in flight land before the CTA's memory is released
                 for (uint32_t s2 = 0; s2 < n_stages; ++s2)
@@ -255,7 +256,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 }
                 if (ok && tc::elect_one()) tc::umma_commit(&acc_full[acc]);
                 __syncwarp();
+                if (local == 0 && lane == 0) odin_trace_mark(2, true);  // the first item's MMAs are issued
             }
+            if (lane == 0) odin_trace_mark(3, true);  // the last commit is issued
         } else {
             // many tokens: an MMA of 256 columns takes 128 cycles, the issuing lane is never the limit,
             // and a single lane that walks the loop alone measured 2 % faster than the converged warp
@@ -356,6 +359,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(&acc_empty[acc]);
         }
+        if (threadIdx.x == 64) odin_trace_mark(5, true);  // the last tile is stored
     }
 
     tc::fence_before_sync();

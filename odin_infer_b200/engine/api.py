@@ -105,8 +105,11 @@ class Engine:
             elif opts.verbose:
                 print("odin_infer_b200: steps run eagerly, not as CUDA graphs: these parts do not declare graph_safe: "
                       + ", ".join(self.model.parts_not_graph_safe()), file=sys.stderr, flush=True)
+        self.notes = self.model.notes(self.rt)
         if opts.verbose:
             print(self.summary(), file=sys.stderr, flush=True)
+            for n in self.notes:
+                print("odin_infer_b200: note: " + n, file=sys.stderr, flush=True)
 
     # ---- construction ------------------------------------------------------
     @classmethod

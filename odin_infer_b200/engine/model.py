@@ -55,6 +55,15 @@ class DecoderModel:
                     out.append(type(q).__name__)
         return sorted(set(out))
 
+    def notes(self, rt) -> list[str]:
+        """Every part's notes, each once."""
+        out: list[str] = []
+        for part in self._all_parts():
+            for n in part.notes(rt):
+                if n not in out:
+                    out.append(n)
+        return out
+
     def bind(self, tensors: dict[str, torch.Tensor], rt, n_positions: int) -> None:
         for part in self._all_parts():
             part.bind(tensors, rt)

@@ -69,6 +69,30 @@ class GQAttention(Mixer):
     def kernel_groups(self):
         return {"head_prep", "attention_plain", "gemm_plain"}
 
+    def notes(self, rt):
+        import torch
+        if rt.dtype != torch.bfloat16:
+            return []
+        out, hd, group = [], self.hd, self.n_q // self.n_kv
+        rot = self.pe.rotation() if self.pe is not None else None
+        if not ops.attention_prefill_supported(hd):
+            out.append(f"attention: head_dim {hd} is not 64 or 128: prompts run the CUDA-core attention kernel "
+                       "(one warp per token and head), far slower than the tensor-core one")
+        if not ops.attention_decode_supported(hd):
+            out.append(f"attention: head_dim {hd} is no power of two from 16 to 256: decoding runs the CUDA-core "
+                       "attention kernel without key splits")
+        elif hd not in (64, 128) or group > 16:
+            out.append(f"attention: head_dim {hd} with {group} query heads per kv head: decoding runs the CUDA-core "
+                       "split-key kernel (the tensor-core one takes head_dim 64 or 128 and up to 16 query heads per kv head)")
+        elif rot is not None and rot[2] != hd:
+            out.append(f"attention: rotary_dim {rot[2]} < head_dim {hd}: head preparation runs as a kernel of its own "
+                       "when decoding")
+        for what, k in (("width", self.width), ("n_q_heads * head_dim", self.n_q * hd)):
+            if k % 8:
+                out.append(f"attention: {what} = {k} is no multiple of 8: its matrix products run on CUDA cores "
+                           "(the tensor-core kernels read rows of whole 16 bytes)")
+        return out
+
     takes_residual = True
 
     def forward(self, rt, step, h, entry, residual=None):

@@ -71,6 +71,11 @@ class Part:
         """Kernel libraries this part launches (compiled before the first step)."""
         return set()
 
+    def notes(self, rt) -> list[str]:
+        """What a user should know at load about how this part will run with its sizes (a size that
+        a fast kernel does not take and what runs instead); printed once, never an error."""
+        return []
+
 
 class ResidualAdded:
     """The answer of `Runtime.linear(..., add_to=x)` when the product has added its result to

@@ -34,6 +34,9 @@ class PreNormBlock(Block):
     def kernel_groups(self):
         return set().union(*(p.kernel_groups() for p in self._parts()))
 
+    def notes(self, rt):
+        return [n for p in self._parts() for n in p.notes(rt)]
+
     @property
     def graph_safe(self):
         return all(p.graph_safe for p in self._parts())

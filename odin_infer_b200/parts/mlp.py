@@ -33,6 +33,13 @@ class SwiGLU(FeedForward):
     def kernel_groups(self):
         return {"elementwise", "gemm_plain"}
 
+    def notes(self, rt):
+        if rt.dtype != torch.bfloat16:
+            return []
+        return [f"feed-forward: {what} = {k} is no multiple of 8: its matrix products run on CUDA cores "
+                "(the tensor-core kernels read rows of whole 16 bytes)"
+                for what, k in (("width", self.width), ("inner", self.inner)) if k % 8]
+
     takes_residual = True
 
     def forward(self, rt, step, h, residual=None):

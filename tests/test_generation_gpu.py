@@ -180,3 +180,20 @@ def test_one_step_ahead_equals_the_hosts_pace(folders, dtype):
         e.cache.check()
         assert all(g.pool.n_held == 0 for g in e.cache.groups.values())
         e.destroy()
+
+
+def test_load_says_when_a_size_falls_off_a_fast_kernel(folders, capfd):
+    """Sizes that config.json allows and a fast kernel does not take run on a slower kernel, correctly;
+    the engine says so at load instead of leaving it to a profile."""
+    e = engine_for(folders["C"], "bfloat16", verbose=True)          # head size 48, five query heads on one kv head
+    err = capfd.readouterr().err
+    assert any("head_dim 48 is not 64 or 128" in n for n in e.notes) and "note: attention: head_dim 48" in err
+    assert any("no power of two" in n for n in e.notes)
+    e.destroy()
+    for name in ("D", "E"):                                         # head sizes 64 and 128: nothing to say
+        e = engine_for(folders[name], "bfloat16")
+        assert e.notes == []
+        e.destroy()
+    e = engine_for(folders["C"], "float32")                         # the 32-bit path has one kernel per operation
+    assert e.notes == []
+    e.destroy()
