@@ -42,6 +42,7 @@ struct PrefillTcParams {
     int window;
     float scale_log2;
     int* error;
+    int n_heads, n_seqs, n_tile_levels;  // the work: (head, sequence, tile) triples, heaviest tile level first
 };
 
 // The first wait that runs out records who it was: [which wait, head, sequence, tile, iteration,
@@ -68,6 +69,10 @@ __device__ __forceinline__ float ex2(float x) {
 // by before the accumulated O is rescaled.  Probabilities then reach at most 2^8, which
 // bfloat16 and the 32-bit sums hold without loss; most pages need no rescaling at all.
 constexpr float RESCALE_LAG = 8.0f;
+
+#ifdef ODIN_TRACE
+__device__ unsigned long long* odin_attn_clk = nullptr;
+#endif
 
 template <int HD>
 __global__ void __launch_bounds__(320, 2)
@@ -105,19 +110,49 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         if (threadIdx.x == 0 && p.error != nullptr) atomicExch(p.error, 2);
         return;
     }
-    // grid (heads, sequences, tiles): the tile number is the slowest index and runs backwards,
-    // so every head's heaviest (latest) tiles start first and the light ones fill the end
-    const int seq = blockIdx.y, h = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp == 1) tc::tmem_alloc(tmem_slot, TMEM_COLS);
+    if (threadIdx.x == 0) *abort_flag = 0;
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // The CTAs are persistent (two per SM) and walk the (head, sequence, tile) triples themselves: the triples are
+    // numbered with the tile level slowest and backwards (a sequence's latest, heaviest tiles first), and CTA c takes
+    // numbers c, 2G-1-c, 2G+c, 4G-1-c, ... (G CTAs): back and forth, so that whoever took a heavy tile takes a light one
+    // next.  Left to the hardware's block scheduler, a grid of one CTA per triple kept an SM's second place empty
+    // until both of its first CTAs had ended (measured: the second wave of a 2,048-token prompt began at 41 of 67 us,
+    // although CTAs had been ending since 26 us).
+    const long long total = (long long)p.n_heads * p.n_seqs * p.n_tile_levels;
+    bool first_item = true;
+    for (long long base = 0, round = 0; base < total; base += gridDim.x, ++round) {
+    const long long w = (round & 1) ? base + ((long long)gridDim.x - 1 - blockIdx.x) : base + blockIdx.x;
+    if (w >= total) continue;
+    const int h = (int)(w % p.n_heads), seq = (int)((w / p.n_heads) % p.n_seqs);
+    const int level = (int)(w / ((long long)p.n_heads * p.n_seqs));
     const int tok0 = p.seq_start[seq], n_new = p.seq_start[seq + 1] - tok0;
     const int n_tiles = (n_new + BQT - 1) / BQT;
-    const int tile = (int)gridDim.z - 1 - (int)blockIdx.z;
-    if (tile >= n_tiles) return;
+    const int tile = p.n_tile_levels - 1 - level;
+    if (tile >= n_tiles) continue;
     const int q0 = tile * BQT;
     const int rows = min(BQT, n_new - q0);
     const int len_after = p.seq_len_after[seq];
     const int pos0 = len_after - n_new + q0;
     const int kvh = h / (p.Hq / p.Hkv);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef ODIN_TRACE
+    // Clock marks of the first triple's work (the heaviest tile of head 0), trace builds only: role 0 the MMA thread,
+    // role 1 the first softmax thread; [role][n] = (clock << 8) | point.
+    const bool traced = w == 0 && odin_attn_clk != nullptr;
+    int clk_n = 0;
+#define CLK(role, point)                                                                                         \
+    do {                                                                                                         \
+        if (traced && (role == 0 || threadIdx.x == 64) && clk_n < 1024)                                          \
+            odin_attn_clk[(role) * 1024 + clk_n++] = ((unsigned long long)clock64() << 8) | (point);            \
+    } while (0)
+#else
+#define CLK(role, point) do {} while (0)
+#endif
 
     int first_key = 0;
     if (p.window > 0 && pos0 - p.window + 1 > 0) first_key = pos0 - p.window + 1;
@@ -126,15 +161,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int* bt = p.block_table + (size_t)seq * p.bt_stride;
 
     if (threadIdx.x == 0) {
+        // every triple starts with fresh barriers (all threads are past the last one's: the sync at the loop's end)
+        if (!first_item)
+            for (int i = 0; i < 14; ++i) tc::mbar_inval(&bars[i]);
         for (int i = 0; i < 10; ++i) tc::mbar_init(&bars[i], 1);
         tc::mbar_init(&p_full[0], 8);   // one arrival per softmax warp
         tc::mbar_init(&p_full[1], 8);
         tc::mbar_init(&pv_done[0], 1);
         tc::mbar_init(&pv_done[1], 1);
-        *abort_flag = 0;
         tc::fence_barrier_init();
     }
-    if (warp == 1) tc::tmem_alloc(tmem_slot, TMEM_COLS);
+    first_item = false;
     // Q: [128 x HD] in 64-column sub-tiles, each row's 16-byte chunks XOR-swizzled with the row
     for (int idx = threadIdx.x; idx < BQT * (HD / 8); idx += 320) {
         const int r = idx / (HD / 8), c = idx % (HD / 8);
@@ -146,7 +183,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
-    const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
         // ------------------------------------------------------------- producer
@@ -188,6 +224,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 }
                 tc::umma_commit(&s_full[stage]);
                 tc::umma_commit(&k_empty[stage]);
+                CLK(0, 10);  // S issued
                 return true;
             };
             bool ok = issue_s(0);
@@ -197,6 +234,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 if (!tc::mbar_wait(&p_full[stage], (it >> 1) & 1, abort_flag)) { report_attn(p.error, 4, it, n_pages); ok = false; break; }
                 if (!tc::mbar_wait(&v_full[stage], (it >> 1) & 1, abort_flag)) { report_attn(p.error, 5, it, n_pages); ok = false; break; }
                 tc::fence_after_sync();
+                CLK(0, 11);  // P and V are there
                 const uint32_t v_u = tc::smem_u32(sV + stage * KV_TILE);
 #pragma unroll
                 for (int j = 0; j < PAGE_T / 16; ++j) {
@@ -209,6 +247,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 }
                 tc::umma_commit(&v_empty[stage]);
                 tc::umma_commit(&pv_done[stage]);
+                CLK(0, 13);  // P V issued
                 if (it + 2 < n_pages) ok = issue_s(it + 2);  // its S buffer was read before p_full(it)
             }
         }
@@ -227,9 +266,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             const int pg = page_a + it, stage = it & 1;
             if (!tc::mbar_wait(&s_full[stage], (it >> 1) & 1, abort_flag)) { report_attn(p.error, 6, it, n_pages); ok = false; break; }
             tc::fence_after_sync();
+            CLK(1, 20);  // scores are there
             uint32_t sr[32];
             tc::tmem_ld32(tmem_base + lane_addr + S_COL + stage * PAGE_T + half * 32, sr);
             tc::tmem_ld_wait();
+            CLK(1, 21);  // read
             const int key0 = pg * PAGE_T + half * 32;
             if ((pg * PAGE_T + PAGE_T - 1 > pos0) || p.window > 0) {  // a page on the diagonal or at the window's edge
 #pragma unroll
@@ -246,6 +287,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             s_max[(it & 1) * 256 + half * 128 + row] = mx;
             asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
             mx = fmaxf(mx, s_max[(it & 1) * 256 + (half ^ 1) * 128 + row]) * scale;
+            CLK(1, 22);  // maximum known
             // move the scaling maximum only when the row's maximum ran ahead by more than the lag
             float corr = 1.0f;
             if (mx > m_run + RESCALE_LAG) {
@@ -261,6 +303,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 sum4[c & 3] += pv;
             }
             l_run = l_run * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            CLK(1, 23);  // exponentials done
             // P: this thread's 32 keys as 16 packed words, written over the S buffer's columns
             {
                 uint32_t pk[16];
@@ -301,6 +344,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             tc::fence_before_sync();
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(&p_full[stage]);
+            CLK(1, 24);  // P handed over
         }
         if (ok && !tc::mbar_wait(&pv_done[(n_pages - 1) & 1], ((n_pages - 1) >> 1) & 1, abort_flag)) { report_attn(p.error, 8, n_pages, n_pages); ok = false; }
         if (ok) {
@@ -332,7 +376,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     }
 
     tc::fence_before_sync();
-    __syncthreads();
+    __syncthreads();   // the triple is done: its barriers, Q and stages are free
+    if (*abort_flag) break;
+    }  // the next triple
+
+    odin_trace_mark(9);  // the CTA's work is done (trace builds only)
     if (threadIdx.x == 0 && *abort_flag && p.error != nullptr) atomicCAS(p.error, 0, 99);
     if (warp == 1) {
         tc::fence_after_sync();
@@ -361,8 +409,15 @@ int launch_prefill_tc(const CUtensorMap& mk, const CUtensorMap& mv, const Prefil
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(p.Hq, n_seqs, (max_new + BQT - 1) / BQT);
-    odin_launch(attn_prefill_tc_kernel<HD>, grid, dim3(320), (size_t)SMEM, s, mk, mv, p);
+    PrefillTcParams q = p;
+    q.n_heads = p.Hq; q.n_seqs = n_seqs; q.n_tile_levels = (max_new + BQT - 1) / BQT;
+    const long long total = (long long)q.n_heads * q.n_seqs * q.n_tile_levels;
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+    const int grid = (int)(total < 2LL * sms ? total : 2LL * sms);
+    odin_launch(attn_prefill_tc_kernel<HD>, dim3(grid), dim3(320), (size_t)SMEM, s, mk, mv, q);
     ODIN_LAUNCH_CHECK();
     return 0;
 }
@@ -377,7 +432,6 @@ extern "C" int odin_attention_prefill_tc(const void* q, long long q_row_stride, 
                                          void* stream) {
     if (n_seqs <= 0 || max_new <= 0) return 0;
     if (Hkv <= 0 || Hq % Hkv != 0) return ODIN_ERR_BAD_ARG;
-    if (n_seqs > 65535 || (max_new + BQT - 1) / BQT > 65535) return ODIN_ERR_UNSUPPORTED;
     if ((q_row_stride % 8) || (((uintptr_t)q) & 15) || (out_row_stride % 8) || (((uintptr_t)out) & 15))
         return ODIN_ERR_UNSUPPORTED;
     CUtensorMap mk, mv;
@@ -399,6 +453,12 @@ extern "C" int odin_attention_prefill_tc(const void* q, long long q_row_stride, 
     if (hd == 128) return launch_prefill_tc<128>(mk, mv, p, n_seqs, max_new, s);
     return ODIN_ERR_UNSUPPORTED;
 }
+
+#ifdef ODIN_TRACE
+extern "C" int odin_attention_prefill_tc_set_clk(void* buf) {
+    return cudaMemcpyToSymbol(odin_attn_clk, &buf, sizeof(buf)) != cudaSuccess;
+}
+#endif
 
 extern "C" int odin_attention_prefill_tc_error_detail(int* out8) {
     int* f = tc_error_flag();
