@@ -16,6 +16,16 @@
 // S has two buffers in TMEM and K and V have barriers of their own, so the scores of the
 // next two pages are computed while the softmax of the current one runs; two CTAs share
 // an SM (96 KB of shared memory and 256 TMEM columns each) and fill each other's gaps.
+// The CTAs are persistent and walk the (head, sequence, tile) triples back and forth.
+//
+// Measured on one CTA with clock marks (2,048 tokens, head size 128): a page costs the MMA thread ~2,100
+// cycles, of which it is blocked issuing S for ~1,000 and P V for ~640 while the SM's other CTA does the same:
+// the tensor core with its operand fetches is what the two CTAs queue for.  Two variants that feed it
+// differently were built and measured slower at every length and are not kept: two heads of a kv head per
+// CTA with Q in tensor memory and K/V shared (one S buffer per head left the softmax warps idle during the
+// head's own products: 748 against 588 us at 8,192 tokens), and one CTA per SM with Q in tensor memory, two
+// pages per step and four threads per row (its 128 x 128 x 16 MMAs took ~130 cycles each, twice their
+// arithmetic: 83 against 63 us at 2,048 tokens, 887 against 1,113 TFLOP/s at 32,768).
 //
 // Arithmetic as infer/forward.odin:88-115 (scale 1/sqrt(hd), causal bound t <= pos,
 // maximum-subtracted softmax, weighted sum of values), in 32-bit except the bfloat16
