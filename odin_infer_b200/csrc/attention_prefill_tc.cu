@@ -84,6 +84,9 @@ constexpr float RESCALE_LAG = 8.0f;
 __device__ unsigned long long* odin_attn_clk = nullptr;
 #endif
 
+// The persistent CTAs' work counter and the count of CTAs that have left (see the kernel).
+__device__ unsigned int g_prefill_next = 0, g_prefill_done = 0;
+
 template <int HD>
 __global__ void __launch_bounds__(320, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -128,17 +131,25 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     tc::fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    // The CTAs are persistent (two per SM) and walk the (head, sequence, tile) triples themselves: the triples are
-    // numbered with the tile level slowest and backwards (a sequence's latest, heaviest tiles first), and CTA c takes
-    // numbers c, 2G-1-c, 2G+c, 4G-1-c, ... (G CTAs): back and forth, so that whoever took a heavy tile takes a light one
-    // next.  Left to the hardware's block scheduler, a grid of one CTA per triple kept an SM's second place empty
-    // until both of its first CTAs had ended (measured: the second wave of a 2,048-token prompt began at 41 of 67 us,
-    // although CTAs had been ending since 26 us).
+    // The CTAs are persistent (two per SM) and take the (head, sequence, tile) triples themselves: the triples are
+    // numbered with the tile level slowest and backwards (every sequence's latest, heaviest tiles first); a CTA
+    // starts with the triple of its own number and then draws the next free number from a counter, so that unequal
+    // sequences of a batch balance out.  Left to the hardware's block scheduler, a grid of one CTA per triple kept
+    // an SM's second place empty until both of its first CTAs had ended (measured: the second wave of a 2,048-token
+    // prompt began at 41 of 67 us, although CTAs had been ending since 26 us).  The counter lives in the library's
+    // device image and is back at zero when the kernel ends (the last CTA out resets it), so the launches of a
+    // process that use it must not overlap on the GPU: one stream, or events between streams.
     const long long total = (long long)p.n_heads * p.n_seqs * p.n_tile_levels;
-    bool first_item = true;
-    for (long long base = 0, round = 0; base < total; base += gridDim.x, ++round) {
-    const long long w = (round & 1) ? base + ((long long)gridDim.x - 1 - blockIdx.x) : base + blockIdx.x;
-    if (w >= total) continue;
+    int* s_item = reinterpret_cast<int*>(tmem_slot + 2);
+    bool first_item = true, first_ticket = true;
+    for (;;) {
+    if (threadIdx.x == 0)
+        *s_item = first_ticket ? (int)blockIdx.x : (int)(gridDim.x + atomicAdd(&g_prefill_next, 1u));
+    first_ticket = false;
+    __syncthreads();
+    const long long w = *s_item;
+    __syncthreads();   // all have read the number before it is drawn again
+    if (w >= total) break;
     const int h = (int)(w % p.n_heads), seq = (int)((w / p.n_heads) % p.n_seqs);
     const int level = (int)(w / ((long long)p.n_heads * p.n_seqs));
     const int tok0 = p.seq_start[seq], n_new = p.seq_start[seq + 1] - tok0;
@@ -391,7 +402,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     }  // the next triple
 
     odin_trace_mark(9);  // the CTA's work is done (trace builds only)
-    if (threadIdx.x == 0 && *abort_flag && p.error != nullptr) atomicCAS(p.error, 0, 99);
+    if (threadIdx.x == 0) {
+        if (*abort_flag && p.error != nullptr) atomicCAS(p.error, 0, 99);
+        if (atomicAdd(&g_prefill_done, 1u) == gridDim.x - 1) {  // the last CTA out: the counters start from zero again
+            g_prefill_next = 0;
+            g_prefill_done = 0;
+            __threadfence();
+        }
+    }
     if (warp == 1) {
         tc::fence_after_sync();
         tc::tmem_dealloc(tmem_base, TMEM_COLS);
@@ -422,6 +440,7 @@ int launch_prefill_tc(const CUtensorMap& mk, const CUtensorMap& mv, const Prefil
     PrefillTcParams q = p;
     q.n_heads = p.Hq; q.n_seqs = n_seqs; q.n_tile_levels = (max_new + BQT - 1) / BQT;
     const long long total = (long long)q.n_heads * q.n_seqs * q.n_tile_levels;
+    if (total > (1LL << 30)) return ODIN_ERR_UNSUPPORTED;  // the work counter is 32 bits wide
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -482,6 +501,12 @@ extern "C" int odin_attention_prefill_tc_error() {
     if (f == nullptr) return 0;
     int v = 0;
     if (cudaMemcpy(&v, f, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-    if (v) cudaMemset(f, 0, 32 * sizeof(int));
+    if (v) {
+        cudaMemset(f, 0, 32 * sizeof(int));
+        // a launch that gave up may have left the work counters anywhere
+        const unsigned int zero = 0;
+        cudaMemcpyToSymbol(g_prefill_next, &zero, sizeof(zero));
+        cudaMemcpyToSymbol(g_prefill_done, &zero, sizeof(zero));
+    }
     return v;
 }

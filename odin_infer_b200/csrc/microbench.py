@@ -50,7 +50,7 @@ def paged(batch: int, ctx: int, n_kv: int, hd: int):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm", "decode-attention", "prefill-attention", "add-rmsnorm"])
+    ap.add_argument("kernel", choices=["gemm", "decode-attention", "prefill-attention", "add-rmsnorm", "head-prep"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=24576)
     ap.add_argument("--k", type=int, default=4096)
@@ -117,6 +117,21 @@ def main(argv=None) -> int:
                     args.iters)
         ops.attention_prefill_check()
         out.update(tokens=T, us=round(ms * 1e3, 2), tflops=round(4 * hq * hd * (T * (T + 1) / 2) / ms / 1e9, 1))
+    elif args.kernel == "head-prep":
+        # the prompt's head preparation: per-head norm of q and k, rotation, cache write, from a bfloat16 projection
+        T, hq, hkv, hd = args.tokens, args.heads, args.kv_heads, args.head_dim
+        k, v, bt = paged(1, T, hkv, hd)
+        width = (hq + 2 * hkv) * hd
+        qkv = torch.randn(T, width, device=DEV).bfloat16()
+        q_out = torch.empty(T, hq * hd, device=DEV, dtype=torch.bfloat16)
+        qn = torch.ones(hd, device=DEV).bfloat16()
+        ang = torch.rand(T, hd // 2, device=DEV)
+        cos, sin = torch.cos(ang), torch.sin(ang)
+        pos = torch.arange(T, dtype=torch.int32, device=DEV)
+        seq = torch.zeros(T, dtype=torch.int32, device=DEV)
+        ms = timeit(lambda: ops.head_prep(qkv, hq, hkv, hd, qn, qn, 1e-6, cos, sin, hd, pos, seq, bt, k, v, write_kv=True,
+                                          q_out=q_out), args.iters)
+        out.update(tokens=T, us=round(ms * 1e3, 2), gbs=round(2 * T * width * 2 / ms / 1e6, 1))
     else:
         n, d, s = args.rows, args.width, max(args.split, 1)
         x = torch.randn(n, d, device=DEV)
