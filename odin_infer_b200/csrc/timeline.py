@@ -28,6 +28,8 @@ def main(argv=None) -> int:
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--intermediate", type=int, default=12288)
     ap.add_argument("--vocab", type=int, default=151936)
+    ap.add_argument("--blocks", type=int, default=0, metavar="GRID",
+                    help="also print, block by block, the marks of the first kernel of the last layer whose grid has this size")
     args = ap.parse_args(argv)
     import numpy as np
     import torch
@@ -93,6 +95,7 @@ def main(argv=None) -> int:
                     break
         elif k is not None:
             k["marks"].setdefault(int(point[i]), []).append(us[i])
+            k.setdefault("by_block", {}).setdefault(int(blk[i]), {})[int(point[i])] = us[i]
     names = {2: "first item's MMAs issued / loads back", 3: "last commit / sum known", 4: "stores issued / end", 5: "last tile stored",
              6: "all loads requested"}
     print(f"records {n}; batch {args.batch}, {args.layers} layers; times in us from the step's first mark")
@@ -108,6 +111,14 @@ def main(argv=None) -> int:
         print(f"{k['sig'][0]:6d} {k['sig'][1]:5d} | {min(k['start']):11.2f} {max(k['start']):10.2f} | {go:8.2f} | "
               f"{(go - prev) if prev is not None else 0.0:6.2f} | {extra}")
         prev = go
+    if args.blocks:
+        picked = [k for k in kernels if k["sig"][0] == args.blocks and k.get("go") and k.get("by_block")]
+        if picked:
+            k = picked[-2] if len(picked) > 1 else picked[-1]  # the last one of the size is the head when the sizes agree
+            go = min(k["go"])
+            print(f"blocks of the kernel with grid {args.blocks} that went at {go:.2f}: block: mark=us after go ...")
+            for b in sorted(k["by_block"]):
+                print(f"{b:5d}: " + " ".join(f"{p}={v - go:.1f}" for p, v in sorted(k["by_block"][b].items())))
     return 0
 
 
