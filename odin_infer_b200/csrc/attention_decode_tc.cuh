@@ -118,6 +118,88 @@ struct DecodeTcSmem {
     static_assert(SLOTS <= 7, "barriers and the flag share 64 bytes");
 };
 
+// One page (64 keys) of one warp's online softmax: S = Q K^T, the running maximum and sum, O += P V.
+// sK_u, sV_u: the page's key and value tiles in shared memory (tile_off layout); qa: the warp's query
+// fragments (16 rows x HD); keys outside [t_lo, t_hi) are masked; page_key0: position of the page's first key.
+template <int HD>
+__device__ __forceinline__ void attend_page(const uint32_t sK_u, const uint32_t sV_u, const uint32_t (&qa)[HD / 16][4],
+                                            float (&o)[HD / 8][4], float (&m_run)[2], float (&l_run)[2],
+                                            const int page_key0, const int t_lo, const int t_hi, const float scale_log2,
+                                            const int lane) {
+    using namespace attn;
+    constexpr int KB = HD / 16, NB_O = HD / 8;
+    // S = Q K^T for the page's 64 keys: eight blocks of eight keys
+    float s[8][4];
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[nb][j] = 0.f;
+#pragma unroll
+    for (int kb = 0; kb < KB; ++kb) {
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+            uint32_t b[4];
+            ldmatrix_x4(b, sK_u + tile_off(np * 16 + (lane & 7) + ((lane >> 4) << 3), kb * 16 + ((lane >> 3) & 1) * 8));
+            mma_bf16(s[2 * np], qa[kb], b[0], b[1]);
+            mma_bf16(s[2 * np + 1], qa[kb], b[2], b[3]);
+        }
+    }
+    const int key0 = page_key0 + (lane & 3) * 2;
+    float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int tk = key0 + nb * 8 + (j & 1);
+            float v = s[nb][j] * scale_log2;
+            if (tk < t_lo || tk >= t_hi) v = -CUDART_INF_F;
+            s[nb][j] = v;
+            mx[j >> 1] = fmaxf(mx[j >> 1], v);
+        }
+    }
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m_run[r], mx[r]);
+        m_use[r] = (m_new == -CUDART_INF_F) ? 0.f : m_new;
+        corr[r] = exp2f(m_run[r] - m_use[r]);
+        m_run[r] = m_new;
+        l_run[r] *= corr[r];
+    }
+#pragma unroll
+    for (int nb = 0; nb < 8; ++nb) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float pv = exp2f(s[nb][j] - m_use[j >> 1]);
+            s[nb][j] = pv;
+            l_run[j >> 1] += pv;
+        }
+    }
+#pragma unroll
+    for (int n = 0; n < NB_O; ++n) {
+        o[n][0] *= corr[0]; o[n][1] *= corr[0];
+        o[n][2] *= corr[1]; o[n][3] *= corr[1];
+    }
+    // O += P V, sixteen keys at a time
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+        uint32_t pf[4];
+        pf[0] = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
+        pf[1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
+        pf[2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
+        pf[3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+#pragma unroll
+        for (int nb2 = 0; nb2 < NB_O / 2; ++nb2) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, sV_u + tile_off(ks * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), nb2 * 16 + (lane >> 4) * 8));
+            mma_bf16(o[2 * nb2], pf, b[0], b[1]);
+            mma_bf16(o[2 * nb2 + 1], pf, b[2], b[3]);
+        }
+    }
+}
+
 // PREP 0: q is given and the cache is complete.  PREP 1 (32-bit parts) and 2 (bfloat16): the
 // kernel prepares its own heads (per-head RMSNorm and rotation, as head_prep.cu does): every
 // CTA its query heads, and the CTA whose pages include the newest one that token's key and
@@ -306,76 +388,7 @@ __device__ __forceinline__ void attn_decode_tc_body(const CUtensorMap& map_k, co
                 __syncwarp();
             }
         }
-        // S = Q K^T for the page's 64 keys: eight blocks of eight keys
-        float s[8][4];
-#pragma unroll
-        for (int nb = 0; nb < 8; ++nb)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) s[nb][j] = 0.f;
-#pragma unroll
-        for (int kb = 0; kb < KB; ++kb) {
-#pragma unroll
-            for (int np = 0; np < 4; ++np) {
-                uint32_t b[4];
-                ldmatrix_x4(b, sK_u + tile_off(np * 16 + (lane & 7) + ((lane >> 4) << 3), kb * 16 + ((lane >> 3) & 1) * 8));
-                mma_bf16(s[2 * np], qa[kb], b[0], b[1]);
-                mma_bf16(s[2 * np + 1], qa[kb], b[2], b[3]);
-            }
-        }
-        const int key0 = pg * PAGE_T + (lane & 3) * 2;
-        float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
-#pragma unroll
-        for (int nb = 0; nb < 8; ++nb) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int tk = key0 + nb * 8 + (j & 1);
-                float v = s[nb][j] * p.scale_log2;
-                if (tk < t_lo || tk >= t_hi) v = -CUDART_INF_F;
-                s[nb][j] = v;
-                mx[j >> 1] = fmaxf(mx[j >> 1], v);
-            }
-        }
-        float corr[2], m_use[2];
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-            const float m_new = fmaxf(m_run[r], mx[r]);
-            m_use[r] = (m_new == -CUDART_INF_F) ? 0.f : m_new;
-            corr[r] = exp2f(m_run[r] - m_use[r]);
-            m_run[r] = m_new;
-            l_run[r] *= corr[r];
-        }
-#pragma unroll
-        for (int nb = 0; nb < 8; ++nb) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float pv = exp2f(s[nb][j] - m_use[j >> 1]);
-                s[nb][j] = pv;
-                l_run[j >> 1] += pv;
-            }
-        }
-#pragma unroll
-        for (int n = 0; n < NB_O; ++n) {
-            o[n][0] *= corr[0]; o[n][1] *= corr[0];
-            o[n][2] *= corr[1]; o[n][3] *= corr[1];
-        }
-        // O += P V, sixteen keys at a time
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-            uint32_t pf[4];
-            pf[0] = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
-            pf[1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
-            pf[2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
-            pf[3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
-#pragma unroll
-            for (int nb2 = 0; nb2 < NB_O / 2; ++nb2) {
-                uint32_t b[4];
-                ldmatrix_x4_trans(b, sV_u + tile_off(ks * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), nb2 * 16 + (lane >> 4) * 8));
-                mma_bf16(o[2 * nb2], pf, b[0], b[1]);
-                mma_bf16(o[2 * nb2 + 1], pf, b[2], b[3]);
-            }
-        }
+        attend_page<HD>(sK_u, sV_u, qa, o, m_run, l_run, pg * PAGE_T, t_lo, t_hi, p.scale_log2, lane);
         __syncwarp();  // every lane is done with the slot
         if (lane == 0 && i + SLOTS < n_here) issue(i + SLOTS, slot);
     }

@@ -523,6 +523,114 @@ def test_attention_decode_with_head_prep_equals_the_two_kernels(geom, parts):
     ops.attention_decode_check()
 
 
+@pytest.mark.parametrize("geom", [(32, 8, 128), (16, 8, 64), (8, 8, 128)])
+@pytest.mark.parametrize("window", [0, 100])
+def test_attention_decode_of_more_items_than_ctas(geom, window):
+    """Many more (sequence, kv head, split) items than CTAs fit on the GPU at once (980 to 4,900 for 296 places):
+    sequences of 1 token to 11 pages in a shuffled order (items of one page, items whose last page is full or just
+    begun, splits that find no page), padding rows, one key per sequence that carries all the weight; against the
+    direct kernel; and a row's result is the same bits whatever else is in the batch (a few rows alone run with
+    the deep ring of one CTA per SM)."""
+    from odin_infer_b200.csrc import ops
+    n_q, n_kv, hd = geom
+    g = n_q // n_kv
+    torch.manual_seed(17 + hd + window)
+    lengths = [1, 64, 65, 128, 129, 200, 641, 700] + [int(x) for x in torch.randint(1, 700, (112,))]
+    B = len(lengths)
+    k_cache, v_cache, bt = paged_cache(B, lengths, n_kv, hd, torch.bfloat16)
+    far_vals = []
+    for s, n in enumerate(lengths):
+        keys = 0.1 * torch.randn(n, n_kv, hd, device=DEV)
+        vals = torch.randn(n, n_kv, hd, device=DEV)
+        lo = max(0, n - window) if window else 0
+        far = lo + (s * 37) % (n - lo)           # a visible key, anywhere in the sequence
+        keys[far] = 0.0
+        keys[far, :, 0] = 40.0
+        far_vals.append(vals[far].bfloat16().float())
+        pages = bt[s, : (n + 63) // 64].long()
+        pad = pages.numel() * 64 - n
+        kp = torch.cat([keys, torch.full((pad, n_kv, hd), float('nan'), device=DEV)]).view(-1, 64, n_kv, hd).permute(0, 2, 1, 3)
+        vp = torch.cat([vals, torch.full((pad, n_kv, hd), float('nan'), device=DEV)]).view(-1, 64, n_kv, hd).permute(0, 2, 1, 3)
+        k_cache[pages] = kp.bfloat16()
+        v_cache[pages] = vp.bfloat16()
+    order = torch.randperm(B).tolist()
+    order[5:5] = [-1]
+    order[60:60] = [-1, -1]
+    T = len(order)
+    tok_seq = torch.tensor(order, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([lengths[s] - 1 if s >= 0 else 0 for s in order], dtype=torch.int32, device=DEV)
+    q = 0.1 * torch.randn(T, n_q, hd, device=DEV)
+    q[:, :, 0] = 40.0 / math.sqrt(hd) * 2
+    qf = q.reshape(T, n_q * hd).bfloat16()
+    ref = torch.full((T, n_q * hd), 7.0, device=DEV, dtype=torch.bfloat16)
+    ops.attention_plain(qf, ref, n_q, n_kv, hd, k_cache, v_cache, tok_pos, tok_seq, bt, window)
+    few = [3, 4, 9, 10, 61, 62, 63]            # rows (some of them padding) run again as a small batch: one CTA per item
+    for n_split in (1, 2, 5):
+        out = torch.full_like(ref, 7.0)
+        scratch = torch.empty(ops.attention_decode_scratch(T, n_q, hd, n_split), device=DEV)
+        for _ in range(2):
+            ops.attention_decode(qf, out, n_q, n_kv, hd, k_cache, v_cache, tok_pos, tok_seq, bt, window, scratch, n_split)
+        ops.attention_decode_check()
+        close(out.float(), ref.float(), 1e-2)
+        for r, s in enumerate(order):
+            if s < 0:
+                assert torch.equal(out[r], torch.full_like(out[r], 7.0)), "a padding row must not be written"
+            else:
+                close(out[r].float().view(n_kv, g, hd)[:, 0], far_vals[s], 2e-2)
+        sub = torch.full((len(few), n_q * hd), 7.0, device=DEV, dtype=torch.bfloat16)
+        ops.attention_decode(qf[few].contiguous(), sub, n_q, n_kv, hd, k_cache, v_cache, tok_pos[few].contiguous(),
+                             tok_seq[few].contiguous(), bt, window, scratch, n_split)
+        assert torch.equal(sub, out[few]), "a row's result depends on the rest of the batch"
+    ops.attention_decode_check()
+
+
+@pytest.mark.parametrize("geom", [(32, 8, 128), (16, 8, 64)])
+@pytest.mark.parametrize("parts", [0, 3])
+def test_attention_decode_of_more_items_than_ctas_with_head_prep(geom, parts):
+    """The same many items with head preparation inside the kernel, against head preparation followed by decode
+    attention: the same bits in the output and in the cache."""
+    from odin_infer_b200.csrc import ops
+    n_q, n_kv, hd = geom
+    torch.manual_seed(23 + hd + parts)
+    lengths = [1, 64, 65, 128, 129, 200, 641, 700] + [int(x) for x in torch.randint(1, 700, (112,))]
+    B = len(lengths)
+    k_cache, v_cache, bt = paged_cache(B, lengths, n_kv, hd, torch.bfloat16)
+    for s, n in enumerate(lengths):  # everything but the newest token is in the cache already
+        pages = bt[s, : (n + 63) // 64].long()
+        k_cache[pages] = torch.randn(pages.numel(), n_kv, 64, hd, device=DEV).bfloat16()
+        v_cache[pages] = torch.randn(pages.numel(), n_kv, 64, hd, device=DEV).bfloat16()
+        last = int(pages[-1])
+        k_cache[last, :, (n - 1) % 64:] = float("nan")   # the newest token's place and what lies behind it
+        v_cache[last, :, (n - 1) % 64:] = float("nan")
+    order = torch.randperm(B).tolist()
+    order[7:7] = [-1]
+    tok_seq = torch.tensor(order, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([lengths[s] - 1 if s >= 0 else 0 for s in order], dtype=torch.int32, device=DEV)
+    T, width = len(order), (n_q + 2 * n_kv) * hd
+    qkv = torch.randn(T, width, device=DEV).bfloat16() if parts == 0 else torch.randn(parts, T, width, device=DEV) / math.sqrt(parts)
+    q_norm = (1 + 0.1 * torch.randn(hd, device=DEV)).bfloat16()
+    k_norm = (1 + 0.1 * torch.randn(hd, device=DEV)).bfloat16()
+    ang = torch.arange(800, device=DEV, dtype=torch.float32)[:, None] * (1.0 / 10000 ** (torch.arange(hd // 2, device=DEV) / (hd // 2)))[None, :]
+    cos, sin = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
+    for n_split in (1, 3):
+        ka, va, kb, vb = k_cache.clone(), v_cache.clone(), k_cache.clone(), v_cache.clone()
+        scratch = torch.empty(ops.attention_decode_scratch(T, n_q, hd, n_split), device=DEV)
+        q = ops.head_prep(qkv.clone(), n_q, n_kv, hd, q_norm, k_norm, 1e-6, cos, sin, hd, tok_pos, tok_seq, bt, ka, va,
+                          q_out=torch.empty(T, n_q * hd, device=DEV, dtype=torch.bfloat16))
+        ref = torch.full((T, n_q * hd), 7.0, device=DEV, dtype=torch.bfloat16)
+        ops.attention_decode(q, ref, n_q, n_kv, hd, ka, va, tok_pos, tok_seq, bt, 0, scratch, n_split)
+        out = torch.full_like(ref, 7.0)
+        assert ops.attention_decode_fused(qkv, out, n_q, n_kv, hd, q_norm, k_norm, 1e-6, cos, sin, hd, kb, vb,
+                                          tok_pos, tok_seq, bt, 0, scratch, n_split)
+        assert not torch.isnan(out.float()).any()
+        assert torch.equal(out, ref)
+        for s, n in enumerate(lengths):  # the newest token's key and value, bit for bit
+            page, row = int(bt[s, (n - 1) // 64]), (n - 1) % 64
+            assert torch.equal(ka[page, :, row], kb[page, :, row]) and torch.equal(va[page, :, row], vb[page, :, row])
+            assert not torch.isnan(kb[page, :, row].float()).any()
+    ops.attention_decode_check()
+
+
 @pytest.mark.parametrize("hd,n,far", [(64, 300, 67), (128, 9000, 70), (128, 9000, 8191), (128, 8300, 4096), (64, 8193, 8128)])
 def test_attention_decode_window_and_far_key(hd, n, far):
     """One key among hundreds or thousands is made to dominate; whichever page, warp or key split it
