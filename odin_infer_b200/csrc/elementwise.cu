@@ -73,12 +73,10 @@ __device__ __forceinline__ float4 load4w(const VecRef& w, int j) {
 // The loads of a group are issued together (eight parts at a time), so that a row costs
 // one trip to memory and not one per part; the weights of the first group and the row
 // number, which no earlier kernel writes, are fetched before the wait for that kernel.
-template <typename TD, typename TO, bool VEC, int MAX_THREADS = 512>
-__global__ void __launch_bounds__(MAX_THREADS, MAX_THREADS > 512 ? 1 : 3) add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_split,
-                                   size_t split_stride, VecRef w, float eps, TO* __restrict__ out,
-                                   const int* __restrict__ rows, int d) {
-    __shared__ float red[32];
-    extern __shared__ float rowbuf[];  // d floats
+template <typename TD, typename TO, bool VEC, int MAX_THREADS>
+__device__ __forceinline__ void add_rmsnorm_body(float* __restrict__ x, const TD* __restrict__ delta, int n_split,
+                                                 size_t split_stride, VecRef w, float eps, TO* __restrict__ out,
+                                                 const int* __restrict__ rows, int d, float* red, float* rowbuf) {
     pdl_trigger();
     const int r = blockIdx.x;
     int src = r;
@@ -98,7 +96,7 @@ __global__ void __launch_bounds__(MAX_THREADS, MAX_THREADS > 512 ? 1 : 3) add_rm
             float4 v = load4<float>(xr + j);
             if (delta != nullptr) {
                 const TD* dp = delta + (size_t)src * d + j;
-                constexpr int BATCH = MAX_THREADS > 512 ? 8 : 2;  // loads in flight per thread (registers)
+                constexpr int BATCH = MAX_THREADS > 512 ? 4 : 2;  // loads in flight per thread (registers)
                 for (int s0 = 0; s0 < n_split; s0 += BATCH) {
                     float4 dv[BATCH];
 #pragma unroll
@@ -145,6 +143,28 @@ __global__ void __launch_bounds__(MAX_THREADS, MAX_THREADS > 512 ? 1 : 3) add_rm
         }
     }
     odin_trace_mark(4);  // stores issued
+}
+
+template <typename TD, typename TO, bool VEC, int MAX_THREADS = 512>
+__global__ void __launch_bounds__(MAX_THREADS, 3)
+add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_split, size_t split_stride, VecRef w,
+                   float eps, TO* __restrict__ out, const int* __restrict__ rows, int d) {
+    __shared__ float red[32];
+    extern __shared__ float rowbuf[];  // d floats
+    add_rmsnorm_body<TD, TO, VEC, MAX_THREADS>(x, delta, n_split, split_stride, w, eps, out, rows, d, red, rowbuf);
+}
+
+// The variant of 1,024 threads for a few wide rows (decoding).  Its registers are capped so that a block leaves
+// more than a third of an SM's registers free: the product that follows starts its CTAs while this kernel runs, to
+// fetch weights, and on the SMs that hold a row it could not (with 64 registers a thread the block took them all;
+// those CTAs then started 4 to 7 us after the others and the whole product ended that much later).
+template <typename TD, typename TO>
+__global__ void __maxnreg__(40)
+add_rmsnorm_wide_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_split, size_t split_stride, VecRef w,
+                        float eps, TO* __restrict__ out, const int* __restrict__ rows, int d) {
+    __shared__ float red[32];
+    extern __shared__ float rowbuf[];  // d floats
+    add_rmsnorm_body<TD, TO, true, 1024>(x, delta, n_split, split_stride, w, eps, out, rows, d, red, rowbuf);
 }
 
 // Many rows (prompts), bfloat16 out: a block of 256 threads per row that keeps its NV groups of four
@@ -235,7 +255,7 @@ static int launch_add_rmsnorm(float* x, const void* delta, int n_split, size_t s
         // order in a prompt and in a decode step, and the 32-bit path's cuts agree bit for bit)
         const bool big = !std::is_same<TO, float>::value && d >= 4096 && n_rows <= 256;
         const int threads = big ? 1024 : (d >= 2048 ? 512 : (d >= 1024 ? 256 : 128));
-        auto kern = big ? add_rmsnorm_kernel<TD, TO, true, 1024> : add_rmsnorm_kernel<TD, TO, true, 512>;
+        auto kern = big ? add_rmsnorm_wide_kernel<TD, TO> : add_rmsnorm_kernel<TD, TO, true, 512>;
         if (smem > 48 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;

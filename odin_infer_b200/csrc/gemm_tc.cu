@@ -21,6 +21,14 @@
 // them in a fixed order.  Which part a CTA takes never depends on M, so a token's
 // result does not depend on what else is in the batch.
 //
+// Weights staged in tensor memory (mode 1, `staged` > 0).  A product of few tokens starts while the
+// kernel before it still runs and can fetch weights, but nothing else, until that kernel is done; its
+// ring of stages is full after ~3 us of the 3 to 9 us that it waits.  So the first `staged` K blocks of
+// the CTA's first item pass through the ring into tensor memory (tcgen05.cp, 32 columns a block beside
+// the accumulators), the ring fills again behind them, and when the wait ends up to 400 KB of the CTA's
+// weights are on the SM.  Their MMAs read A from tensor memory and the tokens' tiles, fetched after the
+// wait, from a small area of their own.  The K blocks are multiplied in the same order either way.
+//
 // In the reference this is the weight-times-activation product of every layer
 // (infer/matmul.odin:77-109, one row-dot per thread on the CPU; gemv kernels in
 // infer/metal.odin:76-109 on the GPU).
@@ -47,6 +55,7 @@ struct GemmParams {
     int n_split, kb_per_split, kb_total;
     int dual_offset;       // DUAL: first row of the second Y tile's matrix half
     int stages;            // length of the ring of stages (0: as many as fit)
+    int staged;            // mode 1: K blocks of a CTA's first item whose weights wait in tensor memory (see the kernel)
     int* error;            // set when a wait runs out
 };
 
@@ -119,12 +128,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t n_stages = (uint32_t)p.stages;  // at most C::STAGES: the ring may be shorter to leave shared memory to a neighbour
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + n_stages * C::STAGE);
+    const int n_staged = (MODE == 1) ? p.staged : 0;
+    uint8_t* y_staged = smem + n_stages * C::STAGE;  // [staged] token tiles of the K blocks whose weights wait in tensor memory
+    uint64_t* bars = reinterpret_cast<uint64_t*>(y_staged + n_staged * C::STAGE_Y1);
     uint64_t* full = bars;                        // [STAGES] TMA landed
     uint64_t* empty = bars + C::STAGES;           // [STAGES] MMAs that read the stage are done
     uint64_t* acc_full = bars + 2 * C::STAGES;    // [ACC_BUFS] accumulator complete
     uint64_t* acc_empty = acc_full + ACC_BUFS;    // [ACC_BUFS] accumulator read back
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_BUFS);
+    uint64_t* y_full = acc_empty + ACC_BUFS;      // the token tiles of the staged K blocks have landed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(y_full + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -139,18 +151,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             tc::mbar_init(&acc_full[a], 1);
             tc::mbar_init(&acc_empty[a], 4);  // one arrival per epilogue warp
         }
+        tc::mbar_init(y_full, 1);
         *abort_flag = 0;
         tc::fence_barrier_init();
         tc::prefetch_tensormap(&map_x);
         tc::prefetch_tensormap(&map_y);
     }
-    if (warp == 1) tc::tmem_alloc(tmem_slot, C::TMEM_COLS);
+    // with staged weights the CTA takes all of tensor memory: 32 columns a staged block beside the accumulators
+    const uint32_t tmem_cols = n_staged > 0 ? 512u : (uint32_t)C::TMEM_COLS;
+    if (warp == 1) tc::tmem_alloc(tmem_slot, tmem_cols);
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_staged = tmem_base + ACC_BUFS * C::ACC_W;
 
     const long long n_items = (long long)p.tiles_x * p.tiles_y * p.n_split;
+    // the CTA's first item: how many of its K blocks are staged (t_first), how many more the ring takes before the wait
+    int first_kb0 = 0, t_first = 0, r_first = 0, first_tx = 0, first_ty = 0;
+    if (MODE == 1 && (long long)blockIdx.x < n_items) {
+        const long long w = blockIdx.x;
+        const int s0 = (int)(w % p.n_split);
+        first_tx = (int)((w / p.n_split) % p.tiles_x);
+        first_ty = (int)((w / p.n_split) / p.tiles_x);
+        first_kb0 = s0 * p.kb_per_split;
+        const int nk = min(p.kb_total, first_kb0 + p.kb_per_split) - first_kb0;
+        t_first = min(n_staged, nk);
+        r_first = min((int)n_stages, nk - t_first);
+    }
 
     if (warp == 0) {
         // ------------------------------------------------------- TMA producer
@@ -159,20 +187,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             bool ok = true;
             // Weights are constant: in mode 1 (X = weights) the first stages of the first tile
             // are requested before the wait for the previous kernel, whose output is only Y.
-            int pre = 0;
+            int pre = 0;  // K blocks of the first item requested before the wait
             if (MODE == 1 && (long long)blockIdx.x < n_items) {
-                const long long w = blockIdx.x;
-                const int s = (int)(w % p.n_split);
-                const int tx = (int)((w / p.n_split) % p.tiles_x), ty = (int)((w / p.n_split) / p.tiles_x);
-                const int kb0 = s * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
-                pre = min((int)n_stages, kb1 - kb0);
-                for (int i = 0; i < pre; ++i) {
-                    tc::mbar_expect_tx(&full[i], C::STAGE);
-                    tc::tma_load_2d(smem + i * C::STAGE, &map_x, (kb0 + i) * BK, tx * BM, &full[i]);
+                // the staged blocks' weights: through the ring, which the MMA warp empties into tensor memory
+                for (int j = 0; j < t_first && ok; ++j) {
+                    if (!tc::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { report(p.error, 1, (int)blockIdx.x, first_kb0 + j, stage, MODE, BN); ok = false; break; }
+                    tc::mbar_expect_tx(&full[stage], C::STAGE_X);
+                    tc::tma_load_2d(smem + stage * C::STAGE, &map_x, (first_kb0 + j) * BK, first_tx * BM, &full[stage]);
+                    if (++stage == n_stages) { stage = 0; phase ^= 1; }
+                }
+                // then the ring's own blocks: their weights now, their tokens after the wait
+                const uint32_t stage_r = stage, phase_r = phase;
+                for (int i = 0; i < r_first && ok; ++i) {
+                    if (!tc::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { report(p.error, 1, (int)blockIdx.x, first_kb0 + t_first + i, stage, MODE, BN); ok = false; break; }
+                    tc::mbar_expect_tx(&full[stage], C::STAGE);
+                    tc::tma_load_2d(smem + stage * C::STAGE, &map_x, (first_kb0 + t_first + i) * BK, first_tx * BM, &full[stage]);
+                    if (++stage == n_stages) { stage = 0; phase ^= 1; }
                 }
                 pdl_wait();
-                for (int i = 0; i < pre; ++i)
-                    tc::tma_load_2d(smem + i * C::STAGE + C::STAGE_X, &map_y, (kb0 + i) * BK, ty * BN, &full[i]);
+                if (ok) {
+                    if (t_first > 0) {
+                        tc::mbar_expect_tx(y_full, (uint32_t)t_first * C::STAGE_Y1);
+                        for (int j = 0; j < t_first; ++j)
+                            tc::tma_load_2d(y_staged + j * C::STAGE_Y1, &map_y, (first_kb0 + j) * BK, first_ty * BN, y_full);
+                    }
+                    uint32_t st = stage_r;
+                    for (int i = 0; i < r_first; ++i) {
+                        tc::tma_load_2d(smem + st * C::STAGE + C::STAGE_X, &map_y, (first_kb0 + t_first + i) * BK, first_ty * BN, &full[st]);
+                        if (++st == n_stages) st = 0;
+                    }
+                }
+                (void)phase_r;
+                pre = t_first + r_first;
             } else {
                 pdl_wait();
             }
@@ -181,12 +227,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 const long long rest = w / p.n_split;
                 const int tx = (int)(rest % p.tiles_x), ty = (int)(rest / p.tiles_x);
                 const int kb0 = s * p.kb_per_split, kb1 = min(p.kb_total, kb0 + p.kb_per_split);
-                for (int kb = kb0; kb < kb1; ++kb) {
-                    if (pre > 0) {  // already requested above
-                        --pre;
-                        if (++stage == n_stages) { stage = 0; phase ^= 1; }
-                        continue;
-                    }
+                for (int kb = kb0 + pre; kb < kb1; ++kb) {
                     if (!tc::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { report(p.error, 1, (int)w, kb, stage, MODE, BN); ok = false; break; }
                     uint8_t* sx = smem + stage * C::STAGE;
                     uint8_t* sy = sx + C::STAGE_X;
@@ -196,6 +237,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     if (DUAL) tc::tma_load_2d(sy + C::STAGE_Y1, &map_y, kb * BK, p.dual_offset + ty * BN, &full[stage]);
                     if (++stage == n_stages) { stage = 0; phase ^= 1; }
                 }
+                pre = 0;
             }
             odin_trace_mark(6, true);  // every load of this CTA is requested
             if (!ok) {
@@ -217,6 +259,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             uint32_t stage = 0, phase = 0;
             uint32_t local = 0;
             bool ok = true;
+            // the staged blocks' weights: from the ring into tensor memory as they land, before the wait ends
+            for (int j = 0; j < t_first && ok; ++j) {
+                ok = __all_sync(0xffffffffu, tc::mbar_wait(&full[stage], phase, abort_flag));
+                if (!ok) { if (lane == 0) report(p.error, 3, (int)blockIdx.x, first_kb0 + j, stage, MODE, BN); break; }
+                tc::fence_after_sync();
+                if (tc::elect_one()) {
+                    const uint64_t dx = tc::make_smem_desc_sw128(tc::smem_u32(smem + stage * C::STAGE));
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) tc::tmem_cp_128x256b(tmem_staged + 32 * j + 8 * k, dx + 2 * k);
+                    tc::umma_commit(&empty[stage]);
+                }
+                __syncwarp();
+                if (++stage == n_stages) { stage = 0; phase ^= 1; }
+            }
             pdl_wait();  // nothing can be multiplied before the previous kernel's output exists: sleep, do not spin
             bool ready = false;
             for (long long w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++local) {
@@ -227,7 +283,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 if (!ok) { if (lane == 0) report(p.error, 2, (int)w, -1, (int)acc, MODE, BN); break; }
                 tc::fence_after_sync();
                 const uint32_t tmem_d = tmem_base + acc * C::ACC_W;
-                for (int kb = kb0; kb < kb1; ++kb) {
+                int staged_here = 0;
+                if (local == 0 && t_first > 0) {
+                    // the staged blocks: A from tensor memory, the tokens' tiles from their own area
+                    ok = __all_sync(0xffffffffu, tc::mbar_wait(y_full, 0, abort_flag));
+                    if (!ok) { if (lane == 0) report(p.error, 3, (int)w, kb0, -1, MODE, BN); break; }
+                    tc::fence_after_sync();
+                    if (tc::elect_one()) {
+                        for (int j = 0; j < t_first; ++j) {
+                            const uint64_t dy = tc::make_smem_desc_sw128(tc::smem_u32(y_staged + j * C::STAGE_Y1));
+#pragma unroll
+                            for (int k = 0; k < BK / UMMA_K; ++k)
+                                tc::umma_bf16_ts(tmem_d, tmem_staged + 32 * j + 8 * k, dy + 2 * k, idesc, (j > 0 || k > 0) ? 1u : 0u);
+                        }
+                    }
+                    __syncwarp();
+                    staged_here = t_first;
+                }
+                for (int kb = kb0 + staged_here; kb < kb1; ++kb) {
                     if (!ready) ready = tc::mbar_wait(&full[stage], phase, abort_flag);
                     ok = __all_sync(0xffffffffu, ready);
                     if (!ok) { if (lane == 0) report(p.error, 3, (int)w, kb, stage, MODE, BN); break; }
@@ -367,7 +440,59 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if (threadIdx.x == 0 && *abort_flag && p.error != nullptr) atomicCAS(p.error, 0, 99);
     if (warp == 1) {
         tc::fence_after_sync();
-        tc::tmem_dealloc(tmem_base, C::TMEM_COLS);
+        tc::tmem_dealloc(tmem_base, tmem_cols);
+    }
+}
+
+// A tile of 128 x 64 bfloat16 through TMA into shared memory, from there by tcgen05.cp into tensor memory,
+// and back out through tcgen05.ld: out[row][c] must be the row's elements 2c and 2c + 1 (the layout in which
+// an MMA reads its A operand from tensor memory).  Checks the copy that stages weights in tensor memory.
+__global__ void __launch_bounds__(128, 1)
+stage_probe_kernel(const __grid_constant__ CUtensorMap map_x, uint32_t* __restrict__ out, int* error) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + BM * BK * 2);
+    uint64_t* done = full + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        tc::mbar_init(full, 1);
+        tc::mbar_init(done, 1);
+        *abort_flag = 0;
+        tc::fence_barrier_init();
+    }
+    if (warp == 0) tc::tmem_alloc(tmem_slot, 32);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) {
+        tc::mbar_expect_tx(full, BM * BK * 2);
+        tc::tma_load_2d(smem, &map_x, 0, 0, full);
+        if (tc::mbar_wait(full, 0, abort_flag)) {
+            tc::fence_after_sync();
+            const uint64_t dx = tc::make_smem_desc_sw128(tc::smem_u32(smem));
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) tc::tmem_cp_128x256b(tmem_base + 8 * k, dx + 2 * k);
+        }
+        tc::umma_commit(done);
+    }
+    const bool ok = tc::mbar_wait(done, 0, abort_flag);
+    tc::fence_after_sync();
+    if (ok) {
+        uint32_t r[32];
+        tc::tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16), r);
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) out[(size_t)(warp * 32 + lane) * 32 + c] = r[c];
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag && error != nullptr) atomicCAS(error, 0, 98);
+    if (warp == 0) {
+        tc::fence_after_sync();
+        tc::tmem_dealloc(tmem_base, 32);
     }
 }
 
@@ -459,9 +584,11 @@ template <int BN, int MODE, typename TO, bool DUAL = false>
 int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, cudaStream_t s) {
     using C = Cfg<BN, DUAL>;
     auto kern = gemm_tc_kernel<BN, MODE, TO, DUAL>;
+    constexpr int MOST_SMEM = 227 * 1024;  // what a CTA may ask for at all
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             MODE == 1 ? MOST_SMEM : C::SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
@@ -469,7 +596,21 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, cu
     const int grid = (int)(items < sm_count() ? items : sm_count());
     GemmParams q = p;
     q.stages = (p.stages >= 2 && p.stages < C::STAGES) ? p.stages : C::STAGES;
-    const size_t smem = (size_t)C::SMEM - (size_t)(C::STAGES - q.stages) * C::STAGE;
+    // staged blocks: as many as asked for, as tensor memory has columns for beside the accumulators, and as
+    // shared memory has room for their token tiles
+    q.staged = 0;
+    if (MODE == 1 && !DUAL && p.staged > 0) {
+        const int by_tmem = (512 - ACC_BUFS * C::ACC_W) / 32;
+        const int by_smem = (MOST_SMEM - (C::SMEM - (C::STAGES - q.stages) * C::STAGE)) / C::STAGE_Y1;
+        q.staged = p.staged < by_tmem ? p.staged : by_tmem;
+        if (q.staged > by_smem) q.staged = by_smem;
+        if (q.staged < 0) q.staged = 0;
+    }
+    size_t smem = (size_t)C::SMEM - (size_t)(C::STAGES - q.stages) * C::STAGE + (size_t)q.staged * C::STAGE_Y1;
+    // A CTA with staged weights holds all of tensor memory; a second one on the same SM would sit in its
+    // allocation until the first is gone instead of fetching weights (measured: the step 14 % slower).  It asks
+    // for more than half of an SM's shared memory, so no two of them ever share an SM.
+    if (q.staged > 0 && smem < (size_t)117 * 1024) smem = (size_t)117 * 1024;
     odin_launch(kern, dim3(grid), dim3(192), smem, s, mx, my, q);
     ODIN_LAUNCH_CHECK();
     return 0;
@@ -496,9 +637,11 @@ int dispatch_bn(int bn, const CUtensorMap& mx, const CUtensorMap& my, const Gemm
 // of 8 elements and the pointers 16-byte aligned (TMA), else ODIN_ERR_UNSUPPORTED.
 // stages: the length of the ring of shared-memory stages; 0: as many as fit (the product then has the SM to
 // itself), fewer to let a CTA of the kernel before or after it share the SM.
+// staged (mode 1): K blocks of each CTA's first item whose weights wait in tensor memory while the kernel before
+// this one still runs (fewer where tensor or shared memory has no room for them); the result is the same bits.
 extern "C" int odin_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, long long lda,
                             long long ldw, long long ldc, int mode, int bn, int n_split, long long split_stride,
-                            int stages, void* stream) {
+                            int stages, int staged, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || n_split < 1) return ODIN_ERR_BAD_ARG;
     if ((lda % 8) || (ldw % 8) || (K % 8) || (((uintptr_t)A) & 15) || (((uintptr_t)W) & 15)) return ODIN_ERR_UNSUPPORTED;
@@ -516,6 +659,7 @@ extern "C" int odin_gemm_tc(const void* A, const void* W, void* C, int c_dtype, 
     p.n_split = n_split;
     p.dual_offset = 0;
     p.stages = stages;
+    p.staged = mode == 1 ? staged : 0;
     p.error = error_flag();
     CUtensorMap mx, my;
     int rc;
@@ -557,6 +701,7 @@ extern "C" int odin_gemm_tc_swiglu(const void* A, const void* W, void* C, int c_
     p.kb_per_split = p.kb_total;
     p.n_split = 1;
     p.stages = 0;
+    p.staged = 0;
     p.dual_offset = I;
     p.error = error_flag();
     p.rows_x = M;
@@ -571,6 +716,18 @@ extern "C" int odin_gemm_tc_swiglu(const void* A, const void* W, void* C, int c_
     if (c_dtype == ODIN_BF16) return launch<BN, 0, bf16, true>(mx, my, p, s);
     if (c_dtype == ODIN_F32) return launch<BN, 0, float, true>(mx, my, p, s);
     return ODIN_ERR_UNSUPPORTED;
+}
+
+// X: [128, 64] bfloat16, contiguous; out: [128, 32] 32-bit words (see stage_probe_kernel).
+extern "C" int odin_gemm_tc_stage_probe(const void* X, void* out, void* stream) {
+    if ((((uintptr_t)X) & 15) != 0) return ODIN_ERR_UNSUPPORTED;
+    CUtensorMap mx;
+    int rc;
+    if ((rc = make_map(&mx, X, BM, BK, BK, BM))) return rc;
+    const size_t smem = BM * BK * 2 + 1024 + 64;
+    stage_probe_kernel<<<1, 128, smem, (cudaStream_t)stream>>>(mx, (uint32_t*)out, error_flag());
+    ODIN_LAUNCH_CHECK();
+    return 0;
 }
 
 // The number of K parts that odin_gemm_tc will really use for (K, n_split).

@@ -167,7 +167,7 @@ def gemm_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, bn: int, n_split: int = 1,
-            stages: int = 0) -> None:
+            stages: int = 0, staged: int = 0) -> None:
     """out = a[M, K] @ w[N, K]^T on the tcgen05 tensor cores (bfloat16 in, 32-bit accumulation).
 
     mode 0: tokens on the 128-row side of the MMA, tiles of bn weight rows.
@@ -175,6 +175,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, bn: 
     n_split > 1: out is float32 [n_split, M, N]; slice s holds the partial sum of K part s.
     stages: length of the kernel's ring of shared-memory stages; 0: as many as fit, fewer to
     leave room on the SM for a CTA of the neighbouring kernel.
+    staged (mode 1): K blocks of every CTA's first item whose weights are fetched into tensor memory
+    while the kernel before this one still runs; changes no bit of the result.
     """
     M, K = a.shape
     N = w.shape[0]
@@ -191,7 +193,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int, bn: 
     _check(_fn("gemm_tc", "odin_gemm_tc")(
         _ptr(a), _ptr(w), _ptr(out), c_int(dtype_code(out.dtype)), c_int(M), c_int(N), c_int(K),
         c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(ldc), c_int(mode), c_int(bn), c_int(n_split),
-        c_longlong(stride), c_int(stages), _stream()), "gemm_tc")
+        c_longlong(stride), c_int(stages), c_int(staged), _stream()), "gemm_tc")
 
 
 def gemm_tc_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> None:

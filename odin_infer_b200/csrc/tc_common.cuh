@@ -251,6 +251,13 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, u
         : "memory");
 }
 
+// 128 rows x 256 bits from shared memory (a matrix descriptor as for an MMA operand, here one K step
+// of 16 bfloat16 of a K-major tile) into tensor memory: row m to lane m, eight 32-bit columns from
+// taddr on.  Asynchronous, in order with this thread's MMAs; tcgen05.commit tells when it is done.
+__device__ __forceinline__ void tmem_cp_128x256b(uint32_t taddr, uint64_t desc) {
+    asm volatile("tcgen05.cp.cta_group::1.128x256b [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+
 // The barrier gets one arrival when every MMA issued so far by this thread is done.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))

@@ -87,6 +87,7 @@ def main(argv=None) -> int:
                 open_k[sig] = k
             k["seen"].add(blk[i])
             k["start"].append(us[i])
+            k.setdefault("by_block", {}).setdefault(int(blk[i]), {})[0] = us[i]
         elif point[i] == 1:
             for kk in kernels:
                 if kk["sig"] == sig and blk[i] in kk["seen"] and blk[i] not in kk.setdefault("went", set()):
@@ -116,7 +117,7 @@ def main(argv=None) -> int:
         if picked:
             k = picked[-2] if len(picked) > 1 else picked[-1]  # the last one of the size is the head when the sizes agree
             go = min(k["go"])
-            print(f"blocks of the kernel with grid {args.blocks} that went at {go:.2f}: block: mark=us after go ...")
+            print(f"blocks of the kernel with grid {args.blocks} that went at {go:.2f}: block: mark=us after go ... (0: the block's start)")
             for b in sorted(k["by_block"]):
                 print(f"{b:5d}: " + " ".join(f"{p}={v - go:.1f}" for p, v in sorted(k["by_block"][b].items())))
     return 0

@@ -48,7 +48,11 @@ SWIGLU_FUSED_FROM = int(os.environ.get("ODIN_SWIGLU_FUSED_FROM", "129"))
 WIDE_CHUNKS_MAX_TOKENS = int(os.environ.get("ODIN_WIDE_CHUNKS_MAX_TOKENS", "1024"))  # measured: faster up to there
 
 # ring length of a product that shares the SM with a decode attention CTA (see Runtime.linear)
-LIGHT_STAGES = int(os.environ.get("ODIN_GEMM_LIGHT_STAGES", "6"))
+LIGHT_STAGES = int(os.environ.get("ODIN_GEMM_LIGHT_STAGES", "5"))
+
+# K blocks of a few-token product's weights that wait in tensor memory while the kernel before it still runs
+# (the kernel takes fewer where tensor or shared memory has no room); with the ring that is up to 400 KB an SM
+STAGED_BLOCKS = int(os.environ.get("ODIN_GEMM_STAGED", "15"))
 
 
 def context_class_of(longest: int, page: int = 64) -> int:
@@ -126,12 +130,15 @@ class Runtime:
                     out = self.empty(n_split, M, N, dtype=torch.float32) if n_split > 1 else self.empty(M, N, dtype=out_dtype)
                     ops.gemm_tc2_wide(a, w, out, n_split)
                     return out
+                # tiles of 64 tokens and more: their token tiles would take the ring's shared memory (measured at 64
+                # sequences: 4.82 to 5.28 ms a step with 5 to 12 blocks staged and the ring that much shorter, 4.80 without)
+                staged = STAGED_BLOCKS if bn <= 32 else 0
                 if n_split > 1:
                     out = self.empty(n_split, M, N, dtype=torch.float32)
-                    ops.gemm_tc(a, w, out, 1, bn, n_split, stages)
+                    ops.gemm_tc(a, w, out, 1, bn, n_split, stages, staged)
                     return out
                 out = self.empty(M, N, dtype=out_dtype)
-                ops.gemm_tc(a, w, out, 1, bn, 1, stages)
+                ops.gemm_tc(a, w, out, 1, bn, 1, stages, staged)
                 return out
         if (M > 0 and PAIR_MIN_TOKENS <= M <= WIDE_CHUNKS_MAX_TOKENS and may_split and ops.gemm_tc_supported(a, w)
                 and (N + 255) // 256 < self.n_sms // 2):

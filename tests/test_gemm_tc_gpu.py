@@ -83,6 +83,54 @@ def test_split_k(case):
     close(run(a, w, mode, bn, torch.float32, n_split), a.double() @ w.double().t(), 2e-7 * math.sqrt(K), "split")
 
 
+@pytest.mark.parametrize("case", [
+    # (M, N, K, bn, n_split, stages, staged)
+    (8, 6144, 4096, 16, 3, 5, 15),      # q|k|v of the 8B shape beside attention: 20 of a CTA's 22 blocks before the wait
+    (8, 4096, 4096, 16, 4, 5, 15),      # o: all 16 blocks of an item staged or in the ring
+    (8, 24576, 4096, 16, 3, 0, 15),     # gate|up: four items a CTA, the first one staged
+    (3, 384, 1032, 16, 1, 0, 15),       # a K tail, fewer items than CTAs, more blocks staged than the ring is long
+    (16, 1000, 4096, 16, 2, 3, 15),     # a ring of three: the staged blocks pass through it five times
+    (30, 2048, 2048, 32, 2, 4, 12),     # 32 tokens
+    (5, 128, 64, 16, 1, 0, 15),         # one K block
+    (8, 1024, 8192, 16, 1, 0, 40),      # more asked for than tensor memory holds
+])
+def test_weights_staged_in_tensor_memory(case):
+    """The first K blocks of a CTA's first item wait in tensor memory (tcgen05.cp from the ring, then MMAs with A
+    from tensor memory): the same bits as without, on the ladder's structured inputs and on random ones."""
+    from odin_infer_b200.csrc import ops
+    M, N, K, bn, n_split, stages, staged = case
+
+    def product(a, w, staged_blocks):
+        ns = ops.gemm_tc_splits(K, n_split)
+        out = torch.full((ns, M, N), float("nan"), device=DEV, dtype=torch.float32)
+        ops.gemm_tc(a, w, out, 1, bn, n_split, stages, staged_blocks)
+        ops.gemm_tc_check()
+        assert not torch.isnan(out).any()
+        return out
+
+    ladder(lambda a, w: product(a, w, staged).sum(0), M, N, K, torch.float32)
+    a = torch.randn(M, K, device=DEV).bfloat16()
+    w = torch.randn(N, K, device=DEV).bfloat16()
+    plain = product(a, w, 0)
+    for _ in range(3):
+        assert torch.equal(product(a, w, staged), plain)
+
+
+def test_tensor_memory_staging_copy():
+    """tcgen05.cp of a swizzled 128 x 64 tile: row m lands in lane m, elements 2c and 2c + 1 in column c."""
+    import ctypes
+    from odin_infer_b200.csrc import build, ops
+    f = build.load("gemm_tc").odin_gemm_tc_stage_probe
+    f.restype = ctypes.c_int
+    x = torch.randn(128, 64, device=DEV).bfloat16().contiguous()
+    out = torch.full((128, 32), -1, dtype=torch.int32, device=DEV)
+    assert f(ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(out.data_ptr()),
+             ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
+    torch.cuda.synchronize()
+    ops.gemm_tc_check()
+    assert torch.equal(out.view(torch.bfloat16).view(128, 64), x)
+
+
 def test_strided_views_and_batch_invariance():
     """A row's result must not depend on the other rows (same mode, tile and split)."""
     from odin_infer_b200.csrc import ops
