@@ -58,6 +58,8 @@ def main(argv=None) -> int:
     ap.add_argument("--bn", type=int, default=0)
     ap.add_argument("--split", type=int, default=0, help="0: as the runtime chooses")
     ap.add_argument("--stages", type=int, default=0, help="gemm: length of the ring of stages (0: as many as fit)")
+    ap.add_argument("--staged", type=int, default=-1,
+                    help="gemm, mode 1: K blocks of a CTA's first item staged in tensor memory (-1: as the runtime chooses)")
     ap.add_argument("--pair", action="store_true", help="gemm: the two-CTA kernel (tiles of 256 x 256 on pairs of SMs)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=640)
@@ -89,9 +91,11 @@ def main(argv=None) -> int:
         split = ops.gemm_tc_splits(K, split)
         c = torch.empty((split, M, N) if split > 1 else (M, N), device=DEV,
                         dtype=torch.float32 if split > 1 else torch.bfloat16)
-        ms = timeit(lambda: ops.gemm_tc(a, w, c, mode, bn, split, args.stages), args.iters)
+        from ..engine.runtime import STAGED_BLOCKS
+        staged = args.staged if args.staged >= 0 else (STAGED_BLOCKS if mode == 1 and bn <= 32 else 0)
+        ms = timeit(lambda: ops.gemm_tc(a, w, c, mode, bn, split, args.stages, staged), args.iters)
         ops.gemm_tc_check()
-        out.update(m=M, n=N, k=K, mode=mode, bn=bn, split=split, us=round(ms * 1e3, 2),
+        out.update(m=M, n=N, k=K, mode=mode, bn=bn, split=split, staged=staged, us=round(ms * 1e3, 2),
                    weight_gbs=round(N * K * 2 / ms / 1e6, 1), tflops=round(2 * M * N * K / ms / 1e9, 1))
     elif args.kernel == "decode-attention":
         B, hq, hkv, hd = args.batch, args.heads, args.kv_heads, args.head_dim
