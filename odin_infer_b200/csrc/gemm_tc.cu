@@ -122,7 +122,7 @@ __device__ __forceinline__ void store_vec<bf16>(bf16* dst, const uint32_t* r, in
 template <int BN, int MODE, typename TO, bool DUAL = false>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
-               const GemmParams p) {
+               const __grid_constant__ CUtensorMap map_y3, const GemmParams p) {
     using C = Cfg<BN, DUAL>;
     static_assert(!DUAL || MODE == 0, "the SwiGLU epilogue exists for mode 0 only");
     extern __shared__ uint8_t smem_raw[];
@@ -156,6 +156,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         tc::fence_barrier_init();
         tc::prefetch_tensormap(&map_x);
         tc::prefetch_tensormap(&map_y);
+        if (MODE == 1 && p.staged > 0) tc::prefetch_tensormap(&map_y3);
     }
     // with staged weights the CTA takes all of tensor memory: 32 columns a staged block beside the accumulators
     const uint32_t tmem_cols = n_staged > 0 ? 512u : (uint32_t)C::TMEM_COLS;
@@ -207,9 +208,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 pdl_wait();
                 if (ok) {
                     if (t_first > 0) {
-                        tc::mbar_expect_tx(y_full, (uint32_t)t_first * C::STAGE_Y1);
-                        for (int j = 0; j < t_first; ++j)
-                            tc::tma_load_2d(y_staged + j * C::STAGE_Y1, &map_y, (first_kb0 + j) * BK, first_ty * BN, y_full);
+                        // the staged blocks' token tiles in one copy: a box of `staged` K blocks (those beyond the
+                        // item's are read and not used)
+                        tc::mbar_expect_tx(y_full, (uint32_t)n_staged * C::STAGE_Y1);
+                        tc::tma_load_3d(y_staged, &map_y3, 0, first_ty * BN, first_kb0, y_full);
                     }
                     uint32_t st = stage_r;
                     for (int i = 0; i < r_first; ++i) {
@@ -559,6 +561,33 @@ int make_map(CUtensorMap* out, const void* ptr, long long rows, long long K, lon
     return 0;
 }
 
+// The same matrix seen as [K / 64 blocks][rows][64]: a box of `blocks` K blocks of box_rows x 64 lands as that many
+// swizzled tiles one after the other.  K must be a multiple of 64 (else the last block would run into the next row).
+int make_map3(CUtensorMap* out, const void* ptr, long long rows, long long K, long long ld, int box_rows, int blocks) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    MapKey key{ptr, rows, K, ld, box_rows * 1024 + blocks};
+    {
+        std::lock_guard<std::mutex> g(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) { *out = it->second; return 0; }
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return ODIN_ERR_UNSUPPORTED;
+    cuuint64_t dims[3] = {(cuuint64_t)BK, (cuuint64_t)rows, (cuuint64_t)(K / BK)};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)BK * 2};
+    cuuint32_t box[3] = {(cuuint32_t)BK, (cuuint32_t)box_rows, (cuuint32_t)blocks};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return ODIN_ERR_BAD_ARG;
+    std::lock_guard<std::mutex> g(mu);
+    if (cache.size() > 65536) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+
 int* error_flag() {
     static int* flag = nullptr;
     static std::once_flag once;
@@ -581,7 +610,8 @@ int sm_count() {
 }
 
 template <int BN, int MODE, typename TO, bool DUAL = false>
-int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, cudaStream_t s) {
+int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, cudaStream_t s,
+           const void* y_ptr = nullptr, long long y_ld = 0) {
     using C = Cfg<BN, DUAL>;
     auto kern = gemm_tc_kernel<BN, MODE, TO, DUAL>;
     constexpr int MOST_SMEM = 227 * 1024;  // what a CTA may ask for at all
@@ -604,26 +634,32 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, cu
         const int by_smem = (MOST_SMEM - (C::SMEM - (C::STAGES - q.stages) * C::STAGE)) / C::STAGE_Y1;
         q.staged = p.staged < by_tmem ? p.staged : by_tmem;
         if (q.staged > by_smem) q.staged = by_smem;
-        if (q.staged < 0) q.staged = 0;
+        if (q.staged < 0 || y_ptr == nullptr || (p.K % BK) != 0) q.staged = 0;  // the staged tokens' tiles come as one box of whole K blocks
+    }
+    CUtensorMap my3 = my;
+    if (q.staged > 0) {
+        int rc = make_map3(&my3, y_ptr, p.rows_y, p.K, y_ld, BN, q.staged);
+        if (rc) return rc;
     }
     size_t smem = (size_t)C::SMEM - (size_t)(C::STAGES - q.stages) * C::STAGE + (size_t)q.staged * C::STAGE_Y1;
     // A CTA with staged weights holds all of tensor memory; a second one on the same SM would sit in its
     // allocation until the first is gone instead of fetching weights (measured: the step 14 % slower).  It asks
     // for more than half of an SM's shared memory, so no two of them ever share an SM.
     if (q.staged > 0 && smem < (size_t)117 * 1024) smem = (size_t)117 * 1024;
-    odin_launch(kern, dim3(grid), dim3(192), smem, s, mx, my, q);
+    odin_launch(kern, dim3(grid), dim3(192), smem, s, mx, my, my3, q);
     ODIN_LAUNCH_CHECK();
     return 0;
 }
 
 template <int MODE, typename TO>
-int dispatch_bn(int bn, const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, cudaStream_t s) {
+int dispatch_bn(int bn, const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, cudaStream_t s,
+                const void* y_ptr = nullptr, long long y_ld = 0) {
     switch (bn) {
-        case 16: return launch<16, MODE, TO>(mx, my, p, s);
-        case 32: return launch<32, MODE, TO>(mx, my, p, s);
-        case 64: return launch<64, MODE, TO>(mx, my, p, s);
-        case 128: return launch<128, MODE, TO>(mx, my, p, s);
-        case 256: return launch<256, MODE, TO>(mx, my, p, s);
+        case 16: return launch<16, MODE, TO>(mx, my, p, s, y_ptr, y_ld);
+        case 32: return launch<32, MODE, TO>(mx, my, p, s, y_ptr, y_ld);
+        case 64: return launch<64, MODE, TO>(mx, my, p, s, y_ptr, y_ld);
+        case 128: return launch<128, MODE, TO>(mx, my, p, s, y_ptr, y_ld);
+        case 256: return launch<256, MODE, TO>(mx, my, p, s, y_ptr, y_ld);
         default: return ODIN_ERR_UNSUPPORTED;
     }
 }
@@ -677,9 +713,9 @@ extern "C" int odin_gemm_tc(const void* A, const void* W, void* C, int c_dtype, 
     p.tiles_x = (p.rows_x + BM - 1) / BM;
     p.tiles_y = (p.rows_y + bn - 1) / bn;
     if (c_dtype == ODIN_F32)
-        return mode == 0 ? dispatch_bn<0, float>(bn, mx, my, p, s) : dispatch_bn<1, float>(bn, mx, my, p, s);
+        return mode == 0 ? dispatch_bn<0, float>(bn, mx, my, p, s) : dispatch_bn<1, float>(bn, mx, my, p, s, A, lda);
     if (c_dtype == ODIN_BF16)
-        return mode == 0 ? dispatch_bn<0, bf16>(bn, mx, my, p, s) : dispatch_bn<1, bf16>(bn, mx, my, p, s);
+        return mode == 0 ? dispatch_bn<0, bf16>(bn, mx, my, p, s) : dispatch_bn<1, bf16>(bn, mx, my, p, s, A, lda);
     return ODIN_ERR_UNSUPPORTED;
 }
 
