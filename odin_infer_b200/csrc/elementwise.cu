@@ -96,7 +96,7 @@ __device__ __forceinline__ void add_rmsnorm_body(float* __restrict__ x, const TD
             float4 v = load4<float>(xr + j);
             if (delta != nullptr) {
                 const TD* dp = delta + (size_t)src * d + j;
-                constexpr int BATCH = MAX_THREADS > 512 ? 4 : 2;  // loads in flight per thread (registers)
+                constexpr int BATCH = 2;  // loads in flight per thread (registers)
                 for (int s0 = 0; s0 < n_split; s0 += BATCH) {
                     float4 dv[BATCH];
 #pragma unroll
@@ -154,17 +154,71 @@ add_rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_sp
     add_rmsnorm_body<TD, TO, VEC, MAX_THREADS>(x, delta, n_split, split_stride, w, eps, out, rows, d, red, rowbuf);
 }
 
-// The variant of 1,024 threads for a few wide rows (decoding).  Its registers are capped so that a block leaves
-// more than a third of an SM's registers free: the product that follows starts its CTAs while this kernel runs, to
-// fetch weights, and on the SMs that hold a row it could not (with 64 registers a thread the block took them all;
-// those CTAs then started 4 to 7 us after the others and the whole product ended that much later).
-template <typename TD, typename TO>
-__global__ void __maxnreg__(40)
+// The variant of 1,024 threads for a few wide rows (decoding): NV groups of four per thread, kept in registers
+// (no staging in shared memory), the parts' loads of a group issued together; the same order of additions as the
+// kernel above, so the same bits.  Its registers are capped so that a block leaves more than a third of an SM's
+// registers free: the product that follows starts its CTAs while this kernel runs, to fetch weights, and on the
+// SMs that hold a row it could not (with 64 registers a thread the block took them all; those CTAs then started 4
+// to 7 us after the others and the whole product ended that much later).
+template <typename TD, typename TO, int NV>
+__global__ void __maxnreg__(NV == 1 ? 40 : 48)
 add_rmsnorm_wide_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_split, size_t split_stride, VecRef w,
                         float eps, TO* __restrict__ out, const int* __restrict__ rows, int d) {
     __shared__ float red[32];
-    extern __shared__ float rowbuf[];  // d floats
-    add_rmsnorm_body<TD, TO, true, 1024>(x, delta, n_split, split_stride, w, eps, out, rows, d, red, rowbuf);
+    pdl_trigger();
+    const int r = blockIdx.x;
+    int src = r;
+    if (rows != nullptr) src = rows[r];
+    const int j0 = (int)threadIdx.x * 4;
+    float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (j0 < d) w0 = load4w(w, j0);
+    pdl_wait();
+    TO* o = out + (size_t)r * d;
+    if (src < 0) {
+        for (int j = threadIdx.x; j < d; j += blockDim.x) o[j] = from_f32<TO>(0.f);
+        return;
+    }
+    float* xr = x + (size_t)src * d;
+    float4 v[NV];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int j = j0 + k * 4096;
+        v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (j < d) {
+            v[k] = load4<float>(xr + j);
+            if (delta != nullptr) {
+                const TD* dp = delta + (size_t)src * d + j;
+                for (int s0 = 0; s0 < n_split; s0 += 4) {
+                    float4 dv[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (s0 + u < n_split) dv[u] = load4<TD>(dp + (size_t)(s0 + u) * split_stride);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (s0 + u < n_split) { v[k].x += dv[u].x; v[k].y += dv[u].y; v[k].z += dv[u].z; v[k].w += dv[u].w; }
+                }
+            }
+            ss += v[k].x * v[k].x; ss += v[k].y * v[k].y; ss += v[k].z * v[k].z; ss += v[k].w * v[k].w;
+        }
+    }
+    odin_trace_mark(2);  // loads done
+    ss = block_sum(ss, red);
+    odin_trace_mark(3);  // sum known
+    ss /= (float)d;
+    ss += eps;
+    const float rs = 1.0f / sqrtf(ss);
+    const bool write_back = (delta != nullptr) && (rows == nullptr);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int j = j0 + k * 4096;
+        if (j < d) {
+            if (write_back) store4(xr + j, v[k]);
+            const float4 wv = (k == 0) ? w0 : load4w(w, j);
+            store4(o + j, make_float4(wv.x * (rs * v[k].x), wv.y * (rs * v[k].y), wv.z * (rs * v[k].z), wv.w * (rs * v[k].w)));
+        }
+    }
+    odin_trace_mark(4);  // stores issued
 }
 
 // Many rows (prompts), bfloat16 out: a block of 256 threads per row that keeps its NV groups of four
@@ -253,9 +307,16 @@ static int launch_add_rmsnorm(float* x, const void* delta, int n_split, size_t s
         // more rows: smaller blocks, more of them per SM, two passes each
         // (32-bit out: one block size per width, so that a row's sum of squares is added in the same
         // order in a prompt and in a decode step, and the 32-bit path's cuts agree bit for bit)
-        const bool big = !std::is_same<TO, float>::value && d >= 4096 && n_rows <= 256;
-        const int threads = big ? 1024 : (d >= 2048 ? 512 : (d >= 1024 ? 256 : 128));
-        auto kern = big ? add_rmsnorm_wide_kernel<TD, TO> : add_rmsnorm_kernel<TD, TO, true, 512>;
+        const bool big = !std::is_same<TO, float>::value && d >= 4096 && d <= 8192 && n_rows <= 256;
+        if (big) {
+            auto wide = d <= 4096 ? add_rmsnorm_wide_kernel<TD, TO, 1> : add_rmsnorm_wide_kernel<TD, TO, 2>;
+            odin_launch(wide, dim3(n_rows), dim3(1024), 0, s, x, (const TD*)delta, n_split, split_stride, w, eps, (TO*)out,
+                        rows, d);
+            ODIN_LAUNCH_CHECK();
+            return 0;
+        }
+        const int threads = d >= 2048 ? 512 : (d >= 1024 ? 256 : 128);
+        auto kern = add_rmsnorm_kernel<TD, TO, true, 512>;
         if (smem > 48 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;
