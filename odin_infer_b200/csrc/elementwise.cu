@@ -307,7 +307,12 @@ static int launch_add_rmsnorm(float* x, const void* delta, int n_split, size_t s
         // more rows: smaller blocks, more of them per SM, two passes each
         // (32-bit out: one block size per width, so that a row's sum of squares is added in the same
         // order in a prompt and in a decode step, and the 32-bit path's cuts agree bit for bit)
-        const bool big = !std::is_same<TO, float>::value && d >= 4096 && d <= 8192 && n_rows <= 256;
+        // The block of 1,024 threads per row is for rows that all run at once, ahead of the few-token product.  With
+        // 224 and 256 rows (two rounds of blocks, the products then on pairs of SMs) a decode step with this kernel
+        // never ended under programmatic dependent launch: it ran when the kernel triggered its dependents at its end
+        // instead of its start, when it was launched plainly, and with 192 rows; the cause was not found.  From 129
+        // rows on the kernel of 512 threads runs, as it does for prompts.
+        const bool big = !std::is_same<TO, float>::value && d >= 4096 && d <= 8192 && n_rows <= 128;
         if (big) {
             auto wide = d <= 4096 ? add_rmsnorm_wide_kernel<TD, TO, 1> : add_rmsnorm_wide_kernel<TD, TO, 2>;
             odin_launch(wide, dim3(n_rows), dim3(1024), 0, s, x, (const TD*)delta, n_split, split_stride, w, eps, (TO*)out,
