@@ -67,6 +67,42 @@ def test_add_rmsnorm(d, w_dtype, out_dtype):
     close(out3, ref3, 2e-6 if out_dtype == torch.float32 else 5e-3)
 
 
+@pytest.mark.parametrize("case", [(1, 4096, 4), (8, 4096, 4), (128, 4096, 3), (129, 4096, 3), (200, 4096, 5), (8, 5120, 4),
+                                  (64, 8192, 2), (8, 8200, 2), (16, 4100, 9)])
+def test_add_rmsnorm_wide_rows(case):
+    """Few wide rows, bfloat16 out, as in a decode step: the kernel of 1,024 threads with the row in registers
+    (one or two groups of four a thread, up to 128 rows and a width of 8192) and the kernel of 512 threads on either
+    side of it; every row with a scale of its own, one to nine parts to add; and the same bits as the 32-bit-out
+    kernel's x, whose sum runs in the same order."""
+    from odin_infer_b200.csrc import ops
+    n, d, parts = case
+    eps = 1e-6
+    torch.manual_seed(n + d)
+    x = torch.randn(n, d, device=DEV) * torch.linspace(0.1, 30.0, n, device=DEV)[:, None]
+    x0 = x.clone()
+    w = (1 + 0.1 * torch.randn(d, device=DEV)).bfloat16()
+    delta = torch.randn(parts, n, d, device=DEV) * 3
+    out = torch.full((n, d), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops.add_rmsnorm(x, delta, w, eps, out)
+    xr = x0.double() + delta.double().sum(0)
+    ref = w.double() * (xr / torch.sqrt((xr * xr).mean(-1, keepdim=True) + eps))
+    close(x, xr, 1e-6)
+    assert (out.double() - ref).abs().max().item() <= 2 ** -7 * ref.abs().max().item()
+    x32 = x0.clone()
+    ops.add_rmsnorm(x32, delta, w, eps, torch.empty(n, d, device=DEV))
+    assert torch.equal(x32, x), "the parts are added in another order than in the 32-bit kernel"
+    # gather of rows (the final norm of a decode step): x untouched, padding rows give zeros
+    rows = torch.tensor([n - 1, -1, 0], dtype=torch.int32, device=DEV)
+    out2 = torch.full((3, d), float("nan"), device=DEV, dtype=torch.bfloat16)
+    x1 = x.clone()
+    ops.add_rmsnorm(x, None, w, eps, out2, rows)
+    assert torch.equal(x, x1)
+    ref2 = w.double() * (x1.double() / torch.sqrt((x1.double() ** 2).mean(-1, keepdim=True) + eps))
+    assert (out2[0].double() - ref2[n - 1]).abs().max().item() <= 2 ** -7 * ref2[n - 1].abs().max().item()
+    assert (out2[2].double() - ref2[0]).abs().max().item() <= 2 ** -7 * ref2[0].abs().max().item()
+    assert torch.equal(out2[1], torch.zeros_like(out2[1]))
+
+
 @pytest.mark.parametrize("delta_dtype", [None, torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("d", [72, 1000, 2048, 4096, 5120, 8200])
 def test_add_rmsnorm_many_rows(d, delta_dtype):
