@@ -374,7 +374,8 @@ int launch_decode_tc(const bf16* q, size_t q_stride, bf16* out, size_t out_strid
         mode = prep->in_dtype == ODIN_F32 ? 1 : 2;
     }
     dim3 grid(n_split, Hkv, B);
-    // few CTAs: one per SM with a deep ring; many: two per SM with a ring half as deep
+    // very few CTAs: a deep ring each; else a ring half as deep, with which a CTA fits an SM beside the CTA of the
+    // projection before it (and a second one of its own kind) and has its pages before that projection is done
     static int sms = 0;
     if (sms == 0) {
         int dev = 0;
@@ -382,7 +383,9 @@ int launch_decode_tc(const bf16* q, size_t q_stride, bf16* out, size_t out_strid
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
     }
     const long long ctas = (long long)n_split * Hkv * B;
-    const bool deep = ctas <= sms;
+    static int deep_upto = -1;
+    if (deep_upto < 0) { const char* e = getenv("ODIN_DECODE_DEEP_UPTO"); deep_upto = e ? atoi(e) : 32; }
+    const bool deep = ctas <= deep_upto;
 #define GO(PREP)                                                                  \
     (deep ? launch_decode_tc_slots<HD, 6, PREP>(mk, mv, p, grid, s)               \
           : launch_decode_tc_slots<HD, 3, PREP>(mk, mv, p, grid, s))

@@ -328,6 +328,7 @@ __device__ __forceinline__ void attn_decode_tc_body(const CUtensorMap& map_k, co
         }
     }
     group_sync<BAR>();
+    odin_trace_mark(2);  // the query heads are prepared
 
     uint32_t qa[KB][4];
     const uint32_t sQ_u = tc::smem_u32(sQ);
@@ -393,6 +394,7 @@ __device__ __forceinline__ void attn_decode_tc_body(const CUtensorMap& map_k, co
         if (lane == 0 && i + SLOTS < n_here) issue(i + SLOTS, slot);
     }
     group_sync<BAR>();  // no warp reads a slot any more and every requested page has been consumed
+    odin_trace_mark(3);  // every page is multiplied
     if (*abort_flag) {
         if (tid == 0 && p.error != nullptr) atomicExch(p.error, 1);
         return;
@@ -450,7 +452,9 @@ __device__ __forceinline__ void attn_decode_tc_body(const CUtensorMap& map_k, co
             if (d == 0) { my_ml[(size_t)r * head_step_ml] = mm; my_ml[(size_t)r * head_step_ml + 1] = ll; }
         }
     }
+    odin_trace_mark(4);  // the warps are merged, the result or the partial is written
     if (p.n_split > 1) split_arrive_and_combine<HD, BAR>(p, t, kvh, g, h0, s_last, tid);
+    odin_trace_mark(5);  // the splits have met
 }
 
 

@@ -97,8 +97,8 @@ def main(argv=None) -> int:
         elif k is not None:
             k["marks"].setdefault(int(point[i]), []).append(us[i])
             k.setdefault("by_block", {}).setdefault(int(blk[i]), {})[int(point[i])] = us[i]
-    names = {2: "first item's MMAs issued / loads back", 3: "last commit / sum known", 4: "stores issued / end", 5: "last tile stored",
-             6: "all loads requested"}
+    names = {2: "first item's MMAs issued / loads back / heads prepared", 3: "last commit / sum known / pages multiplied",
+             4: "stores issued / end / warps merged", 5: "last tile stored / splits met", 6: "all loads requested"}
     print(f"records {n}; batch {args.batch}, {args.layers} layers; times in us from the step's first mark")
     print("go: the kernel's wait for the kernel before it has ended; 'previous took': from the previous kernel's go to this one's,")
     print("i.e. what the kernel in the line above cost the chain")
