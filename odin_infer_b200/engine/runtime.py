@@ -72,12 +72,13 @@ def decode_key_splits(n_seqs: int, n_kv_heads: int, longest: int, page: int = 64
 
     Short contexts: the kernel is a chain of latencies, and what a choice costs is about, in
     microseconds on the 8B shape's decode step: 1.3 per round of pages (a CTA's four warps take a
-    page each), 1.0 for the meeting of the splits if there is more than one, and 0.6 if there are
-    more CTAs than SMs: a CTA that is there early, beside the projection's CTA on its SM, has its
-    pages before the projection is done; one that comes later has not.  Of equal costs the larger
-    number of splits wins.  (Measured, 520 to 580 tokens of context: 8 sequences: four splits 3.030
-    ms a step, three 3.044, one 3.056; 16 sequences: one split 3.18, two 3.30; 4 sequences: four
-    splits 2.90, two 2.94.)"""
+    page each), 1.0 for the meeting of the splits if there is more than one, and 2.0 times the
+    share of the CTAs that do not find an SM at once: a CTA that is there early, beside the
+    projection's CTA on its SM, has its pages before the projection is done; one that comes later
+    has not.  Of equal costs the larger number of splits wins.  (Measured, 520 to 580 tokens of
+    context: 8 sequences: four splits 3.030 ms a step, three 3.044, one 3.056; 12 sequences: one
+    split 3.134, two 3.155, three 3.173; 16 sequences: one 3.18, two 3.30; 4 sequences: four splits
+    2.90, two 2.94.)"""
     forced = int(os.environ.get("ODIN_DECODE_SPLITS", "0"))
     if forced:
         return forced
@@ -91,7 +92,7 @@ def decode_key_splits(n_seqs: int, n_kv_heads: int, longest: int, page: int = 64
     best, best_cost = 1, None
     for s in range(1, min(pages, room, 2 * cls) + 1):  # at most two splits per 8 pages
         per = (pages + s - 1) // s
-        cost = 1.3 * ((per + 3) // 4) + (1.0 if s > 1 else 0.0) + (0.6 if items * s > n_sms else 0.0)
+        cost = 1.3 * ((per + 3) // 4) + (1.0 if s > 1 else 0.0) + 2.0 * max(0, items * s - n_sms) / n_sms
         if best_cost is None or cost <= best_cost + 1e-9:
             best, best_cost = s, cost
     return best
