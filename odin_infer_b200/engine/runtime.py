@@ -92,7 +92,8 @@ def decode_key_splits(n_seqs: int, n_kv_heads: int, longest: int, page: int = 64
     best, best_cost = 1, None
     for s in range(1, min(pages, room, 2 * cls) + 1):  # at most two splits per 8 pages
         per = (pages + s - 1) // s
-        cost = 1.3 * ((per + 3) // 4) + (1.0 if s > 1 else 0.0) + 2.0 * max(0, items * s - n_sms) / n_sms
+        busy = (pages + per - 1) // per  # splits that find pages
+        cost = 1.3 * ((per + 3) // 4) + (1.0 if s > 1 else 0.0) + 2.0 * max(0, items * busy - n_sms) / n_sms
         if best_cost is None or cost <= best_cost + 1e-9:
             best, best_cost = s, cost
     return best
