@@ -87,7 +87,9 @@ def decode_key_splits(n_seqs: int, n_kv_heads: int, longest: int, page: int = 64
     if cls > 2:
         room = max(1, (ctas_per_sm * n_sms) // items)
         return max(1, min(2 * cls, room, 16))  # a split that finds no page of its own writes an empty partial
-    pages = (cls - 1) * 8 + 1  # the class's shortest context: one choice per class, whichever of its lengths comes first
+    # one choice per class, whichever of its lengths comes first: for the class's shortest context (in the first
+    # class: for half of its eight pages)
+    pages = max(4, (cls - 1) * 8 + 1)
     room = max(1, (ctas_per_sm * n_sms) // items)  # never more CTAs than fit the GPU twice
     best, best_cost = 1, None
     for s in range(1, min(pages, room, 2 * cls) + 1):  # at most two splits per 8 pages
