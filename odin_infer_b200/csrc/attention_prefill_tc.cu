@@ -57,8 +57,8 @@ struct PrefillTcParams {
 
 // The first wait that runs out records who it was: [which wait, head, sequence, tile, iteration,
 // pages of the tile, thread].  Waits: 1 producer on a free K stage, 2 producer on a free V stage,
-// 3 MMA on a landed K tile, 4 MMA on P, 5 MMA on a landed V tile, 6 softmax on scores, 7 softmax on the
-// previous P V (rescaling), 8 softmax on the last P V.
+// 3 MMA on the first K pages, 4 MMA on P, 5 MMA on a landed slot (V and the K after next), 6 softmax on scores,
+// 7 softmax on the previous P V (rescaling), 8 softmax on the last P V.
 __device__ __noinline__ void report_attn(int* err, int what, int it, int n_pages) {
     if (err == nullptr) return;
     atomicOr(&err[7], 1 << what);           // every kind of wait that ran out
@@ -104,15 +104,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     uint8_t* sK = sQ + NSUB * Q_SUB;      // 2 stages
     uint8_t* sV = sK + 2 * KV_TILE;       // 2 stages
     uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * KV_TILE);
-    uint64_t* k_full = bars;           // [2] K page landed
-    uint64_t* k_empty = bars + 2;      // [2] the S product that read it is done
-    uint64_t* v_full = bars + 4;       // [2]
-    uint64_t* v_empty = bars + 6;      // [2] the P V product that read it is done
-    uint64_t* s_full = bars + 8;       // [2] scores complete in S buffer b
     // Every barrier completes once per use of ITS buffer or stage, and nobody can get two
     // completions ahead of its waiter: a parity wait cannot tell a phase from the one after next.
-    uint64_t* p_full = bars + 10;      // [2] P written over S buffer b, O rescaled if need be
-    uint64_t* pv_done = bars + 12;     // [2] the P V product of an iteration with buffer b is complete
+    uint64_t* kv_full = bars;          // [2] slot j (barrier j & 1): K page j and V page j - 2 landed (see the producer)
+    uint64_t* s_full = bars + 2;       // [2] scores complete in S buffer b: the softmax may read, the K stage is free
+    uint64_t* p_full = bars + 4;       // [2] P written over S buffer b, O rescaled if need be
+    uint64_t* pv_done = bars + 6;      // [2] the P V product of an iteration with buffer b is complete: its V stage is free
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* s_max = reinterpret_cast<float*>(bars + 16);  // [2 buffers][2 halves][128 rows]: the pair's exchange
@@ -150,6 +147,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const long long w = *s_item;
     __syncthreads();   // all have read the number before it is drawn again
     if (w >= total) break;
+    odin_trace_mark(2);  // a triple begins (trace builds only)
     const int h = (int)(w % p.n_heads), seq = (int)((w / p.n_heads) % p.n_seqs);
     const int level = (int)(w / ((long long)p.n_heads * p.n_seqs));
     const int tok0 = p.seq_start[seq], n_new = p.seq_start[seq + 1] - tok0;
@@ -163,13 +161,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int kvh = h / (p.Hq / p.Hkv);
 #ifdef ODIN_TRACE
     // Clock marks of the first triple's work (the heaviest tile of head 0), trace builds only: role 0 the MMA thread,
-    // role 1 the first softmax thread; [role][n] = (clock << 8) | point.
+    // roles 1..8 the first lanes of the softmax warps; [role][n] = (clock << 8) | point.
     const bool traced = w == 0 && odin_attn_clk != nullptr;
     int clk_n = 0;
 #define CLK(role, point)                                                                                         \
     do {                                                                                                         \
-        if (traced && (role == 0 || threadIdx.x == 64) && clk_n < 1024)                                          \
-            odin_attn_clk[(role) * 1024 + clk_n++] = ((unsigned long long)clock64() << 8) | (point);            \
+        if (traced && (role == 0 || lane == 0) && clk_n < 1024)                                                  \
+            odin_attn_clk[((role) == 0 ? 0 : warp - 1) * 1024 + clk_n++] = ((unsigned long long)clock64() << 8) | (point); \
     } while (0)
 #else
 #define CLK(role, point) do {} while (0)
@@ -184,12 +182,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     if (threadIdx.x == 0) {
         // every triple starts with fresh barriers (all threads are past the last one's: the sync at the loop's end)
         if (!first_item)
-            for (int i = 0; i < 14; ++i) tc::mbar_inval(&bars[i]);
-        for (int i = 0; i < 10; ++i) tc::mbar_init(&bars[i], 1);
-        tc::mbar_init(&p_full[0], 8);   // one arrival per softmax warp
-        tc::mbar_init(&p_full[1], 8);
-        tc::mbar_init(&pv_done[0], 1);
-        tc::mbar_init(&pv_done[1], 1);
+            for (int i = 0; i < 8; ++i) tc::mbar_inval(&bars[i]);
+        for (int i = 0; i < 8; ++i) tc::mbar_init(&bars[i], (i == 4 || i == 5) ? 8 : 1);   // p_full: one arrival per softmax warp
         tc::fence_barrier_init();
     }
     first_item = false;
@@ -208,21 +202,30 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     if (warp == 0) {
         // ------------------------------------------------------------- producer
         if (lane == 0) {
-            for (int it = 0; it < n_pages; ++it) {
-                const int stage = it & 1;
-                const uint32_t par = ((it >> 1) & 1) ^ 1;
-                const int page = bt[page_a + it];
-                const int row = (page * p.Hkv + kvh) * PAGE_T;
-                if (!tc::mbar_wait(&k_empty[stage], par, abort_flag)) { report_attn(p.error, 1, it, n_pages); break; }
-                tc::mbar_expect_tx(&k_full[stage], KV_TILE);
+            // Slot j brings K page j and V page j - 2 under one barrier: the MMA thread needs both at the same point
+            // of its program (P V of page j - 2, then the scores of page j), and every wait costs it time that
+            // nothing hides.  K page j goes where the scores of page j - 2 read, V page j - 2 where P V of page j - 4 read.
+            for (int j = 0; j < n_pages + 2; ++j) {
+                const int b = j & 1;
+                const bool has_k = j < n_pages, has_v = j >= 2;
+                // Slot j - 2 (the barrier's last use) must have landed AND the MMA thread must have seen it before the
+                // barrier is armed again, or a parity wait would mistake the phase after next for its own.  The scores
+                // of page j - 2 being complete says both (they were issued after that wait), and frees K's stage.
+                if (j >= 2 && !tc::mbar_wait(&s_full[b], ((j - 2) >> 1) & 1, abort_flag)) { report_attn(p.error, 1, j, n_pages); break; }
+                if (has_v && j >= 4 && !tc::mbar_wait(&pv_done[b], ((j - 4) >> 1) & 1, abort_flag)) { report_attn(p.error, 2, j, n_pages); break; }
+                tc::mbar_expect_tx(&kv_full[b], (has_k ? KV_TILE : 0) + (has_v ? KV_TILE : 0));
+                if (has_v) {
+                    const int row = (bt[page_a + j - 2] * p.Hkv + kvh) * PAGE_T;
 #pragma unroll
-                for (int sub = 0; sub < NSUB; ++sub)
-                    tc::tma_load_2d(sK + stage * KV_TILE + sub * KV_SUB, &map_k, sub * 64, row, &k_full[stage]);
-                if (!tc::mbar_wait(&v_empty[stage], par, abort_flag)) { report_attn(p.error, 2, it, n_pages); break; }
-                tc::mbar_expect_tx(&v_full[stage], KV_TILE);
+                    for (int sub = 0; sub < NSUB; ++sub)
+                        tc::tma_load_2d(sV + b * KV_TILE + sub * KV_SUB, &map_v, sub * 64, row, &kv_full[b]);
+                }
+                if (has_k) {
+                    const int row = (bt[page_a + j] * p.Hkv + kvh) * PAGE_T;
 #pragma unroll
-                for (int sub = 0; sub < NSUB; ++sub)
-                    tc::tma_load_2d(sV + stage * KV_TILE + sub * KV_SUB, &map_v, sub * 64, row, &v_full[stage]);
+                    for (int sub = 0; sub < NSUB; ++sub)
+                        tc::tma_load_2d(sK + b * KV_TILE + sub * KV_SUB, &map_k, sub * 64, row, &kv_full[b]);
+                }
             }
         }
     } else if (warp == 1) {
@@ -230,46 +233,59 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         if (lane == 0) {
             constexpr uint32_t idesc_s = tc::make_idesc_bf16(BQT, PAGE_T);
             constexpr uint32_t idesc_o = tc::make_idesc_bf16_b_mn(BQT, HD);
-            const uint32_t q_u = tc::smem_u32(sQ);
-            // scores of page `it` into S buffer it & 1; frees the K stage when done
-            auto issue_s = [&](int it) -> bool {
+            // The descriptors are made once per triple: a descriptor of a place `off` bytes further on is the
+            // descriptor plus off / 16 (the address field holds bytes / 16 and cannot carry out of its 14 bits inside
+            // the shared-memory window).  This thread shares its scheduler with softmax warps, so every instruction
+            // between two MMAs costs it several cycles.
+            const uint64_t q_desc = tc::make_smem_desc_sw128(tc::smem_u32(sQ));
+            const uint64_t k_desc[2] = {tc::make_smem_desc_sw128(tc::smem_u32(sK)),
+                                        tc::make_smem_desc_sw128(tc::smem_u32(sK + KV_TILE))};
+            const uint64_t v_desc[2] = {tc::make_smem_desc_sw128_mn(tc::smem_u32(sV), KV_SUB, 1024),
+                                        tc::make_smem_desc_sw128_mn(tc::smem_u32(sV + KV_TILE), KV_SUB, 1024)};
+            // scores of page `it` into S buffer it & 1 (its K page landed with slot `it`, which the caller waited for)
+            auto issue_s = [&](int it) {
                 const int stage = it & 1;
-                if (!tc::mbar_wait(&k_full[stage], (it >> 1) & 1, abort_flag)) { report_attn(p.error, 3, it, n_pages); return false; }
-                tc::fence_after_sync();
-                const uint32_t k_u = tc::smem_u32(sK + stage * KV_TILE);
+                const uint64_t kd = stage ? k_desc[1] : k_desc[0];
+                const uint32_t s_addr = tmem_base + S_COL + stage * PAGE_T;
 #pragma unroll
-                for (int k = 0; k < HD / 16; ++k) {
-                    const uint64_t a = tc::make_smem_desc_sw128(q_u + (k >> 2) * Q_SUB + (k & 3) * 32);
-                    const uint64_t b = tc::make_smem_desc_sw128(k_u + (k >> 2) * KV_SUB + (k & 3) * 32);
-                    tc::umma_bf16(tmem_base + S_COL + stage * PAGE_T, a, b, idesc_s, k > 0 ? 1u : 0u);
-                }
+                for (int k = 0; k < HD / 16; ++k)
+                    tc::umma_bf16(s_addr, q_desc + (uint64_t)(((k >> 2) * Q_SUB + (k & 3) * 32) >> 4),
+                                  kd + (uint64_t)(((k >> 2) * KV_SUB + (k & 3) * 32) >> 4), idesc_s, k > 0 ? 1u : 0u);
+                CLK(0, 16);  // S MMAs issued
                 tc::umma_commit(&s_full[stage]);
-                tc::umma_commit(&k_empty[stage]);
                 CLK(0, 10);  // S issued
-                return true;
             };
-            bool ok = issue_s(0);
-            if (ok && n_pages > 1) ok = issue_s(1);
+            bool ok = true;
+            for (int j = 0; j < 2 && j < n_pages && ok; ++j) {
+                if (!tc::mbar_wait(&kv_full[j], 0, abort_flag)) { report_attn(p.error, 3, j, n_pages); ok = false; break; }
+                tc::fence_after_sync();
+                issue_s(j);
+            }
             for (int it = 0; it < n_pages && ok; ++it) {
                 const int stage = it & 1;
                 if (!tc::mbar_wait(&p_full[stage], (it >> 1) & 1, abort_flag)) { report_attn(p.error, 4, it, n_pages); ok = false; break; }
-                if (!tc::mbar_wait(&v_full[stage], (it >> 1) & 1, abort_flag)) { report_attn(p.error, 5, it, n_pages); ok = false; break; }
+                if (!tc::mbar_wait(&kv_full[stage], ((it + 2) >> 1) & 1, abort_flag)) { report_attn(p.error, 5, it, n_pages); ok = false; break; }
                 tc::fence_after_sync();
                 CLK(0, 11);  // P and V are there
-                const uint32_t v_u = tc::smem_u32(sV + stage * KV_TILE);
+                const uint64_t vd = stage ? v_desc[1] : v_desc[0];
+                const uint32_t p_addr = tmem_base + S_COL + stage * PAGE_T;
+                // P: 16 keys = 8 packed columns of the S buffer that the softmax overwrote.
+                // V as stored: rows are keys (the MMA's K), head_dim contiguous (its N): MN-major.
+                // 16 keys further = 16 rows of 128 bytes; 64-column sub-tiles KV_SUB apart; 8-key groups 1 KB apart.
+                if (it > 0) {
 #pragma unroll
-                for (int j = 0; j < PAGE_T / 16; ++j) {
-                    // P: 16 keys = 8 packed columns of the S buffer that the softmax overwrote.
-                    // V as stored: rows are keys (the MMA's K), head_dim contiguous (its N): MN-major.
-                    // 16 keys further = 16 rows of 128 bytes; 64-column sub-tiles KV_SUB apart; 8-key groups 1 KB apart.
-                    const uint64_t b = tc::make_smem_desc_sw128_mn(v_u + j * 2048, KV_SUB, 1024);
-                    tc::umma_bf16_ts(tmem_base + O_COL, tmem_base + S_COL + stage * PAGE_T + j * 8, b, idesc_o,
-                                     (it > 0 || j > 0) ? 1u : 0u);
+                    for (int j = 0; j < PAGE_T / 16; ++j)
+                        tc::umma_bf16_ts(tmem_base + O_COL, p_addr + j * 8, vd + (uint64_t)((j * 2048) >> 4), idesc_o, 1u);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < PAGE_T / 16; ++j)
+                        tc::umma_bf16_ts(tmem_base + O_COL, p_addr + j * 8, vd + (uint64_t)((j * 2048) >> 4), idesc_o,
+                                         j > 0 ? 1u : 0u);
                 }
-                tc::umma_commit(&v_empty[stage]);
+                CLK(0, 15);  // P V MMAs issued
                 tc::umma_commit(&pv_done[stage]);
                 CLK(0, 13);  // P V issued
-                if (it + 2 < n_pages) ok = issue_s(it + 2);  // its S buffer was read before p_full(it)
+                if (it + 2 < n_pages) issue_s(it + 2);  // its S buffer was read before p_full(it)
             }
         }
     } else {
@@ -353,7 +369,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 // 0 x NaN is NaN: clear those value rows (their probabilities are exactly 0).
                 const int valid = len_after - pg * PAGE_T;
                 if (valid < PAGE_T) {
-                    tc::mbar_wait(&v_full[stage], (it >> 1) & 1, abort_flag);  // the tile must have landed before it is patched
+                    tc::mbar_wait(&kv_full[stage], ((it + 2) >> 1) & 1, abort_flag);  // the tile (slot it + 2) must have landed before it is patched
                     for (int idx = threadIdx.x - 64; idx < (PAGE_T - valid) * NSUB * 8; idx += 256) {
                         const int r = valid + idx / (NSUB * 8), rest = idx % (NSUB * 8);
                         *reinterpret_cast<uint4*>(sV + stage * KV_TILE + (rest >> 3) * KV_SUB + r * 128 + ((rest & 7) << 4)) =
