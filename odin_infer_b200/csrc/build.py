@@ -34,6 +34,7 @@ GROUPS = {
     "gemm_tc": ["gemm_tc.cu", "gemm_tc2.cu"],
     "attention_decode": ["attention_decode.cu"],
     "attention_prefill": ["attention_prefill_tc.cu"],
+    "mma_probe": ["mma_probe.cu"],   # a measuring tool (see microbench mma-rate), no part of a step
 }
 
 NVCC_FLAGS = [

@@ -5,9 +5,12 @@
     python -m odin_infer_b200.csrc.microbench decode-attention --batch 64 --ctx 640
     python -m odin_infer_b200.csrc.microbench prefill-attention --tokens 2048
     python -m odin_infer_b200.csrc.microbench add-rmsnorm --rows 8 --width 4096 --split 4
+    python -m odin_infer_b200.csrc.microbench mma-rate
 
 Prints one JSON line: the median time and the achieved bytes/s and flop/s of the kernel's
-algorithmic traffic and work.  Small enough to run under a profiler.
+algorithmic traffic and work.  Small enough to run under a profiler.  `mma-rate` is of another kind:
+it times no kernel of a step but tcgen05.mma itself (see mma_probe.cu), in cycles of the SM clock,
+for the shapes and issue orders of the attention kernels, one line per case.
 """
 from __future__ import annotations
 
@@ -50,7 +53,7 @@ def paged(batch: int, ctx: int, n_kv: int, hd: int):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["gemm", "decode-attention", "prefill-attention", "add-rmsnorm", "head-prep"])
+    ap.add_argument("kernel", choices=["gemm", "decode-attention", "prefill-attention", "add-rmsnorm", "head-prep", "mma-rate"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=24576)
     ap.add_argument("--k", type=int, default=4096)
@@ -121,6 +124,30 @@ def main(argv=None) -> int:
                     args.iters)
         ops.attention_prefill_check()
         out.update(tokens=T, us=round(ms * 1e3, 2), tflops=round(4 * hq * hd * (T * (T + 1) / 2) / ms / 1e9, 1))
+    elif args.kernel == "mma-rate":
+        # (name, pattern, N, B MN-major, commits per group, CTAs per SM, arithmetic cycles at 4,096 multiply-adds a cycle and SM)
+        cases = [("A and B from shared memory, N 64", 0, 64, False, 0, 1, 32),
+                 ("A and B from shared memory, N 128", 0, 128, False, 0, 1, 64),
+                 ("A and B from shared memory, N 256", 0, 256, False, 0, 1, 128),
+                 ("A from tensor memory, N 64", 1, 64, False, 0, 1, 32),
+                 ("A from tensor memory, N 128, B MN-major", 1, 128, True, 0, 1, 64),
+                 ("two CTAs: A and B from shared memory, N 64", 0, 64, False, 0, 2, 32),
+                 ("two CTAs: A from tensor memory, N 128, B MN-major", 1, 128, True, 0, 2, 64),
+                 ("page of 64 keys (4 P V + 8 scores N 64)", 2, 0, False, 0, 1, 512),
+                 ("page of 64 keys, one commit per group", 2, 0, False, 1, 1, 512),
+                 ("page of 64 keys, two commits per group", 2, 0, False, 2, 1, 512),
+                 ("two CTAs: page of 64 keys", 2, 0, False, 0, 2, 512),
+                 ("two CTAs: page of 64 keys, one commit per group", 2, 0, False, 1, 2, 512),
+                 ("two CTAs: page of 64 keys, two commits per group", 2, 0, False, 2, 2, 512),
+                 ("two pages (8 P V + 8 scores N 128)", 3, 0, False, 0, 1, 1024),
+                 ("two pages, one commit per group", 3, 0, False, 1, 1, 1024),
+                 ("two CTAs: two pages, one commit per group", 3, 0, False, 1, 2, 1024)]
+        for name, pattern, n, b_mn, commits, per_sm, arith in cases:
+            iters = 4096 if pattern <= 1 else 512
+            best = min(ops.mma_probe(pattern, n, b_mn, commits, per_sm, iters) for _ in range(3))
+            print(json.dumps({"kernel": "mma-rate", "case": name, "cycles": round(best, 1),
+                              "unit": "per MMA" if pattern <= 1 else "per step of a CTA", "arithmetic": arith}))
+        return 0
     elif args.kernel == "head-prep":
         # the prompt's head preparation: per-head norm of q and k, rotation, cache write, from a bfloat16 projection
         T, hq, hkv, hd = args.tokens, args.heads, args.kv_heads, args.head_dim
