@@ -2,30 +2,36 @@
 //
 // A CTA of 320 threads takes 128 consecutive query tokens of one sequence and one
 // query head and walks over the sequence's cache pages (64 keys each):
-//   warp 0      TMA producer: K and V page tiles, two stages;
+//   warp 0      TMA producer: K and V page tiles, two stages each; K page j and V page j - 2 arrive under
+//               one barrier, because the MMA thread needs both at the same point of its program;
 //   warp 1      allocates tensor memory and issues the MMAs (one thread):
 //               S = Q K^T (tcgen05.mma M128 N64, K and Q both K-major), then
 //               O += P V (M128 N=head_dim, P read from tensor memory, V MN-major exactly
-//               as the cache stores it), accumulators S and O in TMEM;
+//               as the cache stores it), accumulators S and O in TMEM; one commit per product tells
+//               the softmax (or the next rescaling) and the producer (the stage is free) at once;
 //   warps 2..9  two threads per query row (32 keys of the page each; the row maximum is
 //               exchanged through shared memory): read S from TMEM, mask, online
 //               softmax in 32-bit registers (exponentials as ex2 of one fused
 //               multiply-add), write P as packed bfloat16 back into the columns of the S
 //               buffer just read, rescale O in TMEM only when the row maximum ran ahead
 //               of the scaling maximum by more than 2^8, and at the end normalise and store.
-// S has two buffers in TMEM and K and V have barriers of their own, so the scores of the
-// next two pages are computed while the softmax of the current one runs; two CTAs share
-// an SM (96 KB of shared memory and 256 TMEM columns each) and fill each other's gaps.
-// The CTAs are persistent and walk the (head, sequence, tile) triples back and forth.
+// S has two buffers in TMEM, so the scores of the next page are computed while the softmax of the
+// current one runs; two CTAs share an SM (96 KB of shared memory and 256 TMEM columns each) and fill
+// each other's gaps.  The CTAs are persistent and walk the (head, sequence, tile) triples back and forth.
 //
-// Measured on one CTA with clock marks (2,048 tokens, head size 128): a page costs the MMA thread ~2,100
-// cycles, of which it is blocked issuing S for ~1,000 and P V for ~640 while the SM's other CTA does the same:
-// the tensor core with its operand fetches is what the two CTAs queue for.  Two variants that feed it
-// differently were built and measured slower at every length and are not kept: two heads of a kv head per
+// Measured on one CTA with clock marks (2,048 tokens, head size 128): a page costs ~1,900 cycles.  The MMA
+// thread issues for ~1,500 of them and waits ~400 for P; a softmax thread works ~1,450 and waits the rest for
+// scores.  Per S buffer the chain "P handed over, P V and the scores after next issued, softmax" is serial (the
+// next scores overwrite P), so a page costs about the larger of the two plus the two hand-overs; the tensor core
+// itself would need 570 cycles per page and SM (measured in isolation, mma_probe.cu: an MMA of N 64 takes 57
+// cycles for 32 of arithmetic).  Every wait and commit of the MMA thread is on that chain, which is why K and V
+// pages share barriers and each product has one commit (65.5 -> 61.5 us at 2,048 tokens, 553 -> 517 us at 8,192).
+// Variants that were built and measured slower at every length, and are not kept: two heads of a kv head per
 // CTA with Q in tensor memory and K/V shared (one S buffer per head left the softmax warps idle during the
-// head's own products: 748 against 588 us at 8,192 tokens), and one CTA per SM with Q in tensor memory, two
-// pages per step and four threads per row (its 128 x 128 x 16 MMAs took ~130 cycles each, twice their
-// arithmetic: 83 against 63 us at 2,048 tokens, 887 against 1,113 TFLOP/s at 32,768).
+// head's own products: 748 against 588 us at 8,192 tokens); one CTA per SM with Q in tensor memory, two
+// pages per step and four threads per row (83 against 63 us at 2,048 tokens, 887 against 1,113 TFLOP/s at
+// 32,768); the MMA warp running as a whole with only the MMAs predicated on one lane (no change: the thread is
+// not short of issue slots); a start offset between an SM's two CTAs (no change).
 //
 // Arithmetic as infer/forward.odin:88-115 (scale 1/sqrt(hd), causal bound t <= pos,
 // maximum-subtracted softmax, weighted sum of values), in 32-bit except the bfloat16
@@ -205,9 +211,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             // Slot j brings K page j and V page j - 2 under one barrier: the MMA thread needs both at the same point
             // of its program (P V of page j - 2, then the scores of page j), and every wait costs it time that
             // nothing hides.  K page j goes where the scores of page j - 2 read, V page j - 2 where P V of page j - 4 read.
+            // (Bringing the first two V pages with slots 0 and 1 gained nothing at 512 tokens and would let a barrier
+            // run two phases ahead of the softmax threads that patch a short tile's last V page.)
             for (int j = 0; j < n_pages + 2; ++j) {
                 const int b = j & 1;
                 const bool has_k = j < n_pages, has_v = j >= 2;
+                const int v_page = j - 2;
                 // Slot j - 2 (the barrier's last use) must have landed AND the MMA thread must have seen it before the
                 // barrier is armed again, or a parity wait would mistake the phase after next for its own.  The scores
                 // of page j - 2 being complete says both (they were issued after that wait), and frees K's stage.
@@ -215,7 +224,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 if (has_v && j >= 4 && !tc::mbar_wait(&pv_done[b], ((j - 4) >> 1) & 1, abort_flag)) { report_attn(p.error, 2, j, n_pages); break; }
                 tc::mbar_expect_tx(&kv_full[b], (has_k ? KV_TILE : 0) + (has_v ? KV_TILE : 0));
                 if (has_v) {
-                    const int row = (bt[page_a + j - 2] * p.Hkv + kvh) * PAGE_T;
+                    const int row = (bt[page_a + v_page] * p.Hkv + kvh) * PAGE_T;
 #pragma unroll
                     for (int sub = 0; sub < NSUB; ++sub)
                         tc::tma_load_2d(sV + b * KV_TILE + sub * KV_SUB, &map_v, sub * 64, row, &kv_full[b]);
@@ -369,7 +378,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 // 0 x NaN is NaN: clear those value rows (their probabilities are exactly 0).
                 const int valid = len_after - pg * PAGE_T;
                 if (valid < PAGE_T) {
-                    tc::mbar_wait(&kv_full[stage], ((it + 2) >> 1) & 1, abort_flag);  // the tile (slot it + 2) must have landed before it is patched
+                    tc::mbar_wait(&kv_full[stage], ((it + 2) >> 1) & 1, abort_flag);  // the tile (slot it + 2, the barrier's last) must have landed before it is patched
                     for (int idx = threadIdx.x - 64; idx < (PAGE_T - valid) * NSUB * 8; idx += 256) {
                         const int r = valid + idx / (NSUB * 8), rest = idx % (NSUB * 8);
                         *reinterpret_cast<uint4*>(sV + stage * KV_TILE + (rest >> 3) * KV_SUB + r * 128 + ((rest & 7) << 4)) =
