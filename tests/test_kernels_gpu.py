@@ -756,6 +756,49 @@ def test_attention_prefill_against_plain_kernel_and_reference(geom, window):
         r += b
 
 
+def test_attention_prefill_many_short_tiles_again_and_again():
+    """Hundreds of tiles of one to five pages on persistent CTAs, launched thirty times: the barriers of a
+    tile are armed again for the next one, and a page's loads may land before or after the MMA thread
+    looks.  (A slot's barrier once ran two phases ahead of that thread in a tile of two pages, in a build
+    with clock marks that slowed it; the ordinary build of that version passes this test, which guards
+    the reuse of the barriers as such, not that race.)  Every launch must end without a wait that ran
+    out and give the same bits; the first is compared with the plain kernel."""
+    from odin_infer_b200.csrc import ops
+    n_q, n_kv, hd = 32, 8, 128
+    torch.manual_seed(77)
+    news = [1, 17, 63, 64, 65, 100, 127, 128, 129, 191, 192, 193, 255, 256, 257, 300] * 6
+    olds = [(i * 37) % 130 if i % 3 == 0 else 0 for i in range(len(news))]
+    parts = list(zip(olds, news))
+    lengths = [a + b for a, b in parts]
+    B = len(parts)
+    k_cache, v_cache, bt = paged_cache(B, lengths, n_kv, hd, torch.bfloat16)
+    for s, n in enumerate(lengths):
+        for pg in range((n + 63) // 64):
+            page = int(bt[s, pg])
+            m = min(n, pg * 64 + 64) - pg * 64
+            k_cache[page, :, :m] = torch.randn(n_kv, m, hd, device=DEV).bfloat16()
+            v_cache[page, :, :m] = torch.randn(n_kv, m, hd, device=DEV).bfloat16()
+    T = sum(news)
+    q = torch.randn(T, n_q * hd, device=DEV).bfloat16()
+    seq_start = torch.tensor([0] + list(np.cumsum(news)), dtype=torch.int32, device=DEV)
+    seq_len_after = torch.tensor(lengths, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([a + i for a, b in parts for i in range(b)], dtype=torch.int32, device=DEV)
+    tok_seq = torch.tensor([s for s, (a, b) in enumerate(parts) for _ in range(b)], dtype=torch.int32, device=DEV)
+    first = None
+    for rep in range(30):
+        out = torch.empty(T, n_q * hd, device=DEV, dtype=torch.bfloat16)
+        ops.attention_prefill(q, out, B, max(news), n_q, n_kv, hd, k_cache, v_cache, seq_start, seq_len_after, bt, 0)
+        ops.attention_prefill_check()
+        if first is None:
+            first = out
+            assert not torch.isnan(out.float()).any()
+            plain = torch.empty_like(out)
+            ops.attention_plain(q, plain, n_q, n_kv, hd, k_cache, v_cache, tok_pos, tok_seq, bt, 0)
+            close(out.float(), plain.float(), 1e-2)
+        else:
+            assert torch.equal(out, first), f"launch {rep} differs from the first"
+
+
 @pytest.mark.parametrize("n,far", [(2048, 100), (8448, 100), (8448, 8191)])
 def test_attention_prefill_long_prompt_far_key(n, far):
     """Thousands of tokens: one key of the prompt is made to dominate every later query."""
