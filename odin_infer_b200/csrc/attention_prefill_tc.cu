@@ -30,8 +30,13 @@
 // CTA with Q in tensor memory and K/V shared (one S buffer per head left the softmax warps idle during the
 // head's own products: 748 against 588 us at 8,192 tokens); one CTA per SM with Q in tensor memory, two
 // pages per step and four threads per row (83 against 63 us at 2,048 tokens, 887 against 1,113 TFLOP/s at
-// 32,768); the MMA warp running as a whole with only the MMAs predicated on one lane (no change: the thread is
-// not short of issue slots); a start offset between an SM's two CTAs (no change).
+// 32,768); one CTA per SM with three score buffers of two pages (N 128), sixteen softmax warps, four threads per
+// row, K and V units in two stages (75.8 against 61.5 us at 2,048 tokens, 635 against 518 at 8,192: its sixteen
+// warps take their exponentials at the same time, 1,240 cycles for 32 per thread, which is the XU pipe's rate,
+// and its MMAs still cost the issuing thread 90 to 115 cycles each beside them, as the N 64 ones do here, against
+// 64 alone: two CTAs that drift apart overlap the two kinds of work better than one CTA in step with itself);
+// the MMA warp running as a whole with only the MMAs predicated on one lane (no change); a start offset between
+// an SM's two CTAs (no change).
 //
 // Arithmetic as infer/forward.odin:88-115 (scale 1/sqrt(hd), causal bound t <= pos,
 // maximum-subtracted softmax, weighted sum of values), in 32-bit except the bfloat16
