@@ -36,7 +36,10 @@
 // and its MMAs still cost the issuing thread 90 to 115 cycles each beside them, as the N 64 ones do here, against
 // 64 alone: two CTAs that drift apart overlap the two kinds of work better than one CTA in step with itself);
 // the MMA warp running as a whole with only the MMAs predicated on one lane (no change); a start offset between
-// an SM's two CTAs (no change).
+// an SM's two CTAs (no change); the scores issued by one thread and P V by another, K pages asked for by a softmax
+// thread (68.5 us at 2,048, 590 at 8,192: the scores after next then wait for the P V product's commit to cross
+// from one thread to the other, and each thread still takes ~95 cycles per MMA).  In isolation a thread needs
+// ~59 cycles to issue one tcgen05.mma into an idle tensor core, whatever N (mma_probe.cu, patterns 4 and 5).
 //
 // Arithmetic as infer/forward.odin:88-115 (scale 1/sqrt(hd), causal bound t <= pos,
 // maximum-subtracted softmax, weighted sum of values), in 32-bit except the bfloat16

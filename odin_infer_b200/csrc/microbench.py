@@ -141,12 +141,18 @@ def main(argv=None) -> int:
                  ("two CTAs: page of 64 keys, two commits per group", 2, 0, False, 2, 2, 512),
                  ("two pages (8 P V + 8 scores N 128)", 3, 0, False, 0, 1, 1024),
                  ("two pages, one commit per group", 3, 0, False, 1, 1, 1024),
-                 ("two CTAs: two pages, one commit per group", 3, 0, False, 1, 2, 1024)]
+                 ("two CTAs: two pages, one commit per group", 3, 0, False, 1, 2, 1024),
+                 ("eight P V MMAs (N 128), a commit and the wait for it", 4, 0, False, 0, 1, 512),
+                 ("eight score MMAs (N 64), a commit and the wait for it", 5, 0, False, 0, 1, 256),
+                 ("two CTAs: eight P V MMAs (N 128), a commit and the wait for it", 4, 0, False, 0, 2, 512)]
         for name, pattern, n, b_mn, commits, per_sm, arith in cases:
             iters = 4096 if pattern <= 1 else 512
-            best = min(ops.mma_probe(pattern, n, b_mn, commits, per_sm, iters) for _ in range(3))
-            print(json.dumps({"kernel": "mma-rate", "case": name, "cycles": round(best, 1),
-                              "unit": "per MMA" if pattern <= 1 else "per step of a CTA", "arithmetic": arith}))
+            best, issue = min(ops.mma_probe(pattern, n, b_mn, commits, per_sm, iters) for _ in range(3))
+            line = {"kernel": "mma-rate", "case": name, "cycles": round(best, 1),
+                    "unit": "per MMA" if pattern <= 1 else "per step of a CTA", "arithmetic": arith}
+            if pattern >= 4:
+                line["cycles_until_issued"] = round(issue, 1)
+            print(json.dumps(line))
         return 0
     elif args.kernel == "head-prep":
         # the prompt's head preparation: per-head norm of q and k, rotation, cache write, from a bfloat16 projection

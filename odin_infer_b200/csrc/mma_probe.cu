@@ -11,6 +11,11 @@
 //      products P V (A from tensor memory, N 128, V MN-major), then the eight score products
 //      after next (N 64) into the buffer that P was read from; two score buffers in turn
 //   3  two pages a step: eight P V products over 128 keys, then eight score products with N 128
+//   4  groups of eight MMAs (A from tensor memory, N 128, B MN-major) each followed by a commit and the wait
+//      for it, as a thread issues them that has to wait for its operands in between: the time until the
+//      eighth MMA is issued is counted apart (second half of `cycles`), so that one sees whether issuing
+//      into an idle tensor core returns at once or takes as long as the MMAs before it run
+//   5  the same with A and B from shared memory and N 64
 // `commits` adds the commits that a kernel needs after each group of MMAs (to barriers that
 // nobody waits on).  Launched with one or two CTAs per SM (the second by a larger or smaller
 // shared-memory request), as many CTAs as SMs x that, so that every SM does the same.
@@ -21,7 +26,7 @@ namespace {
 
 struct ProbeParams {
     int pattern, n, b_mn, commits, iters, tmem_cols;
-    long long* cycles;  // [grid]
+    long long* cycles;  // [2 x grid]: the whole run, and for patterns 4 and 5 the part spent issuing
     int* error;
 };
 
@@ -93,6 +98,30 @@ __global__ void __launch_bounds__(128, 2) mma_probe_kernel(const ProbeParams p) 
                 if (p.commits >= 1) tc::umma_commit(&idle[2]);
                 if (p.commits >= 2) tc::umma_commit(&idle[3]);
             }
+        } else if (p.pattern >= 4) {
+            constexpr uint32_t idesc_o = tc::make_idesc_bf16_b_mn(128, 128);
+            constexpr uint32_t idesc_s = tc::make_idesc_bf16(128, 64);
+            long long issue = 0;
+            bool ok = true;
+            for (int i = 0; i < p.iters && ok; ++i) {
+                const long long g0 = clock64();
+                if (p.pattern == 4) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        tc::umma_bf16_ts(t0 + 128, t0 + j * 8, tc::make_smem_desc_sw128_mn(b_u + 32768 + j * 2048, 16384, 1024),
+                                         idesc_o, (i > 0 || j > 0) ? 1u : 0u);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)
+                        tc::umma_bf16(t0, tc::make_smem_desc_sw128(a_u + (k >> 2) * 16384 + (k & 3) * 32),
+                                      tc::make_smem_desc_sw128(b_u + (k >> 2) * 8192 + (k & 3) * 32), idesc_s, k > 0 ? 1u : 0u);
+                }
+                issue += clock64() - g0;
+                tc::umma_commit(&idle[0]);
+                ok = tc::mbar_wait(&idle[0], i & 1, abort_flag);
+                tc::fence_after_sync();
+            }
+            p.cycles[gridDim.x + blockIdx.x] = issue;
         } else {
             constexpr uint32_t idesc_s = tc::make_idesc_bf16(128, 128);
             constexpr uint32_t idesc_o = tc::make_idesc_bf16_b_mn(128, 128);
@@ -132,11 +161,11 @@ int* probe_error_flag() {
 
 }  // namespace
 
-// cycles: [SMs * per_sm] 64-bit counts on the device, one per CTA.  iters: MMAs of the run
-// (patterns 0 and 1, a multiple of 8) or pages / page pairs (patterns 2 and 3).
+// cycles: [2 * SMs * per_sm] 64-bit counts on the device: one per CTA, then (patterns 4 and 5) one per CTA for the issuing.  iters: MMAs of the run
+// (patterns 0 and 1, a multiple of 8), pages / page pairs (patterns 2 and 3) or groups (4 and 5).
 extern "C" int odin_mma_probe(int pattern, int n, int b_mn, int commits, int per_sm, int iters, void* cycles,
                               void* stream) {
-    if (pattern < 0 || pattern > 3 || per_sm < 1 || per_sm > 2 || iters < 8 || iters > 65536) return ODIN_ERR_BAD_ARG;
+    if (pattern < 0 || pattern > 5 || per_sm < 1 || per_sm > 2 || iters < 8 || iters > 65536) return ODIN_ERR_BAD_ARG;
     if (pattern <= 1 && (n < 16 || n > 256 || n % 16 != 0 || iters % 8 != 0)) return ODIN_ERR_BAD_ARG;
     if (pattern <= 1 && b_mn && n % 64 != 0) return ODIN_ERR_BAD_ARG;
     if (pattern == 1 && per_sm == 2 && n > 224) return ODIN_ERR_BAD_ARG;  // the accumulator and A share 256 columns

@@ -452,11 +452,13 @@ def attention_prefill_check() -> None:
 
 
 def mma_probe(pattern: int, n: int = 64, b_mn: bool = False, commits: int = 0, per_sm: int = 1,
-              iters: int = 4096) -> float:
-    """Cycles of the SM clock per MMA (patterns 0 and 1) or per page / page pair (2 and 3) that the median
-    CTA of the measuring kernel in mma_probe.cu took; per_sm CTAs share every SM's tensor core."""
+              iters: int = 4096) -> tuple[float, float]:
+    """Cycles of the SM clock per MMA (patterns 0 and 1), per page / page pair (2 and 3) or per group of eight
+    MMAs with its commit and wait (4 and 5) that the median CTA of the measuring kernel in mma_probe.cu took,
+    and (4 and 5) the part of it until the eighth MMA was issued; per_sm CTAs share every SM's tensor core."""
     sms = torch.cuda.get_device_properties(0).multi_processor_count
-    cycles = torch.zeros(sms * per_sm, dtype=torch.int64, device="cuda:0")
+    grid = sms * per_sm
+    cycles = torch.zeros(2 * grid, dtype=torch.int64, device="cuda:0")
     _check(_fn("mma_probe", "odin_mma_probe")(
         c_int(pattern), c_int(n), c_int(1 if b_mn else 0), c_int(commits), c_int(per_sm), c_int(iters),
         _ptr(cycles), _stream()), "mma_probe")
@@ -465,7 +467,8 @@ def mma_probe(pattern: int, n: int = 64, b_mn: bool = False, commits: int = 0, p
     f.restype = c_int
     if f() != 0:
         raise KernelError("mma_probe: a device-side wait ran out")
-    return float(cycles.sort().values[cycles.numel() // 2].item()) / iters
+    whole, issue = cycles[:grid].sort().values, cycles[grid:].sort().values
+    return float(whole[grid // 2].item()) / iters, float(issue[grid // 2].item()) / iters
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
