@@ -756,6 +756,26 @@ def test_attention_prefill_against_plain_kernel_and_reference(geom, window):
         r += b
 
 
+def test_mma_probe_measures_every_pattern():
+    """The measuring kernel behind `microbench mma-rate`: every pattern runs to its end (no wait runs out) and
+    reports plausible cycle counts: an MMA of N 256 takes longer than one of N 64, and a group that is waited
+    for takes longer than issuing it."""
+    from odin_infer_b200.csrc import ops
+    n64, _ = ops.mma_probe(0, 64, False, 0, 1, 256)
+    n256, _ = ops.mma_probe(0, 256, False, 0, 1, 256)
+    assert 8 < n64 < n256 < 2000
+    ts, _ = ops.mma_probe(1, 128, True, 0, 2, 256)
+    assert 8 < ts < 2000
+    for pattern in (2, 3):
+        page, _ = ops.mma_probe(pattern, 0, False, 1, 1, 32)
+        assert 100 < page < 20000
+    for pattern in (4, 5):
+        whole, issue = ops.mma_probe(pattern, 0, False, 0, 1, 32)
+        assert 0 < issue < whole < 20000
+    with pytest.raises(ops.KernelError):
+        ops.mma_probe(0, 72, False, 0, 1, 256)       # N is no multiple of 16
+
+
 def test_attention_prefill_many_short_tiles_again_and_again():
     """Hundreds of tiles of one to five pages on persistent CTAs, launched thirty times: the barriers of a
     tile are armed again for the next one, and a page's loads may land before or after the MMA thread
