@@ -7,8 +7,8 @@
 //   warp 1      allocates tensor memory and issues the MMAs (one thread):
 //               S = Q K^T (tcgen05.mma M128 N64, K and Q both K-major), then
 //               O += P V (M128 N=head_dim, P read from tensor memory, V MN-major exactly
-//               as the cache stores it), accumulators S and O in TMEM; one commit per product tells
-//               the softmax (or the next rescaling) and the producer (the stage is free) at once;
+//               as the cache stores it), accumulators S and O in TMEM; one commit per page (behind the
+//               scores after next) tells the softmax, the next rescaling and the producer (stages free);
 //   warps 2..9  two threads per query row (32 keys of the page each; the row maximum is
 //               exchanged through shared memory): read S from TMEM, mask, online
 //               softmax in 32-bit registers (exponentials as ex2 of one fused
@@ -25,7 +25,7 @@
 // next scores overwrite P), so a page costs about the larger of the two plus the two hand-overs; the tensor core
 // itself would need 570 cycles per page and SM (measured in isolation, mma_probe.cu: an MMA of N 64 takes 57
 // cycles for 32 of arithmetic).  Every wait and commit of the MMA thread is on that chain, which is why K and V
-// pages share barriers and each product has one commit (65.5 -> 61.5 us at 2,048 tokens, 553 -> 517 us at 8,192).
+// pages share barriers and a page has one commit (65.5 -> 61.5 us at 2,048 tokens, 553 -> 510 us at 8,192).
 // Variants that were built and measured slower at every length, and are not kept: two heads of a kv head per
 // CTA with Q in tensor memory and K/V shared (one S buffer per head left the softmax warps idle during the
 // head's own products: 748 against 588 us at 8,192 tokens); one CTA per SM with Q in tensor memory, two
@@ -123,7 +123,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     uint64_t* kv_full = bars;          // [2] slot j (barrier j & 1): K page j and V page j - 2 landed (see the producer)
     uint64_t* s_full = bars + 2;       // [2] scores complete in S buffer b: the softmax may read, the K stage is free
     uint64_t* p_full = bars + 4;       // [2] P written over S buffer b, O rescaled if need be
-    uint64_t* pv_done = bars + 6;      // [2] the P V product of an iteration with buffer b is complete: its V stage is free
+    uint64_t* pv_done = bars + 6;      // [2] the P V product of one of the last two pages (buffer b) is complete
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* s_max = reinterpret_cast<float*>(bars + 16);  // [2 buffers][2 halves][128 rows]: the pair's exchange
@@ -227,9 +227,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 const int v_page = j - 2;
                 // Slot j - 2 (the barrier's last use) must have landed AND the MMA thread must have seen it before the
                 // barrier is armed again, or a parity wait would mistake the phase after next for its own.  The scores
-                // of page j - 2 being complete says both (they were issued after that wait), and frees K's stage.
+                // of page j - 2 being complete says both (they were issued after that wait), and frees K's stage
+                // and V's: P V of page j - 4 was issued before them, and a commit covers all MMAs before it.
                 if (j >= 2 && !tc::mbar_wait(&s_full[b], ((j - 2) >> 1) & 1, abort_flag)) { report_attn(p.error, 1, j, n_pages); break; }
-                if (has_v && j >= 4 && !tc::mbar_wait(&pv_done[b], ((j - 4) >> 1) & 1, abort_flag)) { report_attn(p.error, 2, j, n_pages); break; }
                 tc::mbar_expect_tx(&kv_full[b], (has_k ? KV_TILE : 0) + (has_v ? KV_TILE : 0));
                 if (has_v) {
                     const int row = (bt[page_a + v_page] * p.Hkv + kvh) * PAGE_T;
@@ -300,9 +300,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                                          j > 0 ? 1u : 0u);
                 }
                 CLK(0, 15);  // P V MMAs issued
-                tc::umma_commit(&pv_done[stage]);
-                CLK(0, 13);  // P V issued
+                // One commit a page: the one behind the scores after next also tells that this P V is over;
+                // only the last two pages, which no scores follow, have a commit of their own.
                 if (it + 2 < n_pages) issue_s(it + 2);  // its S buffer was read before p_full(it)
+                else tc::umma_commit(&pv_done[stage]);
+                CLK(0, 13);  // P V and the scores after next issued
             }
         }
     } else {
@@ -368,7 +370,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             if (it > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
                 // O is touched only when the scaling maximum moved; the previous P V must be over first.
                 // Each thread of the pair rescales half of the row's columns.
-                if (!tc::mbar_wait(&pv_done[(it - 1) & 1], ((it - 1) >> 1) & 1, abort_flag)) { report_attn(p.error, 7, it, n_pages); ok = false; break; }
+                // (told by the commit behind the scores of page it + 1, which were issued after it, or by its own)
+                const bool pv_ok = (it + 1 < n_pages) ? tc::mbar_wait(&s_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_flag)
+                                                      : tc::mbar_wait(&pv_done[(it - 1) & 1], 0, abort_flag);
+                if (!pv_ok) { report_attn(p.error, 7, it, n_pages); ok = false; break; }
                 tc::fence_after_sync();
 #pragma unroll 1
                 for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 32) {
@@ -400,7 +405,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             if (lane == 0) tc::mbar_arrive(&p_full[stage]);
             CLK(1, 24);  // P handed over
         }
-        if (ok && !tc::mbar_wait(&pv_done[(n_pages - 1) & 1], ((n_pages - 1) >> 1) & 1, abort_flag)) { report_attn(p.error, 8, n_pages, n_pages); ok = false; }
+        if (ok && !tc::mbar_wait(&pv_done[(n_pages - 1) & 1], 0, abort_flag)) { report_attn(p.error, 8, n_pages, n_pages); ok = false; }
         if (ok) {
             tc::fence_after_sync();
             // the row's sum is the pair's two shares
