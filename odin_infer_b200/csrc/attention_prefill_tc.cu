@@ -280,8 +280,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             }
             for (int it = 0; it < n_pages && ok; ++it) {
                 const int stage = it & 1;
-                if (!tc::mbar_wait(&p_full[stage], (it >> 1) & 1, abort_flag)) { report_attn(p.error, 4, it, n_pages); ok = false; break; }
+                // the pages first: they land long before P is handed over, and what follows that hand-over is on the
+                // chain that a page's time is made of
                 if (!tc::mbar_wait(&kv_full[stage], ((it + 2) >> 1) & 1, abort_flag)) { report_attn(p.error, 5, it, n_pages); ok = false; break; }
+                if (!tc::mbar_wait(&p_full[stage], (it >> 1) & 1, abort_flag)) { report_attn(p.error, 4, it, n_pages); ok = false; break; }
                 tc::fence_after_sync();
                 CLK(0, 11);  // P and V are there
                 const uint64_t vd = stage ? v_desc[1] : v_desc[0];
